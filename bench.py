@@ -1,0 +1,283 @@
+#!/usr/bin/env python
+"""Headline benchmark: Q4_K decode matvec at the Llama-3-8B FFN-up shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One *step* is one pass of the matvec over a ring of RING distinct device copies
+of the 14336 x 4096 Q4_K weight (RING x 33 MB > the 126 MB L2, so every launch
+streams its weights from HBM).  `value` is weight-GB/s with everything resident
+in HBM (CUDA events on the launching stream); `e2e` is the same metric through
+the host-pointer C-ABI call a binding of the reference's `QuantKernel::gemv`
+makes (pinned host activations in, host outputs back, copies inside the timed
+region).  With N > 1 ranks every rank owns a 14336-row shard of an
+(N*14336) x 4096 matrix and the shard outputs are all-gathered over NCCL after
+every matvec (weak scaling).
+
+`--impl reference` times the CPU restatement of the reference's own fastest
+tier (oracle/qk_cpu_simd.c: AVX-512 / AVX2 rows under a row-parallel driver) on
+the host cores for the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from oxillama_b200 import synth as S  # noqa: E402
+
+ROWS, COLS, QTYPE = 14336, 4096, S.Q4_K
+RING = 16
+METRIC = "q4_k_gemv_weight_bandwidth"
+UNIT = "GB/s"
+WORKLOAD = "config[1]: Q4_K 14336x4096 matvec, M=1, f32 N(0,1) activations, seed 0"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_gemv_rate(seconds: float, threads: int | None = None):
+    """Times the reference's CPU tier restated in oracle/qk_cpu_simd.c on this host."""
+    so = os.path.join(ROOT, "oracle", "_build", "libqk_cpu_simd.so")
+    if not os.path.exists(so):
+        subprocess.check_call(["make", "-s", "-C", os.path.join(ROOT, "oracle")])
+    lib = C.CDLL(so)
+    tier = lib.qk_cpu_best_tier()
+    cores = threads or lib.qk_cpu_max_threads()
+    w = S.gen_weight(QTYPE, ROWS, COLS, seed=0, stream=0)
+    x = S.gen_acts(1, COLS, seed=0)[0]
+    y = np.zeros(ROWS, np.float32)
+    used = C.c_int()
+
+    def once():
+        lib.qk_cpu_gemv(QTYPE, tier, cores, C.c_void_p(w.ctypes.data), C.c_size_t(ROWS), C.c_size_t(COLS),
+                        C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data), C.byref(used))
+
+    for _ in range(3):
+        once()
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        once()
+        n += 1
+    dt = time.perf_counter() - t0
+    tiers = {0: "scalar", 1: "AVX2+FMA", 2: "AVX-512F"}
+    return {"value": w.size * n / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} matvecs of the full 14336x4096 Q4_K weight in {dt:.1f} s, {tiers[used.value]} rows, "
+                      f"row-parallel over {cores} threads", "ms_per_matvec": dt / n * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = max(1.0, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_gemv_rate(min(per_step, 1.0))
+    vals = [cpu_gemv_rate(per_step) for _ in range(args.steps)]
+    v = statistics.mean(r["value"] for r in vals)
+    base = vals[-1]
+    base["value"] = v
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": RING * base["ms_per_matvec"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "host cores only; each step is a bounded sample of the workload"},
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    from oxillama_b200.kernels import Context, CudaQuantKernel, QuantTensor
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path for --impl ours")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = Context(local)
+
+    # ---- synthetic workload: RING distinct shards of this rank's rows
+    host_w = [S.gen_weight(QTYPE, ROWS, COLS, seed=0, stream=rank * RING + i) for i in range(RING)]
+    dws = [DeviceWeights(QTYPE, w, ROWS, COLS, ctx=ctx) for w in host_w]
+    algo_bytes = dws[0].algo_bytes
+    x_host = torch.from_numpy(S.gen_acts(1, COLS, seed=0)[0]).pin_memory()
+    y_host = torch.empty(ROWS, dtype=torch.float32).pin_memory()
+    x = x_host.cuda()
+    ys = [torch.empty(ROWS, device="cuda") for _ in range(RING)]
+    gathered = torch.empty(world * ROWS, device="cuda") if world > 1 else None
+    stream = torch.cuda.Stream()
+
+    def step():
+        for i in range(RING):
+            dws[i].gemv(x, ys[i], stream=stream)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, ys[i])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            step()
+        barrier()
+        check_device_status(ctx, stream)
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        barrier()
+        ev[0].record(stream)
+        for _ in range(args.steps):
+            step()
+        ev[1].record(stream)
+        barrier()
+        ms = ev[0].elapsed_time(ev[1])
+        check_device_status(ctx, stream)
+
+        # kernel-only launch time for the roofline (no collective in the region)
+        barrier()
+        e2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        e2[0].record(stream)
+        for _ in range(args.steps):
+            for i in range(RING):
+                dws[i].gemv(x, ys[i], stream=stream)
+        e2[1].record(stream)
+        torch.cuda.synchronize()
+        kernel_ms = e2[0].elapsed_time(e2[1]) / (args.steps * RING)
+
+    # ---- end to end through the reference-facing host-pointer call
+    kern = CudaQuantKernel(QTYPE, ctx)
+    qts = [QuantTensor(w, (ROWS, COLS), QTYPE) for w in host_w]
+    xn, yn = x_host.numpy(), y_host.numpy()
+    for qt in qts:  # first call uploads and caches the weights, as a model load does
+        kern.gemv(qt, xn, yn)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for qt in qts:
+            kern.gemv(qt, xn, yn)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms, e2e_s * 1e3, kernel_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, kernel_ms = (float(v) for v in t.cpu())
+    total_bytes = algo_bytes * RING * args.steps * world
+    if rank == 0:
+        peak, which = peaks()
+        achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": total_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "ring_copies": RING,
+                       "l2": f"{RING} distinct weight copies ({RING * algo_bytes / 1e6:.0f} MB) rotate, larger than L2",
+                       "sharding": "none" if world == 1 else f"{world} row shards of ({world}x14336)x4096, NCCL all-gather of y per matvec"},
+            "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": RING * COLS * 4, "d2h_bytes_per_step": RING * ROWS * 4,
+                    "note": "qk_gemv host-pointer call per matvec; weights cached on device after first use"},
+            "gpu_launches": RING * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": which, "traffic": None, "algorithmic_bytes_per_launch": algo_bytes,
+                         "us_per_launch": kernel_ms * 1e3},
+            "clocks": clocks,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_gemv_rate(args.cpu_seconds)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,153 @@
+/*
+ * qk_cuda.h — C ABI of the B200 (sm_100a) quantized dequant-dot backend.
+ *
+ * This is the boundary a binding for OxiLLaMa's `QuantKernel` trait links
+ * against (crates/oxillama-quant/src/traits.rs:21-183 of the reference): the
+ * first group of entry points takes plain host pointers and sizes exactly as
+ * the trait methods take slices; the second group keeps weights resident on
+ * the GPU and takes device pointers, for callers that own device memory.
+ *
+ * Conventions
+ *  - Every function returns a qk_status; nothing throws or aborts.
+ *  - The caller owns every buffer; the library keeps only what it allocated
+ *    itself (contexts, uploaded weights, its own scratch).
+ *  - `type` is the GGUF tensor type id (crates/oxillama-gguf/src/types.rs:70-125):
+ *    Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q6_K = 14, IQ4_XS = 23.
+ *  - A weight matrix is [n_rows = out_features][n_cols = in_features], stored as
+ *    n_rows consecutive rows of ceil(n_cols / block_size) blocks in GGUF byte
+ *    layout (reference/q4_k.rs:110-131).  A partial last block is legal; the
+ *    columns past n_cols contribute nothing.
+ *  - One context drives one GPU (one process per GPU); a context may be used
+ *    from any thread, one call at a time.
+ *  - There is no CPU fallback: without a usable CUDA device every compute
+ *    entry point fails with QK_CUDA_ERROR.
+ */
+#ifndef QK_CUDA_H
+#define QK_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  0..7 map one to one onto the variants of the reference's
+ * QuantError (crates/oxillama-quant/src/error.rs:10-71); the rest are new. */
+typedef enum qk_status {
+  QK_OK = 0,
+  QK_UNSUPPORTED_TYPE = 1,     /* QuantError::UnsupportedType */
+  QK_BLOCK_SIZE_MISMATCH = 2,  /* QuantError::BlockSizeMismatch */
+  QK_DIMENSION_MISMATCH = 3,   /* QuantError::DimensionMismatch */
+  QK_KERNEL_ERROR = 4,         /* QuantError::KernelError */
+  QK_BLOCK_COUNT_MISMATCH = 5, /* QuantError::BlockCountMismatch */
+  QK_BUFFER_TOO_SMALL = 6,     /* QuantError::BufferTooSmall */
+  QK_INTERNAL = 7,             /* QuantError::Internal */
+  QK_CUDA_ERROR = 100,         /* a CUDA runtime call failed; see qk_last_error */
+  QK_TIMEOUT = 101,            /* a bounded device-side wait ran out */
+  QK_INVALID_ARGUMENT = 102    /* null pointer, bad handle, bad range */
+} qk_status;
+
+#define QK_TYPE_Q4_0 2
+#define QK_TYPE_Q8_0 8
+#define QK_TYPE_Q4_K 12
+#define QK_TYPE_Q6_K 14
+#define QK_TYPE_IQ4_XS 23
+
+typedef struct qk_ctx qk_ctx;         /* one GPU + its stream and scratch */
+typedef struct qk_weights qk_weights; /* one weight matrix (or row shard) resident in HBM */
+
+/* ---- context: stands where KernelDispatcher::new() stands (dispatch.rs:128-131) ---- */
+int qk_init(int device, qk_ctx **out);
+int qk_shutdown(qk_ctx *ctx);
+/* Copies the text of the last error raised on this context (empty if none). */
+int qk_last_error(qk_ctx *ctx, char *buf, size_t buf_len);
+
+/* ---- trait getters: QuantKernel::{block_size, block_bytes, name} (traits.rs:175-182) ---- */
+size_t qk_block_size(int type);   /* 0 for an unsupported type */
+size_t qk_block_bytes(int type);  /* 0 for an unsupported type */
+const char *qk_name(int type);    /* "Q4_0", "Q8_0", "Q4_K", "Q6_K", "IQ4_XS", or NULL */
+
+/* ================= host-pointer entry points (the trait methods) ================= */
+
+/* QuantKernel::dequant_block (traits.rs:28; e.g. reference/q4_k.rs:52-102).
+ * One block -> block_size f32 values, bit-identical to the scalar reference.
+ * block_len < block_bytes or out_len < block_size -> QK_BUFFER_TOO_SMALL. */
+int qk_dequant_block(qk_ctx *ctx, int type, const uint8_t *block, size_t block_len, float *out,
+                     size_t out_len);
+
+/* Whole-matrix form of the same arithmetic, block by block in order, padding
+ * columns dropped: what the reference's MoE loader does with dequant_block
+ * (crates/oxillama-arch/src/llama/model.rs:843-886).  out is [n_rows x n_cols]. */
+int qk_dequant_matrix(qk_ctx *ctx, int type, const uint8_t *w, size_t w_len, size_t n_rows,
+                      size_t n_cols, float *out, size_t out_len);
+
+/* QuantKernel::gemv (traits.rs:40-45; e.g. reference/q4_k.rs:104-184).
+ * y[0..n_rows) = W x; y is overwritten.  x_len < n_cols or y_len < n_rows ->
+ * QK_DIMENSION_MISMATCH; w_len short -> QK_BUFFER_TOO_SMALL. */
+int qk_gemv(qk_ctx *ctx, int type, const uint8_t *w, size_t w_len, size_t n_rows, size_t n_cols,
+            const float *x, size_t x_len, float *y, size_t y_len);
+
+/* QuantKernel::gemm (traits.rs:59-67; e.g. reference/q4_k.rs:186-201): m
+ * independent gemvs.  x is [m x k] row-major, y is [m x n] row-major and is
+ * overwritten; n = weight rows, k = weight columns. */
+int qk_gemm(qk_ctx *ctx, int type, const uint8_t *w, size_t w_len, const float *x, size_t x_len,
+            float *y, size_t y_len, size_t m, size_t n, size_t k);
+
+/* QuantKernel::matvec_q8_fused (traits.rs:89-173; overrides reference/q4_k.rs:218-333,
+ * reference/q6_k.rs:212-354; free function reference/q4_0.rs:159-232).
+ * acts_q8 holds ceil(n_cols/32) Q8_0 blocks (34 bytes each, already quantized
+ * by the caller); out[row] += dot.  ACCUMULATES. */
+int qk_matvec_q8_fused(qk_ctx *ctx, int type, const uint8_t *w, size_t w_len,
+                       const uint8_t *acts_q8, size_t acts_len, float *out, size_t out_len,
+                       size_t n_rows, size_t n_cols);
+
+/* quantize_f32_to_q8_0 (crates/oxillama-quant/src/quantize.rs:58-75,190-210).
+ * n must be a multiple of 32 (else QK_DIMENSION_MISMATCH); out needs n/32*34 bytes. */
+int qk_quantize_q8_0(qk_ctx *ctx, const float *x, size_t n, uint8_t *out, size_t out_len);
+
+/* The host-pointer calls above keep the device copy of a weight matrix they
+ * have seen, keyed by (pointer, length, type, shape) — weights are immutable
+ * after load in the reference (llama/model.rs:805-822).  Call this before
+ * reusing or rewriting that host memory.  w == NULL drops everything. */
+int qk_weights_cache_evict(qk_ctx *ctx, const uint8_t *w);
+
+/* ================= device-resident entry points (new; no reference counterpart) ================= */
+
+/* Uploads rows [row_begin, row_end) of a [n_rows x n_cols] matrix (a row shard;
+ * pass 0, n_rows for the whole matrix) and re-tiles them for the kernels. */
+int qk_weights_upload(qk_ctx *ctx, int type, const uint8_t *w, size_t w_len, size_t n_rows,
+                      size_t n_cols, size_t row_begin, size_t row_end, qk_weights **out);
+int qk_weights_free(qk_ctx *ctx, qk_weights *h);
+/* Shard shape: rows held, columns, and the algorithmic bytes of the shard
+ * (rows * ceil(cols/block_size) * block_bytes). */
+int qk_weights_info(const qk_weights *h, int *type, size_t *rows, size_t *cols, size_t *bytes);
+
+/* y_dev[0..rows) = W_shard x_dev.  Device pointers; enqueued on `stream`
+ * (a cudaStream_t, NULL = the context's own stream); returns without waiting. */
+int qk_gemv_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_dev, void *stream);
+
+/* y_dev[i*ldy + j] = dot(W_shard row j, x_dev row i), i < m, j < rows.  x_dev is
+ * [m x cols] row-major.  ldy >= rows lets a row shard write its column block of
+ * a wider [m x n] output in place. */
+int qk_gemm_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_dev, size_t m,
+                size_t ldy, void *stream);
+
+/* out_dev[rows x cols] f32 = dequantised shard, bit-identical to dequant_block. */
+int qk_dequant_dev(qk_ctx *ctx, const qk_weights *h, float *out_dev, void *stream);
+
+/* out_dev[row] += dot with already-quantised Q8_0 activations on the device. */
+int qk_matvec_q8_fused_dev(qk_ctx *ctx, const qk_weights *h, const uint8_t *acts_q8_dev,
+                           float *out_dev, void *stream);
+
+/* Q8_0 activation encoder on device memory; n a multiple of 32. */
+int qk_quantize_q8_0_dev(qk_ctx *ctx, const float *x_dev, size_t n, uint8_t *out_dev, void *stream);
+
+/* Reads and clears the device-side status word of the context (bounded waits
+ * that ran out, range checks that tripped).  Synchronises `stream`. */
+int qk_check_device_status(qk_ctx *ctx, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QK_CUDA_H */

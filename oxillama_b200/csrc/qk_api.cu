@@ -1,0 +1,477 @@
+// C ABI of the backend (see include/qk_cuda.h): argument checking in the
+// reference's order, the context (stream, scratch, weight cache), and the
+// choice of kernel for each shape.  Nothing here computes on the CPU: a call
+// that cannot reach the GPU returns QK_CUDA_ERROR.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "../../include/qk_cuda.h"
+#include "qk_kernels.h"
+
+struct qk_weights {
+  QkLayout L;
+  uint8_t *dev;
+  int device;
+  size_t algo_bytes;
+};
+
+struct qk_ctx {
+  int device;
+  int sm_count;
+  cudaStream_t stream;
+  unsigned *status_dev;
+  std::string err;
+  std::mutex mu;
+  // scratch for the host-pointer entry points
+  void *sa = nullptr, *sb = nullptr;
+  size_t sa_cap = 0, sb_cap = 0;
+  // weight cache for the host-pointer entry points
+  typedef std::tuple<const void *, size_t, int, size_t, size_t> Key;
+  std::map<Key, qk_weights *> cache;
+  size_t cache_bytes = 0, cache_cap = (size_t)64 << 30;
+  bool force_simple = false;
+};
+
+#define CK(ctx, call)                                                                     \
+  do {                                                                                    \
+    cudaError_t e__ = (call);                                                             \
+    if (e__ != cudaSuccess) {                                                             \
+      (ctx)->err = std::string(#call) + ": " + cudaGetErrorString(e__);                   \
+      return QK_CUDA_ERROR;                                                               \
+    }                                                                                     \
+  } while (0)
+
+static bool type_ok(int t) {
+  return t == QK_TYPE_Q4_0 || t == QK_TYPE_Q8_0 || t == QK_TYPE_Q4_K || t == QK_TYPE_Q6_K ||
+         t == QK_TYPE_IQ4_XS;
+}
+
+extern "C" size_t qk_block_size(int type) {
+  switch (type) {
+    case QK_TYPE_Q4_0:
+    case QK_TYPE_Q8_0:
+      return 32;
+    case QK_TYPE_Q4_K:
+    case QK_TYPE_Q6_K:
+    case QK_TYPE_IQ4_XS:
+      return 256;
+    default:
+      return 0;
+  }
+}
+
+extern "C" size_t qk_block_bytes(int type) {
+  switch (type) {
+    case QK_TYPE_Q4_0:
+      return 18;
+    case QK_TYPE_Q8_0:
+      return 34;
+    case QK_TYPE_Q4_K:
+      return 144;
+    case QK_TYPE_Q6_K:
+      return 210;
+    case QK_TYPE_IQ4_XS:
+      return 136;
+    default:
+      return 0;
+  }
+}
+
+extern "C" const char *qk_name(int type) {
+  switch (type) {
+    case QK_TYPE_Q4_0:
+      return "Q4_0";
+    case QK_TYPE_Q8_0:
+      return "Q8_0";
+    case QK_TYPE_Q4_K:
+      return "Q4_K";
+    case QK_TYPE_Q6_K:
+      return "Q6_K";
+    case QK_TYPE_IQ4_XS:
+      return "IQ4_XS";
+    default:
+      return nullptr;
+  }
+}
+
+extern "C" int qk_init(int device, qk_ctx **out) {
+  if (!out) return QK_INVALID_ARGUMENT;
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return QK_CUDA_ERROR;
+  if (cudaSetDevice(device) != cudaSuccess) return QK_CUDA_ERROR;
+  qk_ctx *c = new qk_ctx();
+  c->device = device;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major != 10) {
+    delete c;  // the kernels are sm_100a-only
+    return QK_CUDA_ERROR;
+  }
+  c->sm_count = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(&c->status_dev, sizeof(unsigned)) != cudaSuccess ||
+      cudaMemset(c->status_dev, 0, sizeof(unsigned)) != cudaSuccess) {
+    delete c;
+    return QK_CUDA_ERROR;
+  }
+  const char *fs = getenv("QK_FORCE_SIMPLE");
+  c->force_simple = fs && fs[0] == '1';
+  *out = c;
+  return QK_OK;
+}
+
+static void free_weights(qk_weights *h) {
+  if (!h) return;
+  if (h->dev) cudaFree(h->dev);
+  delete h;
+}
+
+extern "C" int qk_shutdown(qk_ctx *c) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  for (auto &kv : c->cache) free_weights(kv.second);
+  if (c->sa) cudaFree(c->sa);
+  if (c->sb) cudaFree(c->sb);
+  cudaFree(c->status_dev);
+  cudaStreamDestroy(c->stream);
+  delete c;
+  return QK_OK;
+}
+
+extern "C" int qk_last_error(qk_ctx *c, char *buf, size_t buf_len) {
+  if (!c || !buf || buf_len == 0) return QK_INVALID_ARGUMENT;
+  snprintf(buf, buf_len, "%s", c->err.c_str());
+  return QK_OK;
+}
+
+static int grow(qk_ctx *c, void **p, size_t *cap, size_t need) {
+  if (need <= *cap) return QK_OK;
+  if (*p) {
+    CK(c, cudaStreamSynchronize(c->stream));
+    cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+  }
+  size_t want = need + need / 4 + 256;
+  CK(c, cudaMalloc(p, want));
+  *cap = want;
+  return QK_OK;
+}
+
+static size_t need_bytes(int type, size_t n_rows, size_t n_cols) {
+  size_t bs = qk_block_size(type), bb = qk_block_bytes(type);
+  return n_rows * ((n_cols + bs - 1) / bs) * bb;
+}
+
+// ------------------------------------------------------------ upload
+static int upload_impl(qk_ctx *c, int type, const uint8_t *w, size_t n_cols, size_t row_begin,
+                       size_t row_end, qk_weights **out) {
+  size_t rows = row_end - row_begin;
+  qk_weights *h = new qk_weights();
+  h->device = c->device;
+  h->dev = nullptr;
+  if (!qk_make_layout(type, rows, n_cols, &h->L)) {
+    delete h;
+    return QK_UNSUPPORTED_TYPE;
+  }
+  h->algo_bytes = need_bytes(type, rows, n_cols);
+  size_t row_bytes = (size_t)h->L.nb * h->L.bb;
+  size_t tiled = h->L.total_bytes ? h->L.total_bytes : 16;
+  cudaError_t e = cudaMalloc(&h->dev, tiled);
+  if (e != cudaSuccess) {
+    c->err = std::string("cudaMalloc(weights): ") + cudaGetErrorString(e);
+    delete h;
+    return QK_CUDA_ERROR;
+  }
+  uint8_t *raw = nullptr;
+  int st = QK_OK;
+  do {
+    if ((e = cudaMemsetAsync(h->dev, 0, tiled, c->stream)) != cudaSuccess) break;
+    if (h->algo_bytes == 0) break;
+    if ((e = cudaMalloc(&raw, h->algo_bytes)) != cudaSuccess) break;
+    if ((e = cudaMemcpyAsync(raw, w + row_begin * row_bytes, h->algo_bytes, cudaMemcpyHostToDevice,
+                             c->stream)) != cudaSuccess)
+      break;
+    if ((e = qk_launch_repack(h->L, raw, h->dev, c->stream)) != cudaSuccess) break;
+  } while (0);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  if (raw) cudaFree(raw);
+  if (e != cudaSuccess) {
+    c->err = std::string("weights upload: ") + cudaGetErrorString(e);
+    free_weights(h);
+    st = QK_CUDA_ERROR;
+  } else {
+    *out = h;
+  }
+  return st;
+}
+
+extern "C" int qk_weights_upload(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows,
+                                 size_t n_cols, size_t row_begin, size_t row_end,
+                                 qk_weights **out) {
+  if (!c || !out) return QK_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (!type_ok(type)) return QK_UNSUPPORTED_TYPE;
+  if (row_begin > row_end || row_end > n_rows) return QK_INVALID_ARGUMENT;
+  if (n_rows >= (1ull << 31) || n_cols >= (1ull << 31)) return QK_INVALID_ARGUMENT;
+  if (w_len < need_bytes(type, n_rows, n_cols)) return QK_BUFFER_TOO_SMALL;
+  if (!w && need_bytes(type, n_rows, n_cols) > 0) return QK_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(c->mu);
+  CK(c, cudaSetDevice(c->device));
+  return upload_impl(c, type, w, n_cols, row_begin, row_end, out);
+}
+
+extern "C" int qk_weights_free(qk_ctx *c, qk_weights *h) {
+  if (!c || !h) return QK_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(c->mu);
+  cudaSetDevice(c->device);
+  free_weights(h);
+  return QK_OK;
+}
+
+extern "C" int qk_weights_info(const qk_weights *h, int *type, size_t *rows, size_t *cols,
+                               size_t *bytes) {
+  if (!h) return QK_INVALID_ARGUMENT;
+  if (type) *type = h->L.type;
+  if (rows) *rows = h->L.rows;
+  if (cols) *cols = h->L.cols;
+  if (bytes) *bytes = h->algo_bytes;
+  return QK_OK;
+}
+
+// Cached device copy for the host-pointer entry points.
+static int cached(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows, size_t n_cols,
+                  qk_weights **out) {
+  qk_ctx::Key k(w, w_len, type, n_rows, n_cols);
+  auto it = c->cache.find(k);
+  if (it != c->cache.end()) {
+    *out = it->second;
+    return QK_OK;
+  }
+  size_t need = need_bytes(type, n_rows, n_cols);
+  if (c->cache_bytes + need > c->cache_cap) {  // simplest policy: start over
+    for (auto &kv : c->cache) free_weights(kv.second);
+    c->cache.clear();
+    c->cache_bytes = 0;
+  }
+  int st = upload_impl(c, type, w, n_cols, 0, n_rows, out);
+  if (st == QK_OK) {
+    c->cache[k] = *out;
+    c->cache_bytes += need;
+  }
+  return st;
+}
+
+extern "C" int qk_weights_cache_evict(qk_ctx *c, const uint8_t *w) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(c->mu);
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  for (auto it = c->cache.begin(); it != c->cache.end();) {
+    if (!w || std::get<0>(it->first) == (const void *)w) {
+      c->cache_bytes -= it->second->algo_bytes;
+      free_weights(it->second);
+      it = c->cache.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  return QK_OK;
+}
+
+// ------------------------------------------------------------ device entry points
+static int gemm_dispatch(qk_ctx *c, const qk_weights *h, const float *x, float *y, size_t m,
+                         size_t ldy, cudaStream_t s) {
+  if (h->L.rows == 0 || m == 0) return QK_OK;
+  if (h->L.cols == 0) {  // empty dot products
+    CK(c, cudaMemset2DAsync(y, ldy * sizeof(float), 0, h->L.rows * sizeof(float), m, s));
+    return QK_OK;
+  }
+  if (!c->force_simple && m <= QK_GEMV_MAX_M && qk_gemv_fast_supported(h->L, (uint32_t)m)) {
+    CK(c, qk_launch_gemv_fast(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->sm_count, s));
+    return QK_OK;
+  }
+  CK(c, qk_launch_gemm_simple(h->L, h->dev, x, y, (uint32_t)m, ldy, s));
+  return QK_OK;
+}
+
+extern "C" int qk_gemv_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, float *y_dev,
+                           void *stream) {
+  if (!c || !h || !x_dev || !y_dev) return QK_INVALID_ARGUMENT;
+  if (h->device != c->device) return QK_INVALID_ARGUMENT;
+  return gemm_dispatch(c, h, x_dev, y_dev, 1, h->L.rows, (cudaStream_t)stream);
+}
+
+extern "C" int qk_gemm_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, float *y_dev,
+                           size_t m, size_t ldy, void *stream) {
+  if (!c || !h || !x_dev || !y_dev) return QK_INVALID_ARGUMENT;
+  if (h->device != c->device) return QK_INVALID_ARGUMENT;
+  if (ldy < h->L.rows) return QK_DIMENSION_MISMATCH;
+  return gemm_dispatch(c, h, x_dev, y_dev, m, ldy, (cudaStream_t)stream);
+}
+
+extern "C" int qk_dequant_dev(qk_ctx *c, const qk_weights *h, float *out_dev, void *stream) {
+  if (!c || !h || !out_dev) return QK_INVALID_ARGUMENT;
+  CK(c, qk_launch_dequant(h->L, h->dev, out_dev, (cudaStream_t)stream));
+  return QK_OK;
+}
+
+extern "C" int qk_matvec_q8_fused_dev(qk_ctx *c, const qk_weights *h, const uint8_t *acts_q8_dev,
+                                      float *out_dev, void *stream) {
+  if (!c || !h || !acts_q8_dev || !out_dev) return QK_INVALID_ARGUMENT;
+  CK(c, qk_launch_fused_simple(h->L, h->dev, acts_q8_dev, out_dev, (cudaStream_t)stream));
+  return QK_OK;
+}
+
+extern "C" int qk_quantize_q8_0_dev(qk_ctx *c, const float *x_dev, size_t n, uint8_t *out_dev,
+                                    void *stream) {
+  if (!c || (n && (!x_dev || !out_dev))) return QK_INVALID_ARGUMENT;
+  if (n % 32 != 0) return QK_DIMENSION_MISMATCH;
+  CK(c, qk_launch_quantize_q8_0(x_dev, n, out_dev, (cudaStream_t)stream));
+  return QK_OK;
+}
+
+extern "C" int qk_check_device_status(qk_ctx *c, void *stream) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  unsigned v = 0;
+  CK(c, cudaMemcpyAsync(&v, c->status_dev, sizeof(v), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  CK(c, cudaStreamSynchronize((cudaStream_t)stream));
+  if (v) {
+    CK(c, cudaMemsetAsync(c->status_dev, 0, sizeof(v), (cudaStream_t)stream));
+    c->err = (v & QK_DEV_TIMEOUT) ? "device-side wait ran out" : "device-side range check tripped";
+    return (v & QK_DEV_TIMEOUT) ? QK_TIMEOUT : QK_KERNEL_ERROR;
+  }
+  return QK_OK;
+}
+
+// ------------------------------------------------------------ host-pointer entry points
+extern "C" int qk_dequant_block(qk_ctx *c, int type, const uint8_t *block, size_t block_len,
+                                float *out, size_t out_len) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) return QK_UNSUPPORTED_TYPE;
+  size_t bs = qk_block_size(type), bb = qk_block_bytes(type);
+  if (block_len < bb) return QK_BUFFER_TOO_SMALL;
+  if (out_len < bs) return QK_BUFFER_TOO_SMALL;
+  if (!block || !out) return QK_INVALID_ARGUMENT;
+  return qk_dequant_matrix(c, type, block, bb, 1, bs, out, bs);
+}
+
+extern "C" int qk_dequant_matrix(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows,
+                                 size_t n_cols, float *out, size_t out_len) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) return QK_UNSUPPORTED_TYPE;
+  if (w_len < need_bytes(type, n_rows, n_cols)) return QK_BUFFER_TOO_SMALL;
+  if (out_len < n_rows * n_cols) return QK_BUFFER_TOO_SMALL;
+  if (n_rows * n_cols == 0) return QK_OK;
+  if (!w || !out) return QK_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(c->mu);
+  CK(c, cudaSetDevice(c->device));
+  qk_weights *h = nullptr;
+  int st = upload_impl(c, type, w, n_cols, 0, n_rows, &h);  // not cached: one-shot
+  if (st) return st;
+  size_t nbytes = n_rows * n_cols * sizeof(float);
+  st = grow(c, &c->sb, &c->sb_cap, nbytes);
+  if (st == QK_OK) {
+    cudaError_t e = qk_launch_dequant(h->L, h->dev, (float *)c->sb, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, c->sb, nbytes, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+      c->err = std::string("dequant: ") + cudaGetErrorString(e);
+      st = QK_CUDA_ERROR;
+    }
+  }
+  free_weights(h);
+  return st;
+}
+
+static int host_gemm(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n, size_t k,
+                     const float *x, float *y, size_t m) {
+  std::lock_guard<std::mutex> g(c->mu);
+  CK(c, cudaSetDevice(c->device));
+  qk_weights *h = nullptr;
+  int st = cached(c, type, w, w_len, n, k, &h);
+  if (st) return st;
+  size_t xb = m * k * sizeof(float), yb = m * n * sizeof(float);
+  if ((st = grow(c, &c->sa, &c->sa_cap, xb ? xb : 4))) return st;
+  if ((st = grow(c, &c->sb, &c->sb_cap, yb ? yb : 4))) return st;
+  if (xb) CK(c, cudaMemcpyAsync(c->sa, x, xb, cudaMemcpyHostToDevice, c->stream));
+  if ((st = gemm_dispatch(c, h, (const float *)c->sa, (float *)c->sb, m, n, c->stream))) return st;
+  if (yb) CK(c, cudaMemcpyAsync(y, c->sb, yb, cudaMemcpyDeviceToHost, c->stream));
+  CK(c, cudaStreamSynchronize(c->stream));
+  return QK_OK;
+}
+
+extern "C" int qk_gemv(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows,
+                       size_t n_cols, const float *x, size_t x_len, float *y, size_t y_len) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) return QK_UNSUPPORTED_TYPE;
+  if (x_len < n_cols) return QK_DIMENSION_MISMATCH;  // order as reference/q4_k.rs:117-128
+  if (y_len < n_rows) return QK_DIMENSION_MISMATCH;
+  if (w_len < need_bytes(type, n_rows, n_cols)) return QK_BUFFER_TOO_SMALL;
+  if (n_rows == 0) return QK_OK;
+  if (!w || !y || (n_cols && !x)) return QK_INVALID_ARGUMENT;
+  return host_gemm(c, type, w, w_len, n_rows, n_cols, x, y, 1);
+}
+
+extern "C" int qk_gemm(qk_ctx *c, int type, const uint8_t *w, size_t w_len, const float *x,
+                       size_t x_len, float *y, size_t y_len, size_t m, size_t n, size_t k) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) return QK_UNSUPPORTED_TYPE;
+  if (x_len < m * k) return QK_DIMENSION_MISMATCH;
+  if (y_len < m * n) return QK_DIMENSION_MISMATCH;
+  if (w_len < need_bytes(type, n, k)) return QK_BUFFER_TOO_SMALL;
+  if (m == 0 || n == 0) return QK_OK;
+  if (!w || !y || (k && !x)) return QK_INVALID_ARGUMENT;
+  return host_gemm(c, type, w, w_len, n, k, x, y, m);
+}
+
+extern "C" int qk_matvec_q8_fused(qk_ctx *c, int type, const uint8_t *w, size_t w_len,
+                                  const uint8_t *acts_q8, size_t acts_len, float *out,
+                                  size_t out_len, size_t n_rows, size_t n_cols) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) return QK_UNSUPPORTED_TYPE;
+  if (out_len < n_rows) return QK_DIMENSION_MISMATCH;  // order as reference/q4_k.rs:226-250
+  size_t bs = qk_block_size(type);
+  size_t acts_needed = ((n_cols + bs - 1) / bs) * (bs / 32) * 34;
+  if (w_len < need_bytes(type, n_rows, n_cols)) return QK_BUFFER_TOO_SMALL;
+  if (acts_len < acts_needed) return QK_BUFFER_TOO_SMALL;
+  if (n_rows == 0 || n_cols == 0) return QK_OK;
+  if (!w || !acts_q8 || !out) return QK_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(c->mu);
+  CK(c, cudaSetDevice(c->device));
+  qk_weights *h = nullptr;
+  int st = cached(c, type, w, w_len, n_rows, n_cols, &h);
+  if (st) return st;
+  if ((st = grow(c, &c->sa, &c->sa_cap, acts_needed))) return st;
+  if ((st = grow(c, &c->sb, &c->sb_cap, n_rows * sizeof(float)))) return st;
+  CK(c, cudaMemcpyAsync(c->sa, acts_q8, acts_needed, cudaMemcpyHostToDevice, c->stream));
+  CK(c, cudaMemcpyAsync(c->sb, out, n_rows * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  CK(c, qk_launch_fused_simple(h->L, h->dev, (const uint8_t *)c->sa, (float *)c->sb, c->stream));
+  CK(c, cudaMemcpyAsync(out, c->sb, n_rows * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+  CK(c, cudaStreamSynchronize(c->stream));
+  return QK_OK;
+}
+
+extern "C" int qk_quantize_q8_0(qk_ctx *c, const float *x, size_t n, uint8_t *out, size_t out_len) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (n % 32 != 0) return QK_DIMENSION_MISMATCH;  // quantize.rs:59-64
+  if (out_len < n / 32 * 34) return QK_BUFFER_TOO_SMALL;
+  if (n == 0) return QK_OK;
+  if (!x || !out) return QK_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(c->mu);
+  CK(c, cudaSetDevice(c->device));
+  int st;
+  if ((st = grow(c, &c->sa, &c->sa_cap, n * sizeof(float)))) return st;
+  if ((st = grow(c, &c->sb, &c->sb_cap, n / 32 * 34))) return st;
+  CK(c, cudaMemcpyAsync(c->sa, x, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  CK(c, qk_launch_quantize_q8_0((const float *)c->sa, n, (uint8_t *)c->sb, c->stream));
+  CK(c, cudaMemcpyAsync(out, c->sb, n / 32 * 34, cudaMemcpyDeviceToHost, c->stream));
+  CK(c, cudaStreamSynchronize(c->stream));
+  return QK_OK;
+}

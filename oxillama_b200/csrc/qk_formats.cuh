@@ -1,0 +1,79 @@
+// Per-format element decode, bit-exact to the scalar reference kernels.
+//
+// Every product and difference is formed with an explicit round-to-nearest
+// intrinsic (__fmul_rn / __fsub_rn) so that the compiler can never contract
+// a*b-c into one FMA: the reference's Rust rounds the product first
+// (e.g. reference/q4_k.rs:79-93: `d1 * q - m1` is two roundings).
+#pragma once
+#include "qk_layout.cuh"
+
+__device__ __forceinline__ float qk_h2f(const uint8_t *p) {
+  return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(p)));
+}
+
+// reference/iq_shared.rs:16-18
+static __device__ __constant__ int8_t QK_KVALUES_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10,
+                                                       1,    13,   25,  38,  53,  69,  89,  113};
+
+// reference/q4_k.rs:27-49: 6-bit scale and min of sub-block j from the 12 packed bytes.
+__device__ __forceinline__ void qk_q4k_scale_min(const uint8_t *s, int j, int &sc, int &mn) {
+  if (j < 4) {
+    sc = s[j] & 0x3F;
+    mn = s[j + 4] & 0x3F;
+  } else {
+    sc = (s[j + 4] & 0x0F) | ((s[j - 4] >> 6) << 4);
+    mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+  }
+}
+
+// Weight (row, col) of a tiled matrix as the reference's dequant_block gives it.
+// `base` is the tiled buffer; col < blocks_per_row * block_size.
+__device__ __forceinline__ float qk_dequant_elem(const QkLayout &L, const uint8_t *base,
+                                                 uint32_t row, uint32_t col) {
+  uint32_t blk = col / L.bs, i = col % L.bs;
+  const uint8_t *p0 = base + qk_field_offset(L, row, blk, 0);
+  switch (L.type) {
+    case QK_T_Q4_0: {  // reference/q4_0.rs:36-46
+      float d = qk_h2f(base + qk_field_offset(L, row, blk, 1));
+      uint8_t byte = p0[i >> 1];
+      int q = (int)((i & 1) ? (byte >> 4) : (byte & 0x0F)) - 8;
+      return __fmul_rn((float)q, d);
+    }
+    case QK_T_Q8_0: {  // reference/q8_0.rs:36-41
+      float d = qk_h2f(base + qk_field_offset(L, row, blk, 1));
+      return __fmul_rn((float)(int8_t)p0[i], d);
+    }
+    case QK_T_Q4_K: {  // reference/q4_k.rs:66-99
+      float d = qk_h2f(p0), dmin = qk_h2f(p0 + 2);
+      int sub = i >> 5, g = i >> 6, l = i & 31;
+      uint8_t byte = p0[16 + 32 * g + l];
+      int q = (sub & 1) ? (byte >> 4) : (byte & 0x0F);
+      int sc, mn;
+      qk_q4k_scale_min(p0 + 4, sub, sc, mn);
+      float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
+      return __fsub_rn(__fmul_rn(d1, (float)q), m1);
+    }
+    case QK_T_Q6_K: {  // reference/q6_k.rs:39-71
+      const uint8_t *sc = base + qk_field_offset(L, row, blk, 1);
+      float d = qk_h2f(base + qk_field_offset(L, row, blk, 2));
+      int g = i >> 7, rem = i & 127, k = rem >> 5, l = rem & 31, is = l >> 4;
+      uint8_t qlb = p0[64 * g + l + ((k & 1) ? 32 : 0)];
+      uint8_t qhb = p0[128 + 32 * g + l];
+      int nib = (k & 2) ? (qlb >> 4) : (qlb & 0x0F);
+      int q = (nib | (((qhb >> (2 * k)) & 3) << 4)) - 32;
+      float s = (float)(int8_t)sc[8 * g + is + 2 * k];
+      return __fmul_rn(__fmul_rn(d, s), (float)q);
+    }
+    default: {  // IQ4_XS, reference/iq4_xs.rs:73-93
+      const uint8_t *h = base + qk_field_offset(L, row, blk, 1);
+      float d = qk_h2f(h);
+      uint32_t sh = h[2] | (h[3] << 8);
+      int sub = i >> 5, j = i & 31;
+      int ls = ((h[4 + (sub >> 1)] >> (4 * (sub & 1))) & 0x0F) | (((sh >> (2 * sub)) & 3) << 4);
+      uint8_t byte = p0[16 * sub + (j >> 1)];
+      int n = (j & 1) ? (byte >> 4) : (byte & 0x0F);
+      float scale = __fmul_rn(d, (float)(ls - 32));
+      return __fmul_rn(scale, (float)QK_KVALUES_IQ4NL[n]);
+    }
+  }
+}

@@ -1,0 +1,604 @@
+// Decode-path dequant-dot (M <= 4 activation rows): HBM-bound, so the kernel is
+// built around keeping many bulk copies in flight and spending few issue slots
+// per weight byte.
+//
+// Shape of the kernel
+//  * Persistent: one CTA per SM slot, CTA i takes row-chunks i, i+grid, ...
+//    (a chunk = 8 weight rows; its k-tiles are contiguous spans of HBM).
+//  * One elected thread streams tiles into a ring of shared-memory stages with
+//    cp.async.bulk (global -> shared, completion on an mbarrier); all waits on
+//    those barriers are bounded and raise QK_DEV_TIMEOUT instead of spinning.
+//  * While the first tiles are in flight every CTA splits the f32 activations
+//    into base-254 signed 8-bit digits per 32-column block:
+//        x ~= sx * (D0 + D1/254 + D2/254^2),  |x - x~| <= amax * 6.1e-8
+//    (two digits: 1.5e-5) and keeps block sums of x for the min / zero-point
+//    terms.  Weights are small integers, so the inner product becomes exact
+//    integer dp4a work; the f32 rounding that remains is one scale multiply and
+//    one add per 32 weights, well inside what f32 summation order costs anyway.
+//  * A thread owns a 64-weight unit of a row for several rows of the chunk, so
+//    the digit registers are reused across rows; partial sums are reduced with
+//    warp shuffles, then across warps through shared memory.
+//
+// Result: y[m][row] = sum_c w(row,c) x[m][c] with w exactly the reference's
+// dequantised weight (reference/q4_k.rs:133-181 and siblings), accumulated in
+// a different order and with x carried to ~24 bits.
+#include "qk_formats.cuh"
+#include "qk_kernels.h"
+
+namespace {
+
+constexpr int NT = 256;          // threads per CTA
+constexpr int NWARP = NT / 32;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the barrier never flipped.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // u8 x s8
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {  // s8 x s8
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float h2f_bits(uint32_t h) {
+  return __half2float(__ushort_as_half((unsigned short)(h & 0xFFFFu)));
+}
+
+// Position of column e's digit byte inside its 256-column span, per format:
+// the order in which the format's packed words meet their activations.
+template <int TYPE>
+__device__ __forceinline__ uint32_t x_pos(uint32_t e) {
+  uint32_t s = e & ~255u, o = e & 255u, p;
+  if (TYPE == QK_T_Q4_0) {
+    // byte i of a block holds elements 2i (low nibble) and 2i+1 (high):
+    // evens first, then odds, inside every 32-block (reference/q4_0.rs:40-46)
+    uint32_t b = o & ~31u, i = o & 31u;
+    p = b + ((i & 1u) << 4) + (i >> 1);
+  } else if (TYPE == QK_T_Q6_K) {
+    // unit (G, is) gathers the four 16-column strips k = 0..3 it decodes
+    // together (reference/q6_k.rs:51-70)
+    uint32_t G = o >> 7, k = (o >> 5) & 3u, is = (o >> 4) & 1u, b = o & 15u;
+    p = ((2u * G + is) << 6) + (k << 4) + b;
+  } else {
+    p = o;  // Q4_K, Q8_0: natural order
+  }
+  // 16-byte slots of a 64-byte unit are XOR-swizzled by the unit index so that
+  // consecutive lanes (consecutive units) hit distinct banks.
+  uint32_t u = (s + p) >> 6, j = (p >> 4) & 3u;
+  return ((s + p) & ~48u) | ((j ^ ((u >> 1) & 3u)) << 4);
+}
+
+struct Smem {
+  uint32_t bars;   // mbarriers, 8 B each
+  uint32_t xd;     // digit planes  [M][D][Kp]
+  uint32_t xs;     // per 32-block float4 (sx, S32, S16a, S16b)  [M][Kp/32]
+  uint32_t dec;    // decoded per-unit scales of the current tile
+  uint32_t red;    // cross-warp reduction  [NWARP][8]
+  uint32_t flag;   // abort flag
+  uint32_t stage;  // ring of tiles
+};
+
+// Fills the CTA's digit planes and block statistics from x (global, f32).
+template <int TYPE, int M, int D>
+__device__ void prep_x(const QkLayout &L, const float *__restrict__ x, unsigned char *smem,
+                       const Smem &S, uint32_t Kp) {
+  const uint32_t quads = Kp / 4;
+  for (uint32_t it = threadIdx.x; it < (uint32_t)M * quads; it += NT) {
+    uint32_t m = it / quads, q = it % quads, e0 = q * 4;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      v[i] = (e0 + i < L.cols) ? x[(uint64_t)m * L.cols + e0 + i] : 0.f;
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float s4 = (v[0] + v[1]) + (v[2] + v[3]);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
+    s4 += __shfl_xor_sync(0xffffffffu, s4, 2);  // sum of this thread's 16-column half
+    float other = __shfl_xor_sync(0xffffffffu, s4, 4);
+    if (!(amax < 3.0e38f)) amax = 3.0e38f;  // inf/nan in x: keep the arithmetic finite
+    float inv = amax > 0.f ? 127.f / amax : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float t0 = v[i] * inv;
+      float d0 = rintf(t0);
+      d0 = fminf(fmaxf(d0, -127.f), 127.f);
+      float t1 = fmaf(v[i], inv, -d0) * 254.f;
+      float d1 = fminf(fmaxf(rintf(t1), -127.f), 127.f);
+      float d2 = fminf(fmaxf(rintf((t1 - d1) * 254.f), -127.f), 127.f);
+      uint32_t pos = x_pos<TYPE>(e0 + i);
+      unsigned char *base = smem + S.xd + (size_t)m * D * Kp + pos;
+      base[0] = (unsigned char)(int)d0;
+      base[Kp] = (unsigned char)(int)d1;
+      if (D == 3) base[2 * Kp] = (unsigned char)(int)d2;
+    }
+    if ((threadIdx.x & 7) == 0) {
+      float4 st = make_float4(amax * (1.f / 127.f), s4 + other, s4, other);
+      *reinterpret_cast<float4 *>(smem + S.xs + ((size_t)m * (Kp / 32) + e0 / 32) * 16) =
+          st;
+    }
+  }
+}
+
+// Combines the integer digit dots into sx * (I0 + I1/254 + I2/254^2).
+template <int D>
+__device__ __forceinline__ float digits_to_f32(const int *I, float sx) {
+  float p = (float)I[D - 1];
+#pragma unroll
+  for (int d = D - 2; d >= 0; d--) p = fmaf(p, 1.f / 254.f, (float)I[d]);
+  return p * sx;
+}
+
+template <int TYPE, int M, int D, int RS>
+__global__ void __launch_bounds__(NT)
+    qk_gemv_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
+                   float *__restrict__ y, uint64_t ldy, unsigned *status, int nstage,
+                   uint32_t stage_bytes, Smem S, uint32_t Kp) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int RPT = 8 / RS;             // rows per thread
+  constexpr int WPS = NWARP / RS;         // warps per row split
+  const uint32_t sbase = smem_u32(smem);  // S.* are offsets from here (S.bars == 0)
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t split = warp % RS, ulane = (warp / RS) * 32 + lane;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + S.flag);
+
+  const uint32_t my_chunks =
+      blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint32_t my_items = my_chunks * L.ktiles;
+
+  auto issue = [&](uint32_t item) {  // thread 0 only
+    uint32_t chunk = blockIdx.x + (item / L.ktiles) * gridDim.x, kt = item % L.ktiles;
+    uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, kt) * L.bb;
+    uint32_t st = item % nstage;
+    uint32_t bar = sbase + S.bars + st * 8;
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s(sbase + S.stage + st * stage_bytes, W + qk_tile_offset(L, chunk, kt), bytes, bar);
+  };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < nstage; s++) mbar_init(sbase + S.bars + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (uint32_t i = 0; i < (uint32_t)nstage && i < my_items; i++) issue(i);
+  }
+  prep_x<TYPE, M, D>(L, x, smem, S, Kp);
+  __syncthreads();
+
+  float acc[M][RPT];
+#pragma unroll
+  for (int m = 0; m < M; m++)
+#pragma unroll
+    for (int r = 0; r < RPT; r++) acc[m][r] = 0.f;
+
+  for (uint32_t item = 0; item < my_items; item++) {
+    const uint32_t chunk = blockIdx.x + (item / L.ktiles) * gridDim.x, kt = item % L.ktiles;
+    const uint32_t st = item % nstage, nbt = qk_tile_nb(L, kt);
+    const uint32_t tile = sbase + S.stage + st * stage_bytes;
+    if (!mbar_wait_bounded(sbase + S.bars + st * 8, (item / nstage) & 1)) {
+      *abort_flag = 1;
+      atomicOr(status, QK_DEV_TIMEOUT);
+    }
+
+    // ---- per-tile scale decode into floats (one thread per block of the tile)
+    if (TYPE == QK_T_Q4_K) {
+      for (uint32_t i = threadIdx.x; i < 8 * nbt; i += NT) {
+        uint4 h = lds128(tile + i * 144);
+        float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
+        // reference/q4_k.rs:27-49, four fields at a time
+        uint32_t sc03 = h.y & 0x3F3F3F3Fu, mn03 = h.z & 0x3F3F3F3Fu;
+        uint32_t sc47 = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+        uint32_t mn47 = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
+          int sh = (g & 1) * 16;
+          float4 o;
+          o.x = d * (float)((scw >> sh) & 0xFF);
+          o.y = d * (float)((scw >> (sh + 8)) & 0xFF) * (1.f / 16.f);  // high nibbles enter x16
+          o.z = dmin * (float)((mnw >> sh) & 0xFF);
+          o.w = dmin * (float)((mnw >> (sh + 8)) & 0xFF);
+          *reinterpret_cast<float4 *>(smem + S.dec + (i * 4 + g) * 16) = o;
+        }
+      }
+      __syncthreads();
+    } else if (TYPE == QK_T_Q6_K) {
+      const uint32_t p1 = tile + 8 * nbt * 192, p2 = p1 + 8 * nbt * 16;
+      for (uint32_t i = threadIdx.x; i < 8 * nbt; i += NT) {
+        uint4 s = lds128(p1 + i * 16);
+        uint32_t dw = lds32((p2 + i * 2) & ~3u);
+        float d = h2f_bits((i & 1) ? (dw >> 16) : dw);
+        uint32_t w[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int u = 0; u < 4; u++) {  // unit u = 2G + is needs scales 8G + is + 2k
+          int G = u >> 1, is = u & 1;
+          float4 o;
+          o.x = d * (float)(int8_t)(w[2 * G] >> (8 * is));
+          o.y = d * (float)(int8_t)(w[2 * G] >> (8 * (is + 2)));
+          o.z = d * (float)(int8_t)(w[2 * G + 1] >> (8 * is));
+          o.w = d * (float)(int8_t)(w[2 * G + 1] >> (8 * (is + 2)));
+          *reinterpret_cast<float4 *>(smem + S.dec + (i * 4 + u) * 16) = o;
+        }
+      }
+      __syncthreads();
+    }
+
+    // ---- main: units of 64 weights, RPT rows each
+    const uint32_t units = nbt * (L.bs == 32 ? 1u : 8u) / 2u;  // 64-weight units per row in this tile
+    const uint32_t kbase = kt * QK_TILE_ELEMS;                 // first column of the tile
+    for (uint32_t u = ulane; u < units; u += WPS * 32) {
+      // digit registers for this unit: 16 words per (m, d)
+      uint32_t xw[M][D][16];
+      const uint32_t xoff = kbase + u * 64, sw = ((xoff >> 6) >> 1) & 3u;
+#pragma unroll
+      for (int m = 0; m < M; m++)
+#pragma unroll
+        for (int d = 0; d < D; d++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint4 t = lds128(sbase + S.xd + (m * D + d) * Kp + xoff + ((j ^ sw) << 4));
+            xw[m][d][4 * j] = t.x, xw[m][d][4 * j + 1] = t.y;
+            xw[m][d][4 * j + 2] = t.z, xw[m][d][4 * j + 3] = t.w;
+          }
+#pragma unroll
+      for (int rr = 0; rr < RPT; rr++) {
+        const uint32_t r = split * RPT + rr;
+        if (TYPE == QK_T_Q4_K) {
+          const uint32_t sb = u >> 2, g = u & 3u;
+          const uint32_t wa = tile + (r * nbt + sb) * 144 + 16 + 32 * g;
+          uint4 a = lds128(wa), b = lds128(wa + 16);
+          float4 sc = lds128f(sbase + S.dec + ((r * nbt + sb) * 4 + g) * 16);
+          uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+          uint32_t lo[8], hi[8];
+#pragma unroll
+          for (int k = 0; k < 8; k++) lo[k] = w[k] & 0x0F0F0F0Fu, hi[k] = w[k] & 0xF0F0F0F0u;
+#pragma unroll
+          for (int m = 0; m < M; m++) {
+            int Il[D], Ih[D];
+#pragma unroll
+            for (int d = 0; d < D; d++) {
+              int il = 0, ih = 0;
+#pragma unroll
+              for (int k = 0; k < 8; k++) {
+                il = dp4a_us(lo[k], xw[m][d][k], il);
+                ih = dp4a_us(hi[k], xw[m][d][8 + k], ih);
+              }
+              Il[d] = il, Ih[d] = ih;
+            }
+            const uint32_t xsa = sbase + S.xs + (m * (Kp / 32) + (xoff >> 5)) * 16;
+            float4 s0 = lds128f(xsa), s1 = lds128f(xsa + 16);
+            float t = acc[m][rr];
+            t = fmaf(sc.x, digits_to_f32<D>(Il, s0.x), t);
+            t = fmaf(-sc.z, s0.y, t);
+            t = fmaf(sc.y, digits_to_f32<D>(Ih, s1.x), t);
+            t = fmaf(-sc.w, s1.y, t);
+            acc[m][rr] = t;
+          }
+        } else if (TYPE == QK_T_Q4_0 || TYPE == QK_T_Q8_0) {
+          const uint32_t qw = TYPE == QK_T_Q4_0 ? 16u : 32u;
+          const uint32_t b0 = 2 * u;  // blocks 2u, 2u+1 of this row in the tile
+          const uint32_t p1 = tile + 8 * nbt * qw;
+          uint32_t dd = lds32(p1 + (r * nbt + b0) * 2);
+#pragma unroll
+          for (int j = 0; j < 2; j++) {
+            if (b0 + j >= nbt) break;
+            float dj = h2f_bits(j ? (dd >> 16) : dd);
+            if (TYPE == QK_T_Q4_0) {
+              uint4 q = lds128(tile + (r * nbt + b0 + j) * 16);
+              uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int m = 0; m < M; m++) {
+                int Ie[D], Io[D];
+#pragma unroll
+                for (int d = 0; d < D; d++) {
+                  int ie = 0, io = 0;
+#pragma unroll
+                  for (int k = 0; k < 4; k++) {
+                    ie = dp4a_us(w[k] & 0x0F0F0F0Fu, xw[m][d][8 * j + k], ie);
+                    io = dp4a_us(w[k] & 0xF0F0F0F0u, xw[m][d][8 * j + 4 + k], io);
+                  }
+                  Ie[d] = ie, Io[d] = io;
+                }
+                float4 s = lds128f(sbase + S.xs + (m * (Kp / 32) + (xoff >> 5) + j) * 16);
+                float p = fmaf(digits_to_f32<D>(Io, s.x), 1.f / 16.f, digits_to_f32<D>(Ie, s.x));
+                acc[m][rr] = fmaf(dj, fmaf(-8.f, s.y, p), acc[m][rr]);  // (q - 8) zero point
+              }
+            } else {
+              uint4 q0 = lds128(tile + (r * nbt + b0 + j) * 32);
+              uint4 q1 = lds128(tile + (r * nbt + b0 + j) * 32 + 16);
+              uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+              for (int m = 0; m < M; m++) {
+                int I[D];
+#pragma unroll
+                for (int d = 0; d < D; d++) {
+                  int i0 = 0;
+#pragma unroll
+                  for (int k = 0; k < 8; k++) i0 = dp4a_ss(w[k], xw[m][d][8 * j + k], i0);
+                  I[d] = i0;
+                }
+                float4 s = lds128f(sbase + S.xs + (m * (Kp / 32) + (xoff >> 5) + j) * 16);
+                acc[m][rr] = fmaf(dj, digits_to_f32<D>(I, s.x), acc[m][rr]);
+              }
+            }
+          }
+        } else {  // Q6_K: unit = (sb, G, is); strips k = 0..3 of 16 columns each
+          const uint32_t sb = u >> 2, G = (u >> 1) & 1u, is = u & 1u;
+          const uint32_t qb = tile + (r * nbt + sb) * 192;
+          uint4 a = lds128(qb + 64 * G + 16 * is), b = lds128(qb + 64 * G + 32 + 16 * is);
+          uint4 h = lds128(qb + 128 + 32 * G + 16 * is);
+          float4 sc = lds128f(sbase + S.dec + ((r * nbt + sb) * 4 + (u & 3u)) * 16);
+          uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+          uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+          uint32_t q[4][4];  // [strip][word], reference/q6_k.rs:55-60
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            q[0][i] = (aw[i] & 0x0F0F0F0Fu) | ((hw[i] << 4) & 0x30303030u);
+            q[1][i] = (bw[i] & 0x0F0F0F0Fu) | ((hw[i] << 2) & 0x30303030u);
+            q[2][i] = ((aw[i] >> 4) & 0x0F0F0F0Fu) | (hw[i] & 0x30303030u);
+            q[3][i] = ((bw[i] >> 4) & 0x0F0F0F0Fu) | ((hw[i] >> 2) & 0x30303030u);
+          }
+          const float scs[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+          for (int m = 0; m < M; m++) {
+            // the unit's four strips sit in x-blocks 4G .. 4G+3 of the super-block
+            const uint32_t xsa =
+                sbase + S.xs + (m * (Kp / 32) + ((kbase + sb * 256) >> 5) + 4 * G) * 16;
+            float t = acc[m][rr];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              int I[D];
+#pragma unroll
+              for (int d = 0; d < D; d++) {
+                int i0 = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) i0 = dp4a_us(q[k][i], xw[m][d][4 * k + i], i0);
+                I[d] = i0;
+              }
+              float4 s = lds128f(xsa + 16 * k);
+              float p = fmaf(-32.f, is ? s.w : s.z, digits_to_f32<D>(I, s.x));  // (q - 32)
+              t = fmaf(scs[k], p, t);
+            }
+            acc[m][rr] = t;
+          }
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with this stage (and with `dec`)
+    if (*abort_flag) break;
+    if (threadIdx.x == 0 && item + nstage < my_items) issue(item + nstage);
+
+    if (kt + 1 == L.ktiles) {  // chunk finished: reduce and write 8 rows x M
+      const uint32_t red_parity = (item / L.ktiles) & 1;  // double-buffered
+      float *red = reinterpret_cast<float *>(smem + S.red) + red_parity * (NWARP * M * RPT);
+#pragma unroll
+      for (int m = 0; m < M; m++)
+#pragma unroll
+        for (int r = 0; r < RPT; r++) {
+          float v = acc[m][r];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == 0) red[warp * (M * RPT) + m * RPT + r] = v;
+          acc[m][r] = 0.f;
+        }
+      __syncthreads();
+      if (threadIdx.x < 8 * M) {
+        uint32_t m = threadIdx.x / 8, r = threadIdx.x % 8;
+        uint32_t sp = r / RPT, rr = r % RPT;
+        float v = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < WPS; wv++) v += red[(wv * RS + sp) * (M * RPT) + m * RPT + rr];
+        uint32_t row = chunk * 8 + r;
+        if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
+      }
+    }
+  }
+
+  if (*abort_flag && threadIdx.x == 0) {
+    // give copies already issued a bounded chance to land before the CTA exits
+    for (int s = 0; s < nstage; s++) {
+      mbar_wait_bounded(sbase + S.bars + s * 8, 0);
+      mbar_wait_bounded(sbase + S.bars + s * 8, 1);
+    }
+  }
+}
+
+struct Plan {
+  Smem S;
+  uint32_t Kp, stage_bytes, total;
+  int nstage, ctas_per_sm, D;
+};
+
+bool make_plan(const QkLayout &L, uint32_t m, int RS, Plan *P) {
+  (void)RS;
+  uint32_t Kp = L.nb * L.bs;
+  Kp = (Kp + 255u) & ~255u;
+  int D = m <= 2 ? 3 : 2;
+  uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
+  uint32_t stage_bytes = QK_TILE_ROWS * nbt_max * L.bb;
+  stage_bytes = (stage_bytes + 127u) & ~127u;
+  uint32_t dec_bytes = (L.type == QK_T_Q4_K || L.type == QK_T_Q6_K) ? 8 * nbt_max * 64 : 0;
+  uint32_t off = 0;
+  Smem S;
+  S.bars = off, off += 64;  // up to 8 stages
+  S.flag = off, off += 16;
+  S.red = off, off += 2 * NWARP * 4 * 8 * 4;
+  off = (off + 127u) & ~127u;
+  S.xd = off, off += m * D * Kp;
+  S.xs = off, off += m * (Kp / 32) * 16;
+  S.dec = off, off += dec_bytes;
+  off = (off + 127u) & ~127u;
+  S.stage = off;
+  const uint32_t budget = 227u * 1024u;
+  if (off + 2 * stage_bytes > budget) return false;
+  // Prefer 2 CTAs per SM (barrier bubbles of one hide behind the other) when
+  // each can still keep >= 3 tiles in flight.
+  int ctas = 1, nstage;
+  uint32_t per2 = (budget / 2) - 1024;
+  if (off + 3 * stage_bytes <= per2) {
+    ctas = 2;
+    nstage = (int)((per2 - off) / stage_bytes);
+  } else {
+    nstage = (int)((budget - 1024 - off) / stage_bytes);
+  }
+  if (nstage > 8) nstage = 8;
+  if (nstage < 2) return false;
+  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage;
+  P->ctas_per_sm = ctas, P->D = D;
+  P->total = off + nstage * stage_bytes;
+  return true;
+}
+
+template <int TYPE, int M, int D, int RS>
+cudaError_t launch_one(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
+                       unsigned *status, int sm_count, const Plan &P, cudaStream_t s) {
+  auto kern = qk_gemv_kernel<TYPE, M, D, RS>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  // A persistent grid must be fully resident: size it from the real occupancy.
+  static int occ_cached[2] = {0, 0};  // [0] smem it was computed for, [1] CTAs per SM
+  if (occ_cached[0] != (int)P.total) {
+    int occ = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, P.total);
+    if (e != cudaSuccess) return e;
+    if (occ < 1) return cudaErrorLaunchOutOfResources;
+    occ_cached[0] = (int)P.total, occ_cached[1] = occ;
+  }
+  int ctas = occ_cached[1] < P.ctas_per_sm ? occ_cached[1] : P.ctas_per_sm;
+  uint32_t grid = (uint32_t)sm_count * ctas;
+  if (grid > L.chunks) grid = L.chunks;
+  kern<<<grid, NT, P.total, s>>>(L, W, x, y, ldy, status, P.nstage, P.stage_bytes, P.S, P.Kp);
+  return cudaGetLastError();
+}
+
+// Row splits: as many rows per thread as still leave every warp a unit to work on.
+int pick_rs(const QkLayout &L) {
+  uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
+  uint32_t units = nbt_max * (L.bs == 32 ? 1u : 8u) / 2u;
+  if (units == 0) units = 1;
+  int rs = 1;
+  while (rs < 8 && units * rs < NT) rs *= 2;
+  return rs;
+}
+
+template <int TYPE, int M, int D>
+cudaError_t launch_rs(int rs, const QkLayout &L, const uint8_t *W, const float *x, float *y,
+                      uint64_t ldy, unsigned *status, int sm_count, const Plan &P, cudaStream_t s) {
+  switch (rs) {
+    case 1:
+      return launch_one<TYPE, M, D, 1>(L, W, x, y, ldy, status, sm_count, P, s);
+    case 2:
+      return launch_one<TYPE, M, D, 2>(L, W, x, y, ldy, status, sm_count, P, s);
+    case 4:
+      return launch_one<TYPE, M, D, 4>(L, W, x, y, ldy, status, sm_count, P, s);
+    default:
+      return launch_one<TYPE, M, D, 8>(L, W, x, y, ldy, status, sm_count, P, s);
+  }
+}
+
+template <int TYPE>
+cudaError_t launch_m(uint32_t m, int rs, const QkLayout &L, const uint8_t *W, const float *x,
+                     float *y, uint64_t ldy, unsigned *status, int sm_count, const Plan &P,
+                     cudaStream_t s) {
+  switch (m) {
+    case 1:
+      return launch_rs<TYPE, 1, 3>(rs, L, W, x, y, ldy, status, sm_count, P, s);
+    case 2:
+      return launch_rs<TYPE, 2, 3>(rs, L, W, x, y, ldy, status, sm_count, P, s);
+    case 3:
+      return launch_rs<TYPE, 3, 2>(rs, L, W, x, y, ldy, status, sm_count, P, s);
+    default:
+      return launch_rs<TYPE, 4, 2>(rs, L, W, x, y, ldy, status, sm_count, P, s);
+  }
+}
+
+}  // namespace
+
+bool qk_gemv_fast_supported(const QkLayout &L, uint32_t m) {
+  if (m < 1 || m > QK_GEMV_MAX_M) return false;
+  if (L.type == QK_T_IQ4_XS) return false;
+  if (L.bs == 32 && (L.nb & 1u)) return false;  // 64-weight units pair two 32-blocks
+  Plan P;
+  return make_plan(L, m, pick_rs(L), &P);
+}
+
+cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
+                                uint32_t m, uint64_t ldy, unsigned *status, int sm_count,
+                                cudaStream_t s) {
+  Plan P;
+  int rs = pick_rs(L);
+  if (!make_plan(L, m, rs, &P)) return cudaErrorInvalidConfiguration;
+  switch (L.type) {
+    case QK_T_Q4_0:
+      return launch_m<QK_T_Q4_0>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
+    case QK_T_Q8_0:
+      return launch_m<QK_T_Q8_0>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
+    case QK_T_Q4_K:
+      return launch_m<QK_T_Q4_K>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
+    case QK_T_Q6_K:
+      return launch_m<QK_T_Q6_K>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}

@@ -1,0 +1,25 @@
+// Internal launch interface between the C-ABI layer and the kernel translation units.
+#pragma once
+#include "qk_layout.cuh"
+
+// Device status word bits (read back by qk_check_device_status).
+#define QK_DEV_TIMEOUT 1u
+#define QK_DEV_BOUNDS 2u
+
+// raw_dev: GGUF-layout bytes of rows [0, L.rows) of the shard; tiled_dev: L.total_bytes, zeroed.
+cudaError_t qk_launch_repack(const QkLayout &L, const uint8_t *raw_dev, uint8_t *tiled_dev,
+                             cudaStream_t s);
+cudaError_t qk_launch_dequant(const QkLayout &L, const uint8_t *tiled, float *out, cudaStream_t s);
+// Generic any-shape path: f32 dequant in registers, f32 FMA, one warp per weight row.
+cudaError_t qk_launch_gemm_simple(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
+                                  uint32_t m, uint64_t ldy, cudaStream_t s);
+cudaError_t qk_launch_fused_simple(const QkLayout &L, const uint8_t *tiled, const uint8_t *acts,
+                                   float *out, cudaStream_t s);
+cudaError_t qk_launch_quantize_q8_0(const float *x, uint64_t n, uint8_t *out, cudaStream_t s);
+
+// Bandwidth-bound decode path (m <= QK_GEMV_MAX_M): bulk-copied tiles, integer dot.
+#define QK_GEMV_MAX_M 4
+bool qk_gemv_fast_supported(const QkLayout &L, uint32_t m);
+cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
+                                uint32_t m, uint64_t ldy, unsigned *status, int sm_count,
+                                cudaStream_t s);

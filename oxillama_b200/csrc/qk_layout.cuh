@@ -1,0 +1,123 @@
+// Device-side weight layout ("row-chunk tiles") and the accessors every kernel uses.
+//
+// Host callers hand over GGUF bytes: rows of ceil(K/bs) blocks, each block a
+// small struct whose size (18, 34, 144, 210, 136 bytes) is not a multiple of
+// 16.  HBM -> shared-memory bulk copies and 128-bit shared loads both want
+// 16-byte alignment, so at upload the same bytes are re-ordered (no byte is
+// added, dropped or changed) into tiles:
+//
+//   tile  = 8 consecutive rows x up to QK_TILE_ELEMS consecutive columns
+//   chunk = the tiles of one 8-row group, k-tile after k-tile
+//   inside a tile the fields of its blocks are split into planes, each plane
+//   an array [8 rows][nbt blocks] of one fixed-width field:
+//
+//     Q4_0   plane0 nibbles 16 B | plane1 d 2 B
+//     Q8_0   plane0 int8s   32 B | plane1 d 2 B
+//     Q4_K   plane0 whole block 144 B (already 16-byte granular)
+//     Q6_K   plane0 ql+qh  192 B | plane1 scales 16 B | plane2 d 2 B
+//     IQ4_XS plane0 nibbles 128 B | plane1 d,scales_h,scales_l 8 B
+//
+// Every plane of every tile then starts on a 16-byte boundary for any K and
+// any row count (8 * nbt * width is a multiple of 16 for all widths above),
+// and one tile is one contiguous span of HBM, so a single bulk copy stages it.
+// Rows are padded up to a multiple of 8 with all-zero blocks (scale 0: they
+// contribute exactly 0 and are never written out).
+#pragma once
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#define QK_TILE_ROWS 8u
+#define QK_TILE_ELEMS 4096u
+
+#define QK_T_Q4_0 2
+#define QK_T_Q8_0 8
+#define QK_T_Q4_K 12
+#define QK_T_Q6_K 14
+#define QK_T_IQ4_XS 23
+
+struct QkLayout {
+  int type;
+  uint32_t bs, bb;       // block size (weights) and bytes
+  uint32_t nb;           // blocks per row = ceil(cols / bs)
+  uint32_t nbt;          // blocks per full k-tile
+  uint32_t ktiles;       // k-tiles per chunk
+  uint32_t nplanes;
+  uint32_t pw[3];        // plane widths, bytes per block
+  uint32_t po[3];        // offset of the plane's field inside the GGUF block
+  uint32_t rows, cols;   // logical shape of this shard
+  uint32_t chunks;       // ceil(rows / 8)
+  uint64_t chunk_bytes;  // 8 * nb * bb
+  uint64_t tile_bytes;   // 8 * nbt * bb (a full tile)
+  uint64_t total_bytes;  // chunks * chunk_bytes
+};
+
+static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayout *L) {
+  QkLayout l = {};
+  l.type = type;
+  switch (type) {
+    case QK_T_Q4_0:
+      l.bs = 32; l.bb = 18; l.nplanes = 2;
+      l.pw[0] = 16; l.po[0] = 2; l.pw[1] = 2; l.po[1] = 0;
+      break;
+    case QK_T_Q8_0:
+      l.bs = 32; l.bb = 34; l.nplanes = 2;
+      l.pw[0] = 32; l.po[0] = 2; l.pw[1] = 2; l.po[1] = 0;
+      break;
+    case QK_T_Q4_K:
+      l.bs = 256; l.bb = 144; l.nplanes = 1;
+      l.pw[0] = 144; l.po[0] = 0;
+      break;
+    case QK_T_Q6_K:
+      l.bs = 256; l.bb = 210; l.nplanes = 3;
+      l.pw[0] = 192; l.po[0] = 0; l.pw[1] = 16; l.po[1] = 192; l.pw[2] = 2; l.po[2] = 208;
+      break;
+    case QK_T_IQ4_XS:
+      l.bs = 256; l.bb = 136; l.nplanes = 2;
+      l.pw[0] = 128; l.po[0] = 8; l.pw[1] = 8; l.po[1] = 0;
+      break;
+    default:
+      return false;
+  }
+  l.rows = (uint32_t)rows;
+  l.cols = (uint32_t)cols;
+  l.nb = (uint32_t)((cols + l.bs - 1) / l.bs);
+  l.nbt = QK_TILE_ELEMS / l.bs;
+  l.ktiles = (l.nb + l.nbt - 1) / l.nbt;
+  l.chunks = (uint32_t)((rows + QK_TILE_ROWS - 1) / QK_TILE_ROWS);
+  l.chunk_bytes = (uint64_t)QK_TILE_ROWS * l.nb * l.bb;
+  l.tile_bytes = (uint64_t)QK_TILE_ROWS * l.nbt * l.bb;
+  l.total_bytes = l.chunk_bytes * l.chunks;
+  *L = l;
+  return true;
+}
+
+// Blocks held by k-tile `kt` (the last one of a chunk may be short).
+__host__ __device__ static inline uint32_t qk_tile_nb(const QkLayout &L, uint32_t kt) {
+  uint32_t left = L.nb - kt * L.nbt;
+  return left < L.nbt ? left : L.nbt;
+}
+
+// Byte offset of tile (chunk, kt) from the start of the buffer.
+__host__ __device__ static inline uint64_t qk_tile_offset(const QkLayout &L, uint32_t chunk,
+                                                          uint32_t kt) {
+  return (uint64_t)chunk * L.chunk_bytes + (uint64_t)kt * L.tile_bytes;
+}
+
+// Byte offset of plane p inside a tile holding nbt_this blocks per row.
+__host__ __device__ static inline uint32_t qk_plane_offset(const QkLayout &L, uint32_t nbt_this,
+                                                           int p) {
+  uint32_t w = 0;
+  for (int i = 0; i < p; i++) w += L.pw[i];
+  return QK_TILE_ROWS * nbt_this * w;
+}
+
+// Address of field-plane p of block (row, blk).
+__host__ __device__ static inline uint64_t qk_field_offset(const QkLayout &L, uint32_t row,
+                                                           uint32_t blk, int p) {
+  uint32_t chunk = row / QK_TILE_ROWS, r = row % QK_TILE_ROWS;
+  uint32_t kt = blk / L.nbt, b = blk % L.nbt;
+  uint32_t nbt_this = qk_tile_nb(L, kt);
+  return qk_tile_offset(L, chunk, kt) + qk_plane_offset(L, nbt_this, p) +
+         (uint64_t)(r * nbt_this + b) * L.pw[p];
+}

@@ -1,0 +1,343 @@
+"""GPU parity: every call goes through the C ABI (ctypes) and is compared with the CPU oracle.
+
+Bars: dequantised values and Q8_0 encodings bit-exact; dot / matmul outputs
+within max_i|y_i - ref_i| / max_j|ref_j| <= 1e-3 of the oracle's f32 result
+(the paths that stay in f32-grade arithmetic are additionally held to 2e-5).
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from oxillama_b200 import synth as S
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3        # stated tolerance of the path
+TOL_F32 = 2e-5    # what the integer-digit / f32 kernels are expected to hold
+
+
+def rel_inf(y, ref):
+    den = float(np.abs(ref).max())
+    return float(np.abs(y.astype(np.float64) - ref.astype(np.float64)).max()) / (den if den > 0 else 1.0)
+
+
+@pytest.fixture(scope="module")
+def K():
+    from oxillama_b200 import kernels
+    return kernels
+
+
+@pytest.fixture(scope="module")
+def disp(K):
+    return K.KernelDispatcher()
+
+
+# ---------------------------------------------------------------- dequant: bit-exact
+@pytest.mark.parametrize("t", S.ALL_TYPES)
+def test_dequant_block_bit_exact(K, disp, t):
+    k = disp.get_kernel(t)
+    bb, bs = S.BLOCK_BYTES[t], S.BLOCK_SIZE[t]
+    assert (k.block_size(), k.block_bytes(), k.name()) == (bs, bb, S.NAMES[t])
+    blocks = S.gen_blocks(t, 24, seed=21).reshape(24, bb).copy()
+    off = 208 if t == S.Q6_K else 0
+    blocks[0, off:off + 2] = [0x01, 0x00]   # smallest f16 subnormal
+    blocks[1, off:off + 2] = [0xFF, 0x03]   # largest subnormal
+    blocks[2, off:off + 2] = [0x00, 0x80]   # -0.0
+    blocks[3, off:off + 2] = [0x00, 0xBC]   # -1.0
+    for b in blocks:
+        out = np.empty(bs, np.float32)
+        k.dequant_block(b, out)
+        st, ref = O.dequant_block(t, b)
+        assert st == 0 and np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("t", S.ALL_TYPES)
+@pytest.mark.parametrize("rows,cols", [(19, 768), (5, None), (64, 4096), (9, 8192 + 512)])
+def test_dequant_matrix_bit_exact(K, disp, t, rows, cols):
+    bs = S.BLOCK_SIZE[t]
+    cols = cols or (bs + bs // 2 + 3)
+    w = S.gen_weight(t, rows, cols, seed=22)
+    out = np.empty((rows, cols), np.float32)
+    disp.get_kernel(t).dequant_matrix(K.QuantTensor(w, (rows, cols), t), out)
+    assert np.array_equal(out.view(np.uint32), O.dequant_matrix(t, w, rows, cols).view(np.uint32))
+
+
+# ---------------------------------------------------------------- gemv / gemm vs oracle
+SHAPES = [(8, 256), (19, 768), (5, None), (33, 4096), (130, 4096 + 256), (16, 14336), (3, 64)]
+
+
+@pytest.mark.parametrize("t", S.ALL_TYPES)
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_gemv_matches_oracle(K, disp, t, rows, cols):
+    bs = S.BLOCK_SIZE[t]
+    cols = cols or (bs + bs // 2 + 3)
+    w = S.gen_weight(t, rows, cols, seed=23)
+    x = S.gen_acts(1, cols, seed=23)[0]
+    y = np.full(rows, np.nan, np.float32)
+    disp.get_kernel(t).gemv(K.QuantTensor(w, (rows, cols), t), x, y)
+    st, ref = O.gemv(t, w, rows, cols, x)
+    assert st == 0
+    assert rel_inf(y, ref) <= TOL_F32, rel_inf(y, ref)
+
+
+@pytest.mark.parametrize("t", S.ALL_TYPES)
+@pytest.mark.parametrize("m", [2, 3, 4, 8, 13])
+def test_gemm_matches_oracle(K, disp, t, m):
+    rows, cols = 40, 1024 + S.BLOCK_SIZE[t]
+    w = S.gen_weight(t, rows, cols, seed=24)
+    x = S.gen_acts(m, cols, seed=24)
+    y = np.full((m, rows), np.nan, np.float32)
+    disp.get_kernel(t).gemm(K.QuantTensor(w, (rows, cols), t), x, y, m, rows, cols)
+    st, ref = O.gemm(t, w, x, m, rows, cols)
+    assert st == 0
+    tol = TOL_F32 if m <= 2 else 1e-4  # two-digit activations for m = 3, 4
+    assert rel_inf(y, ref) <= tol, rel_inf(y, ref)
+
+
+def test_gemv_one_dimensional_shape(K, disp):
+    # shape of rank 1: n_cols = n_elements / n_rows (reference/q4_k.rs:110-115)
+    w = S.gen_weight(S.Q4_K, 1, 512, seed=25)
+    x = S.gen_acts(1, 512, seed=25)[0]
+    qt = K.QuantTensor(w, (1,), S.Q4_K)
+    assert qt.rows_cols() == (1, 1)
+    qt = K.QuantTensor(w, (1, 512), S.Q4_K)
+    y = np.zeros(1, np.float32)
+    disp.get_kernel(S.Q4_K).gemv(qt, x, y)
+    assert rel_inf(y, O.gemv(S.Q4_K, w, 1, 512, x)[1]) <= TOL_F32
+
+
+# ---------------------------------------------------------------- golden fixtures
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "qk_golden.npz"))
+GKEYS = sorted({k.rsplit("_", 1)[0] for k in G.files if k.endswith("_w")})
+TYPE_OF = {v: k for k, v in S.NAMES.items()}
+
+
+@pytest.mark.parametrize("key", GKEYS)
+def test_against_golden(K, disp, key):
+    name, shape = key.rsplit("_", 1)
+    rows, cols = (int(v) for v in shape.split("x"))
+    t = TYPE_OF[name]
+    k = disp.get_kernel(t)
+    w, x = G[key + "_w"], G[key + "_x"]
+    qt = K.QuantTensor(w, (rows, cols), t)
+    dq = np.empty((rows, cols), np.float32)
+    k.dequant_matrix(qt, dq)
+    assert np.array_equal(dq.view(np.uint32), G[key + "_dequant"].view(np.uint32))
+    y = np.empty((3, rows), np.float32)
+    k.gemm(qt, x, y, 3, rows, cols)
+    assert rel_inf(y, G[key + "_gemm"]) <= 1e-4
+    kp = -(-cols // S.BLOCK_SIZE[t]) * S.BLOCK_SIZE[t]
+    xp = np.zeros(kp, np.float32)
+    xp[:cols] = x[0]
+    assert np.array_equal(K.quantize_f32_to_q8_0(xp), G[key + "_q8"])
+    out = G[key + "_fused_init"].copy()
+    k.matvec_q8_fused(w, G[key + "_q8"], out, rows, cols)
+    assert rel_inf(out, G[key + "_fused"]) <= TOL_F32
+
+
+# ---------------------------------------------------------------- fused matvec + encoder
+@pytest.mark.parametrize("t", S.ALL_TYPES)
+def test_fused_accumulates_and_matches_oracle(K, disp, t):
+    rows, cols = 37, 2048
+    w = S.gen_weight(t, rows, cols, seed=26)
+    x = S.gen_acts(1, cols, seed=26)[0]
+    a = K.quantize_f32_to_q8_0(x)
+    st, a_ref = O.quantize_q8_0(x)
+    assert st == 0 and np.array_equal(a, a_ref)  # same integer activations as the reference
+    init = np.linspace(-3, 3, rows, dtype=np.float32)
+    out = init.copy()
+    disp.get_kernel(t).matvec_q8_fused(w, a, out, rows, cols)
+    st, ref = O.matvec_q8_fused(t, w, a, init, rows, cols)
+    assert st == 0 and rel_inf(out, ref) <= TOL_F32
+    # accumulate, not overwrite (reference/q4_k.rs:474-493)
+    out2 = init.copy() + 100.0
+    disp.get_kernel(t).matvec_q8_fused(w, a, out2, rows, cols)
+    assert np.allclose(out2 - out, 100.0, atol=1e-3)
+
+
+def test_quantize_q8_0_bit_exact_edge_cases(K):
+    x = S.gen_acts(1, 32 * 64, seed=27)[0]
+    x[:32] = 0.0
+    x[32:64] = np.arange(32, dtype=np.float32) - 15.5       # .5 ties after scaling
+    x[64:96] = 1e-30                                          # tiny scale
+    x[96:128] = np.float32(65504.0) * 200                     # scale overflows f16 -> inf
+    got = K.quantize_f32_to_q8_0(x)
+    st, ref = O.quantize_q8_0(x)
+    assert st == 0 and np.array_equal(got, ref)
+    with pytest.raises(K.QuantError) as e:
+        K.quantize_f32_to_q8_0(np.zeros(33, np.float32))
+    assert e.value.kind == "DimensionMismatch"
+
+
+# ---------------------------------------------------------------- the reference's known-answer tests, through the GPU
+def f16b(v):
+    return np.array([v], np.float32).astype(np.float16).view(np.uint8)
+
+
+def test_kat_q4_0_interleave(K, disp):  # reference/q4_0.rs:258-270
+    nib = np.full(16, 0x88, np.uint8)
+    nib[0] = 0xF0
+    out = np.empty(32, np.float32)
+    disp.get_kernel(S.Q4_0).dequant_block(np.concatenate([f16b(0.5), nib]), out)
+    assert out[0] == -4.0 and out[1] == 3.5 and np.all(out[2:] == 0)
+
+
+def test_kat_q8_0(K, disp):  # reference/q8_0.rs:158-190
+    v = np.zeros(32, np.int8)
+    v[0], v[1], v[31] = 10, -5, 127
+    out = np.empty(32, np.float32)
+    k = disp.get_kernel(S.Q8_0)
+    k.dequant_block(np.concatenate([f16b(0.5), v.view(np.uint8)]), out)
+    assert out[0] == 5.0 and out[1] == -2.5 and out[31] == 63.5
+    v[:] = 0
+    v[0] = 1
+    x = np.zeros(32, np.float32)
+    x[0] = 3.0
+    y = np.zeros(1, np.float32)
+    k.gemv(K.QuantTensor(np.concatenate([f16b(2.0), v.view(np.uint8)]), (1, 32), S.Q8_0), x, y)
+    assert y[0] == 6.0
+
+
+def test_kat_q4_k(K, disp):  # reference/q4_k.rs:380-436
+    sc = np.array([1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1], np.uint8)
+    k = disp.get_kernel(S.Q4_K)
+    out = np.empty(256, np.float32)
+    k.dequant_block(np.concatenate([f16b(1.0), f16b(0.0), sc, np.full(128, 0x88, np.uint8)]), out)
+    assert np.all(out == 8.0)
+    blk = np.concatenate([f16b(1.0), f16b(0.0), sc, np.full(128, 0x11, np.uint8)])
+    y = np.zeros(1, np.float32)
+    k.gemv(K.QuantTensor(blk, (1, 256), S.Q4_K), np.ones(256, np.float32), y)
+    assert y[0] == 256.0
+
+
+def test_kat_q6_k(K, disp):  # reference/q6_k.rs:381-414
+    b = np.zeros(210, np.uint8)
+    b[128:192] = 0xAA
+    b[192:208] = 1
+    b[208:210] = f16b(1.0)
+    out = np.full(256, 7, np.float32)
+    disp.get_kernel(S.Q6_K).dequant_block(b, out)
+    assert np.all(out == 0.0)
+
+
+def test_kat_iq4_xs(K, disp):  # reference/iq4_xs.rs:265-285,334-354
+    def block(ss, nib):
+        sh, sl = 0, np.zeros(4, np.uint8)
+        for i, v in enumerate(ss):
+            sl[i // 2] |= (v & 0xF) << (4 * (i & 1))
+            sh |= ((v >> 4) & 3) << (2 * i)
+        return np.concatenate([f16b(1.0), np.array([sh & 0xFF, sh >> 8], np.uint8), sl, np.full(128, nib, np.uint8)])
+    k = disp.get_kernel(S.IQ4_XS)
+    out = np.empty(256, np.float32)
+    k.dequant_block(block([33] + [32] * 7, 0x88), out)
+    assert np.all(out[:32] == 1.0) and np.all(out[32:] == 0.0)
+    y = np.zeros(2, np.float32)
+    w = np.concatenate([block([32] * 8, 0x88), block([33] * 8, 0x88)])
+    k.gemv(K.QuantTensor(w, (2, 256), S.IQ4_XS), np.ones(256, np.float32), y)
+    assert y[0] == 0.0 and y[1] == 256.0
+
+
+# ---------------------------------------------------------------- error behaviour (errors are values)
+def test_error_codes(K, disp):
+    k = disp.get_kernel(S.Q4_0)
+    blk = np.concatenate([f16b(1.0), np.full(16, 0x88, np.uint8)])
+    qt1 = K.QuantTensor(blk, (1, 32), S.Q4_0)
+    with pytest.raises(K.QuantError) as e:  # reference/q4_0.rs:310-321
+        k.gemv(qt1, np.zeros(4, np.float32), np.zeros(1, np.float32))
+    assert e.value.kind == "DimensionMismatch"
+    qt2 = K.QuantTensor(np.concatenate([blk, blk]), (2, 32), S.Q4_0)
+    with pytest.raises(K.QuantError) as e:  # reference/q4_0.rs:323-337
+        k.gemv(qt2, np.zeros(32, np.float32), np.zeros(1, np.float32))
+    assert e.value.kind == "DimensionMismatch"
+    with pytest.raises(K.QuantError) as e:  # reference/q4_0.rs:347-355
+        k.dequant_block(np.zeros(4, np.uint8), np.zeros(32, np.float32))
+    assert e.value.kind == "BufferTooSmall"
+    with pytest.raises(K.QuantError) as e:  # reference/q4_0.rs:357-366
+        k.dequant_block(blk, np.zeros(1, np.float32))
+    assert e.value.kind == "BufferTooSmall"
+    with pytest.raises(K.QuantError) as e:  # truncated weight buffer
+        k.gemv(K.QuantTensor(blk[:10], (1, 32), S.Q4_0), np.zeros(32, np.float32), np.zeros(1, np.float32))
+    assert e.value.kind == "BufferTooSmall"
+    with pytest.raises(K.QuantError) as e:
+        disp.get_kernel(13)  # Q5_K: not part of this backend
+    assert e.value.kind == "UnsupportedType"
+    k4 = disp.get_kernel(S.Q4_K)
+    w = S.gen_weight(S.Q4_K, 2, 256, seed=1)
+    with pytest.raises(K.QuantError) as e:  # activations too short (reference/q4_k.rs:245-250)
+        k4.matvec_q8_fused(w, np.zeros(34 * 7, np.uint8), np.zeros(2, np.float32), 2, 256)
+    assert e.value.kind == "BufferTooSmall"
+    with pytest.raises(K.QuantError) as e:
+        k4.matvec_q8_fused(w, np.zeros(34 * 8, np.uint8), np.zeros(1, np.float32), 2, 256)
+    assert e.value.kind == "DimensionMismatch"
+    # empty inputs are fine
+    k.gemv(K.QuantTensor(np.zeros(0, np.uint8), (0, 32), S.Q4_0), np.zeros(32, np.float32), np.zeros(0, np.float32))
+    y = np.full(2, 5.0, np.float32)
+    k.gemv(K.QuantTensor(np.zeros(0, np.uint8), (2, 0), S.Q4_0), np.zeros(0, np.float32), y)
+    assert np.all(y == 0.0)
+
+
+# ---------------------------------------------------------------- benchmark configurations
+def _check_config(K, disp, t, rows, cols, m, seed, tol, row_cap=None):
+    import torch
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    w = S.gen_weight(t, rows, cols, seed=seed)
+    x = S.gen_acts(m, cols, seed=seed)
+    dw = DeviceWeights(t, w, rows, cols)
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.full((m, rows), float("nan"), device="cuda")
+    dw.gemm(xd, yd, m)
+    check_device_status()
+    y = yd.cpu().numpy()
+    rc = rows if row_cap is None else min(rows, row_cap)
+    bpr = S.blocks_per_row(t, cols) * S.BLOCK_BYTES[t]
+    st, ref = O.gemm(t, w[: rc * bpr], x, m, rc, cols)
+    assert st == 0
+    err = rel_inf(y[:, :rc], ref)
+    assert err <= tol, err
+    assert np.all(np.isfinite(y))
+    # linearity, at full size: W(2x) == 2 W(x) exactly (scaling by 2 is exact in every step)
+    dw.gemm(xd * 2, yd, m)
+    assert np.array_equal(yd.cpu().numpy(), 2 * y)
+    dw.free()
+
+
+def test_config1_q4_0_4096(K, disp):
+    _check_config(K, disp, S.Q4_0, 4096, 4096, 1, 0, TOL_F32)
+
+
+@pytest.mark.parametrize("m", [1, 8, 64])
+def test_config2_q4_k_ffn_up(K, disp, m):
+    _check_config(K, disp, S.Q4_K, 14336, 4096, m, 0, TOL_F32 if m == 1 else TOL, row_cap=None if m == 1 else 1024)
+
+
+def test_config3_q6_k_lm_head(K, disp):
+    _check_config(K, disp, S.Q6_K, 128256, 4096, 1, 0, TOL_F32)
+
+
+def test_config3_q8_0_prefill(K, disp):
+    _check_config(K, disp, S.Q8_0, 4096, 4096, 512, 0, TOL, row_cap=64)
+
+
+@pytest.mark.parametrize("name,t,rows,cols", [
+    ("q", S.Q4_K, 4096, 4096), ("k", S.Q4_K, 1024, 4096), ("down", S.Q6_K, 4096, 14336)])
+@pytest.mark.parametrize("m", [1, 8, 32])
+def test_config4_layer_linears(K, disp, name, t, rows, cols, m):
+    _check_config(K, disp, t, rows, cols, m, 4, TOL_F32 if m == 1 else TOL, row_cap=256)
+
+
+def test_row_shard_writes_its_column_block(K, disp):
+    import torch
+    from oxillama_b200.device import DeviceWeights
+    t, rows, cols, m = S.Q4_K, 64, 1024, 3
+    w = S.gen_weight(t, rows, cols, seed=31)
+    x = S.gen_acts(m, cols, seed=31)
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.zeros((m, rows), device="cuda")
+    for g in range(4):  # four row shards fill one [m x rows] output in place
+        dw = DeviceWeights(t, w, rows, cols, row_begin=16 * g, row_end=16 * (g + 1))
+        dw.gemm(xd, yd, m, ldy=rows, col_offset=16 * g)
+        dw.free()
+    st, ref = O.gemm(t, w, x, m, rows, cols)
+    assert rel_inf(yd.cpu().numpy(), ref) <= 1e-4
