@@ -25,13 +25,17 @@ struct qk_ctx {
   int sm_count;
   cudaStream_t stream;
   unsigned *status_dev;
+  // device scratch of the *_dev entry points (split activations); grown on demand,
+  // which synchronises: size it once before capturing into a CUDA graph
+  unsigned char *scratch = nullptr;
+  size_t scratch_cap = 0;
   std::string err;
   std::mutex mu;
   // scratch for the host-pointer entry points
   void *sa = nullptr, *sb = nullptr;
   size_t sa_cap = 0, sb_cap = 0;
   // weight cache for the host-pointer entry points
-  typedef std::tuple<const void *, size_t, int, size_t, size_t> Key;
+  typedef std::tuple<const void *, size_t, int, size_t, size_t, uint64_t> Key;
   std::map<Key, qk_weights *> cache;
   size_t cache_bytes = 0, cache_cap = (size_t)64 << 30;
   bool force_simple = false;
@@ -115,10 +119,12 @@ extern "C" int qk_init(int device, qk_ctx **out) {
   c->sm_count = prop.multiProcessorCount;
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&c->status_dev, sizeof(unsigned)) != cudaSuccess ||
-      cudaMemset(c->status_dev, 0, sizeof(unsigned)) != cudaSuccess) {
+      cudaMemset(c->status_dev, 0, sizeof(unsigned)) != cudaSuccess ||
+      cudaMalloc(&c->scratch, (size_t)1 << 20) != cudaSuccess) {
     delete c;
     return QK_CUDA_ERROR;
   }
+  c->scratch_cap = (size_t)1 << 20;
   const char *fs = getenv("QK_FORCE_SIMPLE");
   c->force_simple = fs && fs[0] == '1';
   *out = c;
@@ -139,6 +145,7 @@ extern "C" int qk_shutdown(qk_ctx *c) {
   if (c->sa) cudaFree(c->sa);
   if (c->sb) cudaFree(c->sb);
   cudaFree(c->status_dev);
+  if (c->scratch) cudaFree(c->scratch);
   cudaStreamDestroy(c->stream);
   delete c;
   return QK_OK;
@@ -245,10 +252,31 @@ extern "C" int qk_weights_info(const qk_weights *h, int *type, size_t *rows, siz
   return QK_OK;
 }
 
+// Cheap content fingerprint of a host weight buffer: every byte when it is small,
+// else head, tail and 2048 evenly spread 8-byte samples.  It guards the
+// pointer-keyed cache against a freed buffer's address being reused for other
+// weights; it does not detect a few bytes edited in place (qk_weights_cache_evict).
+static uint64_t fingerprint(const uint8_t *w, size_t n) {
+  uint64_t h = 1469598103934665603ull ^ n;
+  auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; h ^= h >> 29; };
+  if (n <= 65536) {
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
+    for (; i < n; i++) mix(w[i]);
+    return h;
+  }
+  for (size_t i = 0; i < 4096; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
+  for (size_t i = n - 4096; i + 8 <= n; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
+  size_t step = (n - 8) / 2048;
+  for (size_t k = 0; k < 2048; k++) { uint64_t v; memcpy(&v, w + k * step, 8); mix(v); }
+  return h;
+}
+
 // Cached device copy for the host-pointer entry points.
 static int cached(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows, size_t n_cols,
                   qk_weights **out) {
-  qk_ctx::Key k(w, w_len, type, n_rows, n_cols);
+  size_t need0 = need_bytes(type, n_rows, n_cols);
+  qk_ctx::Key k(w, w_len, type, n_rows, n_cols, fingerprint(w, need0));
   auto it = c->cache.find(k);
   if (it != c->cache.end()) {
     *out = it->second;
@@ -294,7 +322,16 @@ static int gemm_dispatch(qk_ctx *c, const qk_weights *h, const float *x, float *
     return QK_OK;
   }
   if (!c->force_simple && m <= QK_GEMV_MAX_M && qk_gemv_fast_supported(h->L, (uint32_t)m)) {
-    CK(c, qk_launch_gemv_fast(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->sm_count, s));
+    size_t need = qk_gemv_fast_scratch_bytes(h->L, (uint32_t)m);
+    if (need > c->scratch_cap) {
+      CK(c, cudaDeviceSynchronize());
+      cudaFree(c->scratch);
+      c->scratch = nullptr, c->scratch_cap = 0;
+      CK(c, cudaMalloc(&c->scratch, need * 2));
+      c->scratch_cap = need * 2;
+    }
+    CK(c, qk_launch_gemv_fast(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->scratch,
+                              c->sm_count, s));
     return QK_OK;
   }
   CK(c, qk_launch_gemm_simple(h->L, h->dev, x, y, (uint32_t)m, ldy, s));

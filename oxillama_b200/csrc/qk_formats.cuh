@@ -31,31 +31,32 @@ __device__ __forceinline__ void qk_q4k_scale_min(const uint8_t *s, int j, int &s
 __device__ __forceinline__ float qk_dequant_elem(const QkLayout &L, const uint8_t *base,
                                                  uint32_t row, uint32_t col) {
   uint32_t blk = col / L.bs, i = col % L.bs;
-  const uint8_t *p0 = base + qk_field_offset(L, row, blk, 0);
+  auto at = [&](int p, uint32_t o) { return base + qk_byte_offset(L, row, blk, p, o); };
   switch (L.type) {
     case QK_T_Q4_0: {  // reference/q4_0.rs:36-46
-      float d = qk_h2f(base + qk_field_offset(L, row, blk, 1));
-      uint8_t byte = p0[i >> 1];
+      float d = qk_h2f(at(1, 0));
+      uint8_t byte = *at(0, i >> 1);
       int q = (int)((i & 1) ? (byte >> 4) : (byte & 0x0F)) - 8;
       return __fmul_rn((float)q, d);
     }
     case QK_T_Q8_0: {  // reference/q8_0.rs:36-41
-      float d = qk_h2f(base + qk_field_offset(L, row, blk, 1));
-      return __fmul_rn((float)(int8_t)p0[i], d);
+      float d = qk_h2f(at(1, 0));
+      return __fmul_rn((float)(int8_t)*at(0, i), d);
     }
     case QK_T_Q4_K: {  // reference/q4_k.rs:66-99
-      float d = qk_h2f(p0), dmin = qk_h2f(p0 + 2);
+      const uint8_t *h = at(0, 0);
+      float d = qk_h2f(h), dmin = qk_h2f(h + 2);
       int sub = i >> 5, g = i >> 6, l = i & 31;
-      uint8_t byte = p0[16 + 32 * g + l];
+      uint8_t byte = *at(1, 32 * g + l);
       int q = (sub & 1) ? (byte >> 4) : (byte & 0x0F);
       int sc, mn;
-      qk_q4k_scale_min(p0 + 4, sub, sc, mn);
+      qk_q4k_scale_min(h + 4, sub, sc, mn);
       float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
       return __fsub_rn(__fmul_rn(d1, (float)q), m1);
     }
     case QK_T_Q6_K: {  // reference/q6_k.rs:39-71
-      const uint8_t *sc = base + qk_field_offset(L, row, blk, 1);
-      float d = qk_h2f(base + qk_field_offset(L, row, blk, 2));
+      const uint8_t *p0 = at(0, 0), *sc = at(1, 0);
+      float d = qk_h2f(at(2, 0));
       int g = i >> 7, rem = i & 127, k = rem >> 5, l = rem & 31, is = l >> 4;
       uint8_t qlb = p0[64 * g + l + ((k & 1) ? 32 : 0)];
       uint8_t qhb = p0[128 + 32 * g + l];
@@ -65,12 +66,12 @@ __device__ __forceinline__ float qk_dequant_elem(const QkLayout &L, const uint8_
       return __fmul_rn(__fmul_rn(d, s), (float)q);
     }
     default: {  // IQ4_XS, reference/iq4_xs.rs:73-93
-      const uint8_t *h = base + qk_field_offset(L, row, blk, 1);
+      const uint8_t *h = at(1, 0);
       float d = qk_h2f(h);
       uint32_t sh = h[2] | (h[3] << 8);
       int sub = i >> 5, j = i & 31;
       int ls = ((h[4 + (sub >> 1)] >> (4 * (sub & 1))) & 0x0F) | (((sh >> (2 * sub)) & 3) << 4);
-      uint8_t byte = p0[16 * sub + (j >> 1)];
+      uint8_t byte = *at(0, 16 * sub + (j >> 1));
       int n = (j & 1) ? (byte >> 4) : (byte & 0x0F);
       float scale = __fmul_rn(d, (float)(ls - 32));
       return __fmul_rn(scale, (float)QK_KVALUES_IQ4NL[n]);

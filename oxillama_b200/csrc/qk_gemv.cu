@@ -24,80 +24,14 @@
 // a different order and with x carried to ~24 bits.
 #include "qk_formats.cuh"
 #include "qk_kernels.h"
+#include "qk_pipe.cuh"
+
+using namespace qkpipe;
 
 namespace {
 
 constexpr int NT = 256;          // threads per CTA
 constexpr int NWARP = NT / 32;
-constexpr uint32_t SPIN_LIMIT = 1u << 20;
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
-                                         uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false if the barrier never flipped.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; i++)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // u8 x s8
-  int d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {  // s8 x s8
-  int d;
-  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float4 lds128f(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float h2f_bits(uint32_t h) {
-  return __half2float(__ushort_as_half((unsigned short)(h & 0xFFFFu)));
-}
 
 // Position of column e's digit byte inside its 256-column span, per format:
 // the order in which the format's packed words meet their activations.
@@ -237,28 +171,7 @@ __global__ void __launch_bounds__(NT)
     }
 
     // ---- per-tile scale decode into floats (one thread per block of the tile)
-    if (TYPE == QK_T_Q4_K) {
-      for (uint32_t i = threadIdx.x; i < 8 * nbt; i += NT) {
-        uint4 h = lds128(tile + i * 144);
-        float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
-        // reference/q4_k.rs:27-49, four fields at a time
-        uint32_t sc03 = h.y & 0x3F3F3F3Fu, mn03 = h.z & 0x3F3F3F3Fu;
-        uint32_t sc47 = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-        uint32_t mn47 = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          uint32_t scw = g < 2 ? sc03 : sc47, mnw = g < 2 ? mn03 : mn47;
-          int sh = (g & 1) * 16;
-          float4 o;
-          o.x = d * (float)((scw >> sh) & 0xFF);
-          o.y = d * (float)((scw >> (sh + 8)) & 0xFF) * (1.f / 16.f);  // high nibbles enter x16
-          o.z = dmin * (float)((mnw >> sh) & 0xFF);
-          o.w = dmin * (float)((mnw >> (sh + 8)) & 0xFF);
-          *reinterpret_cast<float4 *>(smem + S.dec + (i * 4 + g) * 16) = o;
-        }
-      }
-      __syncthreads();
-    } else if (TYPE == QK_T_Q6_K) {
+    if (TYPE == QK_T_Q6_K) {
       const uint32_t p1 = tile + 8 * nbt * 192, p2 = p1 + 8 * nbt * 16;
       for (uint32_t i = threadIdx.x; i < 8 * nbt; i += NT) {
         uint4 s = lds128(p1 + i * 16);
@@ -299,38 +212,7 @@ __global__ void __launch_bounds__(NT)
 #pragma unroll
       for (int rr = 0; rr < RPT; rr++) {
         const uint32_t r = split * RPT + rr;
-        if (TYPE == QK_T_Q4_K) {
-          const uint32_t sb = u >> 2, g = u & 3u;
-          const uint32_t wa = tile + (r * nbt + sb) * 144 + 16 + 32 * g;
-          uint4 a = lds128(wa), b = lds128(wa + 16);
-          float4 sc = lds128f(sbase + S.dec + ((r * nbt + sb) * 4 + g) * 16);
-          uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-          uint32_t lo[8], hi[8];
-#pragma unroll
-          for (int k = 0; k < 8; k++) lo[k] = w[k] & 0x0F0F0F0Fu, hi[k] = w[k] & 0xF0F0F0F0u;
-#pragma unroll
-          for (int m = 0; m < M; m++) {
-            int Il[D], Ih[D];
-#pragma unroll
-            for (int d = 0; d < D; d++) {
-              int il = 0, ih = 0;
-#pragma unroll
-              for (int k = 0; k < 8; k++) {
-                il = dp4a_us(lo[k], xw[m][d][k], il);
-                ih = dp4a_us(hi[k], xw[m][d][8 + k], ih);
-              }
-              Il[d] = il, Ih[d] = ih;
-            }
-            const uint32_t xsa = sbase + S.xs + (m * (Kp / 32) + (xoff >> 5)) * 16;
-            float4 s0 = lds128f(xsa), s1 = lds128f(xsa + 16);
-            float t = acc[m][rr];
-            t = fmaf(sc.x, digits_to_f32<D>(Il, s0.x), t);
-            t = fmaf(-sc.z, s0.y, t);
-            t = fmaf(sc.y, digits_to_f32<D>(Ih, s1.x), t);
-            t = fmaf(-sc.w, s1.y, t);
-            acc[m][rr] = t;
-          }
-        } else if (TYPE == QK_T_Q4_0 || TYPE == QK_T_Q8_0) {
+        if (TYPE == QK_T_Q4_0 || TYPE == QK_T_Q8_0) {
           const uint32_t qw = TYPE == QK_T_Q4_0 ? 16u : 32u;
           const uint32_t b0 = 2 * u;  // blocks 2u, 2u+1 of this row in the tile
           const uint32_t p1 = tile + 8 * nbt * qw;
@@ -473,7 +355,7 @@ bool make_plan(const QkLayout &L, uint32_t m, int RS, Plan *P) {
   uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
   uint32_t stage_bytes = QK_TILE_ROWS * nbt_max * L.bb;
   stage_bytes = (stage_bytes + 127u) & ~127u;
-  uint32_t dec_bytes = (L.type == QK_T_Q4_K || L.type == QK_T_Q6_K) ? 8 * nbt_max * 64 : 0;
+  uint32_t dec_bytes = L.type == QK_T_Q6_K ? 8 * nbt_max * 64 : 0;
   uint32_t off = 0;
   Smem S;
   S.bars = off, off += 64;  // up to 8 stages
@@ -577,15 +459,22 @@ cudaError_t launch_m(uint32_t m, int rs, const QkLayout &L, const uint8_t *W, co
 
 bool qk_gemv_fast_supported(const QkLayout &L, uint32_t m) {
   if (m < 1 || m > QK_GEMV_MAX_M) return false;
+  if (L.type == QK_T_Q4_K) return qk_gemv_mma_supported(L, m);
   if (L.type == QK_T_IQ4_XS) return false;
   if (L.bs == 32 && (L.nb & 1u)) return false;  // 64-weight units pair two 32-blocks
   Plan P;
   return make_plan(L, m, pick_rs(L), &P);
 }
 
+size_t qk_gemv_fast_scratch_bytes(const QkLayout &L, uint32_t m) {
+  return L.type == QK_T_Q4_K ? qk_gemv_mma_scratch_bytes(L, m) : 0;
+}
+
 cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
-                                uint32_t m, uint64_t ldy, unsigned *status, int sm_count,
-                                cudaStream_t s) {
+                                uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
+                                int sm_count, cudaStream_t s) {
+  if (L.type == QK_T_Q4_K)
+    return qk_launch_gemv_mma(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
   Plan P;
   int rs = pick_rs(L);
   if (!make_plan(L, m, rs, &P)) return cudaErrorInvalidConfiguration;
@@ -594,8 +483,6 @@ cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const f
       return launch_m<QK_T_Q4_0>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
     case QK_T_Q8_0:
       return launch_m<QK_T_Q8_0>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
-    case QK_T_Q4_K:
-      return launch_m<QK_T_Q4_K>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
     case QK_T_Q6_K:
       return launch_m<QK_T_Q6_K>(m, rs, L, tiled, x, y, ldy, status, sm_count, P, s);
     default:

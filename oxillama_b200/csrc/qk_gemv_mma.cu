@@ -1,0 +1,402 @@
+// Q4_K decode-path dequant-dot (1..4 activation rows) on the integer tensor-core MMA.
+//
+// The matvec is HBM-bound; what limits a CUDA-core version on this part is the
+// issue rate of the per-weight multiply (dp4a runs at a quarter of the FP32
+// rate here).  So the multiply-accumulate of every 32-weight sub-block is
+// handed to mma.sync.m16n8k32 (u8 x s8 -> s32), whose k = 32 is exactly one
+// Q4_K sub-block, and the CUDA cores only unpack nibbles and apply one scale
+// per sub-block.  The matrix is NOT reshaped into a GEMM: each MMA still
+// computes plain row dot products, eight weight rows at a time.
+//
+//   A (16 x 32, u8): rows 0-7  = the eight weight rows, low nibbles of one
+//                                32-byte group  (sub-block 2p,   weights q)
+//                    rows 8-15 = same rows, high nibbles kept in place
+//                                               (sub-block 2p+1, weights 16 q)
+//   B (32 x 8,  s8): cols 0-2 = the three base-254 digits of the activations
+//                               of sub-block 2p, cols 3-5 = those of 2p+1
+//   C (16 x 8, s32): C[r][0..2] and C[8+r][3..5] are the integer dots wanted;
+//                    the cross terms are ignored.
+//
+// Activations are split per 32-column block as x ~= sx (D0 + D1/254 + D2/254^2)
+// with |D| <= 127 (error <= amax * 6.1e-8), so the integer dots are exact and
+// the result carries f32-grade accuracy:
+//   y[row] = sum_sub  d sc_sub sx_sub (I0 + I1/254 + I2/254^2)  -  dmin mn_sub Sx_sub
+// with d, dmin, sc, mn decoded as reference/q4_k.rs:27-49,141-157 and Sx the
+// f32 sum of x over the sub-block (the `- m1` term of reference/q4_k.rs:163).
+//
+// Two kernels per call:
+//  1. qk_xsplit_kernel splits x once into the digit planes and (sx, Sx) pairs
+//     and leaves them in a small scratch image in global memory;
+//  2. qk_gemv_q4k_mma_kernel, persistent, one CTA per SM: a producer warp
+//     streams 8-row tiles into a ring of shared-memory stages with
+//     cp.async.bulk (mbarrier completion) and brings the x image in with one
+//     more bulk copy; 16 compute warps take one super-block column of the tile
+//     each (header decode in-lane, four MMAs), hand the stage back through an
+//     "empty" mbarrier, and leave their row partials in a small ring that one
+//     warp per chunk sums and writes out.  No CTA-wide barrier in steady state.
+// Both kernels use programmatic dependent launch: the weight prefetch of call
+// i+1 (weights are immutable) overlaps the tail of call i; griddepcontrol.wait
+// orders everything that touches x, y or the scratch image.  Every wait on an
+// mbarrier is bounded and reports QK_DEV_TIMEOUT instead of spinning.
+#include <cstdlib>
+
+#include "qk_formats.cuh"
+#include "qk_kernels.h"
+#include "qk_pipe.cuh"
+
+using namespace qkpipe;
+
+namespace {
+
+constexpr int CW = 16;                          // compute warps
+constexpr int NT = (CW + 1) * 32;               // + one producer warp
+constexpr uint32_t NBT = QK_TILE_ELEMS / 256;   // super-blocks per full k-tile (16)
+constexpr int MAX_STAGE = 12;
+constexpr int MAX_SLOT = MAX_STAGE + 1;
+static_assert(NBT == CW, "one compute warp per super-block column of a tile");
+
+struct SmemMma {
+  uint32_t full, empty, redfull, xbar, flag;  // mbarriers (8 B each) and the abort flag
+  uint32_t red, ximg, stage;
+  uint32_t PS;         // digit plane stride, bytes
+  uint32_t xs_off;     // offset of the (sx, Sx) table inside the x image
+  uint32_t ximg_bytes;
+};
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%11,%12,%13};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+// Exact int -> float for |v| < 2^22 on the full-rate pipes (no I2F).
+__device__ __forceinline__ float small_int_to_float(int v) {
+  return __int_as_float(0x4B400000 + v) - 12582912.0f;
+}
+
+// ---------------------------------------------------------------- x image
+// [M][3 digit planes of PS bytes, natural column order][M][Kp/32] float2 (sx, Sx)
+__global__ void __launch_bounds__(256)
+    qk_xsplit_kernel(const float *__restrict__ x, uint32_t m_rows, uint32_t cols, uint32_t Kp,
+                     uint32_t PS, uint32_t xs_off, unsigned char *__restrict__ img) {
+  pdl_launch_dependents();
+  pdl_wait();  // x may be the previous kernel's output; the image may still be in use by it
+  const uint32_t quads = Kp / 4, total = m_rows * quads;
+  const uint32_t it = blockIdx.x * 256 + threadIdx.x;
+  if (it >= total) return;  // warp-uniform: total is a multiple of 64
+  const uint32_t m = it / quads, e0 = (it % quads) * 4;
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) v[i] = (e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float s4 = (v[0] + v[1]) + (v[2] + v[3]);
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {  // the 8 threads of one 32-column block
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    s4 += __shfl_xor_sync(0xffffffffu, s4, o);
+  }
+  if (!(amax < 3.0e38f)) amax = 3.0e38f;  // inf/nan in x: keep the arithmetic finite
+  const float inv = amax > 0.f ? 127.f / amax : 0.f;
+  uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float d0 = fminf(fmaxf(rintf(v[i] * inv), -127.f), 127.f);
+    float t1 = fmaf(v[i], inv, -d0) * 254.f;
+    float d1 = fminf(fmaxf(rintf(t1), -127.f), 127.f);
+    float d2 = fminf(fmaxf(rintf((t1 - d1) * 254.f), -127.f), 127.f);
+    w0 |= ((uint32_t)(int)d0 & 0xFFu) << (8 * i);
+    w1 |= ((uint32_t)(int)d1 & 0xFFu) << (8 * i);
+    w2 |= ((uint32_t)(int)d2 & 0xFFu) << (8 * i);
+  }
+  unsigned char *p = img + (size_t)m * 3 * PS + e0;
+  *reinterpret_cast<uint32_t *>(p) = w0;
+  *reinterpret_cast<uint32_t *>(p + PS) = w1;
+  *reinterpret_cast<uint32_t *>(p + 2 * PS) = w2;
+  if ((threadIdx.x & 7) == 0)
+    *reinterpret_cast<float2 *>(img + xs_off + ((size_t)m * (Kp / 32) + e0 / 32) * 8) =
+        make_float2(amax * (1.f / 127.f), s4);
+}
+
+// ---------------------------------------------------------------- main kernel
+template <int M>
+__global__ void __launch_bounds__(NT, 1)
+    qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W,
+                           const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
+                           uint64_t ldy, unsigned *status, int nstage, int nslot,
+                           uint32_t stage_bytes, SmemMma S, uint32_t Kp) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + S.flag);
+
+  const uint32_t my_chunks =
+      blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint32_t my_items = my_chunks * L.ktiles;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < nstage; s++) {
+      mbar_init(sbase + S.full + s * 8, 1);
+      mbar_init(sbase + S.empty + s * 8, CW);
+    }
+    for (int s = 0; s < nslot; s++) mbar_init(sbase + S.redfull + s * 8, CW);
+    mbar_init(sbase + S.xbar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == CW) {
+    // ================= producer warp (one lane) =================
+    if (lane == 0) {
+      auto issue = [&](uint32_t item) {
+        uint32_t chunk = blockIdx.x + (item / L.ktiles) * gridDim.x, kt = item % L.ktiles;
+        uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, kt) * L.bb;
+        uint32_t st = item % nstage, bar = sbase + S.full + st * 8;
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(sbase + S.stage + st * stage_bytes, W + qk_tile_offset(L, chunk, kt), bytes, bar);
+      };
+      // weights are immutable: their prefetch need not wait for the previous kernel
+      uint32_t item = 0;
+      for (; item < (uint32_t)nstage && item < my_items; item++) issue(item);
+      pdl_wait();  // the x image is the previous kernel's output
+      mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
+      bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
+      for (; item < my_items; item++) {
+        if (!mbar_wait_bounded(sbase + S.empty + (item % nstage) * 8, ((item / nstage) - 1) & 1)) {
+          *abort_flag = 1;
+          atomicOr(status, QK_DEV_TIMEOUT);
+        }
+        if (*abort_flag) break;
+        issue(item);
+      }
+    }
+    return;
+  }
+
+  // ================= compute warps =================
+  const uint32_t g = lane >> 2, tig = lane & 3;
+  // lane-constant routing of the useful C entries (see the header comment); the
+  // x16 of the high-nibble rows is folded into the sub-block scale
+  const float kA = tig == 0 ? 1.f : tig == 1 ? 1.f / (254.f * 254.f) : tig == 2 ? 1.f / 254.f : 0.f;
+  const float kB = tig == 0 ? 1.f / 254.f : tig == 1 ? 1.f : tig == 2 ? 1.f / (254.f * 254.f) : 0.f;
+  const bool a_lo = tig < 2, b_lo = tig == 0;
+  const uint32_t b_off = (g % 3) * S.PS + (g >= 3 ? 32u : 0u) + tig * 8;  // B column g of this lane
+  const uint32_t src_base = lane & ~3u;
+
+  pdl_wait();  // y may be read or written by the previous kernel
+  if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
+    *abort_flag = 1;
+    atomicOr(status, QK_DEV_TIMEOUT);
+  }
+
+  float accA[M], accB[M], mt[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) accA[m] = accB[m] = mt[m] = 0.f;
+
+  for (uint32_t item = 0; item < my_items; item++) {
+    const uint32_t cidx = item / L.ktiles, kt = item % L.ktiles;
+    const uint32_t st = item % nstage, nbt = qk_tile_nb(L, kt);
+    const uint32_t tile = sbase + S.stage + st * stage_bytes;
+    if (!mbar_wait_bounded(sbase + S.full + st * 8, (item / nstage) & 1)) {
+      *abort_flag = 1;
+      atomicOr(status, QK_DEV_TIMEOUT);
+    }
+    if (*abort_flag) break;
+
+    if (warp < nbt) {
+      const uint32_t sb = warp;
+      const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
+      // ---- this lane decodes sub-blocks (2 tig, 2 tig + 1) of row g's header
+      float tx[M], ty[M];
+      {
+        uint4 h = lds128(tile + (g * nbt + sb) * 16);
+        const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
+        // reference/q4_k.rs:27-49, four 6-bit fields per word
+        const uint32_t scw = tig < 2 ? (h.y & 0x3F3F3F3Fu)
+                                     : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+        const uint32_t mnw = tig < 2 ? (h.z & 0x3F3F3F3Fu)
+                                     : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
+        const uint32_t sh = (tig & 1u) * 16;
+        const float ds0 = d * small_int_to_float((scw >> sh) & 0xFF);
+        const float ds1 = d * small_int_to_float((scw >> (sh + 8)) & 0xFF) * (1.f / 16.f);
+        const float dm0 = dmin * small_int_to_float((mnw >> sh) & 0xFF);
+        const float dm1 = dmin * small_int_to_float((mnw >> (sh + 8)) & 0xFF);
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+          float4 s = lds128f(sbase + S.ximg + S.xs_off + (m * (Kp / 32) + sub + 2 * tig) * 8);
+          tx[m] = ds0 * s.x;
+          ty[m] = ds1 * s.z;
+          mt[m] = fmaf(dm0, s.y, mt[m]);
+          mt[m] = fmaf(dm1, s.w, mt[m]);
+        }
+      }
+      // ---- four MMAs: one per 32-byte group of the super-block
+      const uint32_t qa = tile + QK_TILE_ROWS * nbt * 16 + sb * 1024 + g * 32 + tig * 8;
+      const uint32_t xb = sbase + S.ximg + sub * 32 + b_off;
+#pragma unroll
+      for (int gq = 0; gq < 4; gq++) {
+        const uint2 w = lds64(qa + gq * 256);
+        const uint32_t a0 = w.x & 0x0F0F0F0Fu, a2 = w.y & 0x0F0F0F0Fu;
+        const uint32_t a1 = w.x & 0xF0F0F0F0u, a3 = w.y & 0xF0F0F0F0u;
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+          uint2 b = make_uint2(0u, 0u);
+          if (g < 6) b = lds64(xb + m * 3 * S.PS + gq * 64);
+          int c[4];
+          mma_u8s8(c, a0, a1, a2, a3, b.x, b.y);
+          const float sx = __shfl_sync(0xffffffffu, tx[m], src_base + gq);
+          const float sy = __shfl_sync(0xffffffffu, ty[m], src_base + gq);
+          accA[m] = fmaf(a_lo ? sx : sy, small_int_to_float(a_lo ? c[0] : c[2]), accA[m]);
+          accB[m] = fmaf(b_lo ? sx : sy, small_int_to_float(b_lo ? c[1] : c[3]), accB[m]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sbase + S.empty + st * 8);  // this warp is done with the stage
+
+    if (kt + 1 == L.ktiles) {  // chunk finished: leave the row partials, one warp sums them
+      const uint32_t slot = cidx % nslot;
+      float *red = reinterpret_cast<float *>(smem + S.red) + slot * (CW * M * 8);
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        float v = fmaf(kA, accA[m], kB * accB[m]) - mt[m];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        if (tig == 0) red[(warp * M + m) * 8 + g] = v;
+        accA[m] = accB[m] = mt[m] = 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sbase + S.redfull + slot * 8);
+      if (warp == cidx % CW) {
+        if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, (cidx / nslot) & 1)) {
+          *abort_flag = 1;
+          atomicOr(status, QK_DEV_TIMEOUT);
+        }
+        if (lane < 8 * M) {
+          const uint32_t m = lane >> 3, r = lane & 7u;
+          float v = 0.f;
+#pragma unroll
+          for (int wv = 0; wv < CW; wv++) v += red[(wv * M + m) * 8 + r];
+          const uint32_t row = (blockIdx.x + cidx * gridDim.x) * 8 + r;
+          if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
+        }
+      }
+    }
+  }
+}
+
+struct PlanMma {
+  SmemMma S;
+  uint32_t Kp, stage_bytes, total;
+  int nstage, nslot;
+};
+
+bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
+  uint32_t Kp = L.nb * 256u;
+  uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
+  uint32_t stage_bytes = QK_TILE_ROWS * nbt_max * L.bb;
+  stage_bytes = (stage_bytes + 127u) & ~127u;
+  SmemMma S;
+  uint32_t off = 0;
+  S.full = off, off += MAX_STAGE * 8;
+  S.empty = off, off += MAX_STAGE * 8;
+  S.redfull = off, off += MAX_SLOT * 8;
+  S.xbar = off, off += 8;
+  S.flag = off, off += 8;
+  off = (off + 127u) & ~127u;
+  S.red = off, off += MAX_SLOT * CW * m * 8 * 4;
+  off = (off + 127u) & ~127u;
+  S.PS = Kp + 64;
+  S.xs_off = m * 3 * S.PS;
+  S.ximg_bytes = S.xs_off + m * (Kp / 32) * 8;  // multiple of 16: PS and Kp/32*8 both are
+  S.ximg = off, off += S.ximg_bytes;
+  off = (off + 127u) & ~127u;
+  S.stage = off;
+  const uint32_t budget = 227u * 1024u - 1024u;
+  if (off + 2 * stage_bytes > budget) return false;
+  int nstage = (int)((budget - off) / stage_bytes);
+  if (nstage > MAX_STAGE) nstage = MAX_STAGE;
+  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1;
+  P->total = off + nstage * stage_bytes;
+  return true;
+}
+
+template <int M>
+cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
+                       unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
+                       cudaStream_t s) {
+  auto kern = qk_gemv_q4k_mma_kernel<M>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  static int use_pdl = -1;
+  if (use_pdl < 0) {
+    const char *e = getenv("QK_PDL");
+    use_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+
+  const uint32_t quads = (uint32_t)M * P.Kp / 4;
+  cudaLaunchConfig_t c0 = {};
+  c0.gridDim = dim3((quads + 255) / 256), c0.blockDim = dim3(256), c0.stream = s;
+  c0.attrs = at, c0.numAttrs = use_pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&c0, qk_xsplit_kernel, x, (uint32_t)M, L.cols, P.Kp, P.S.PS,
+                                     P.S.xs_off, ximg);
+  if (e != cudaSuccess) return e;
+
+  uint32_t grid = (uint32_t)sm_count;  // persistent, one CTA per SM
+  if (grid > L.chunks) grid = L.chunks;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NT), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
+  cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, L, W, (const unsigned char *)ximg, y, ldy, status, P.nstage,
+                            P.nslot, P.stage_bytes, P.S, P.Kp);
+}
+
+}  // namespace
+
+bool qk_gemv_mma_supported(const QkLayout &L, uint32_t m) {
+  if (L.type != QK_T_Q4_K || m < 1 || m > 4) return false;
+  PlanMma P;
+  return make_plan_mma(L, m, &P);
+}
+
+size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m) {
+  PlanMma P;
+  return make_plan_mma(L, m, &P) ? P.S.ximg_bytes : 0;
+}
+
+cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
+                               uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
+                               int sm_count, cudaStream_t s) {
+  PlanMma P;
+  if (!make_plan_mma(L, m, &P)) return cudaErrorInvalidConfiguration;
+  switch (m) {
+    case 1:
+      return launch_mma<1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+    case 2:
+      return launch_mma<2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+    case 3:
+      return launch_mma<3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+    default:
+      return launch_mma<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+  }
+}

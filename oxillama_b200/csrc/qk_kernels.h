@@ -20,6 +20,16 @@ cudaError_t qk_launch_quantize_q8_0(const float *x, uint64_t n, uint8_t *out, cu
 // Bandwidth-bound decode path (m <= QK_GEMV_MAX_M): bulk-copied tiles, integer dot.
 #define QK_GEMV_MAX_M 4
 bool qk_gemv_fast_supported(const QkLayout &L, uint32_t m);
+// Q4_K decode path on the integer tensor-core MMA (m16n8k32 u8 x s8).  `scratch`
+// is device memory of at least qk_gemv_mma_scratch_bytes(L, m) bytes, 16-byte
+// aligned, that the call may overwrite (the split activations live there
+// between its two kernels).
+bool qk_gemv_mma_supported(const QkLayout &L, uint32_t m);
+size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m);
+cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
+                               uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
+                               int sm_count, cudaStream_t s);
+size_t qk_gemv_fast_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
-                                uint32_t m, uint64_t ldy, unsigned *status, int sm_count,
-                                cudaStream_t s);
+                                uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
+                                int sm_count, cudaStream_t s);

@@ -9,17 +9,23 @@
 //   tile  = 8 consecutive rows x up to QK_TILE_ELEMS consecutive columns
 //   chunk = the tiles of one 8-row group, k-tile after k-tile
 //   inside a tile the fields of its blocks are split into planes, each plane
-//   an array [8 rows][nbt blocks] of one fixed-width field:
+//   holding one fixed-width field of every block of the tile:
 //
 //     Q4_0   plane0 nibbles 16 B | plane1 d 2 B
 //     Q8_0   plane0 int8s   32 B | plane1 d 2 B
-//     Q4_K   plane0 whole block 144 B (already 16-byte granular)
+//     Q4_K   plane0 d,dmin,scales 16 B | plane1 nibbles 128 B, interleaved by 32
 //     Q6_K   plane0 ql+qh  192 B | plane1 scales 16 B | plane2 d 2 B
 //     IQ4_XS plane0 nibbles 128 B | plane1 d,scales_h,scales_l 8 B
 //
-// Every plane of every tile then starts on a 16-byte boundary for any K and
-// any row count (8 * nbt * width is a multiple of 16 for all widths above),
-// and one tile is one contiguous span of HBM, so a single bulk copy stages it.
+//   A plane is either row-major, [8 rows][nbt blocks][width], or interleaved
+//   with granule g: [nbt blocks][width/g granules][8 rows][g bytes].  The
+//   interleaved form puts the same 32-byte group of all 8 rows side by side,
+//   which is exactly one tensor-core B/A fragment row per lane group and reads
+//   from shared memory without bank conflicts.
+//
+// Every plane of every tile starts on a 16-byte boundary for any K and any row
+// count (8 * nbt * width is a multiple of 16 for all widths above), and one
+// tile is one contiguous span of HBM, so a single bulk copy stages it.
 // Rows are padded up to a multiple of 8 with all-zero blocks (scale 0: they
 // contribute exactly 0 and are never written out).
 #pragma once
@@ -45,6 +51,7 @@ struct QkLayout {
   uint32_t nplanes;
   uint32_t pw[3];        // plane widths, bytes per block
   uint32_t po[3];        // offset of the plane's field inside the GGUF block
+  uint32_t pg[3];        // 0: row-major plane; g > 0: interleaved with granule g bytes
   uint32_t rows, cols;   // logical shape of this shard
   uint32_t chunks;       // ceil(rows / 8)
   uint64_t chunk_bytes;  // 8 * nb * bb
@@ -65,8 +72,8 @@ static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayo
       l.pw[0] = 32; l.po[0] = 2; l.pw[1] = 2; l.po[1] = 0;
       break;
     case QK_T_Q4_K:
-      l.bs = 256; l.bb = 144; l.nplanes = 1;
-      l.pw[0] = 144; l.po[0] = 0;
+      l.bs = 256; l.bb = 144; l.nplanes = 2;
+      l.pw[0] = 16; l.po[0] = 0; l.pw[1] = 128; l.po[1] = 16; l.pg[1] = 32;
       break;
     case QK_T_Q6_K:
       l.bs = 256; l.bb = 210; l.nplanes = 3;
@@ -112,12 +119,16 @@ __host__ __device__ static inline uint32_t qk_plane_offset(const QkLayout &L, ui
   return QK_TILE_ROWS * nbt_this * w;
 }
 
-// Address of field-plane p of block (row, blk).
-__host__ __device__ static inline uint64_t qk_field_offset(const QkLayout &L, uint32_t row,
-                                                           uint32_t blk, int p) {
+// Offset of byte `o` of field-plane p of block (row, blk).  Bytes of one granule
+// (the whole field, for a row-major plane) are contiguous.
+__host__ __device__ static inline uint64_t qk_byte_offset(const QkLayout &L, uint32_t row,
+                                                          uint32_t blk, int p, uint32_t o) {
   uint32_t chunk = row / QK_TILE_ROWS, r = row % QK_TILE_ROWS;
   uint32_t kt = blk / L.nbt, b = blk % L.nbt;
   uint32_t nbt_this = qk_tile_nb(L, kt);
-  return qk_tile_offset(L, chunk, kt) + qk_plane_offset(L, nbt_this, p) +
-         (uint64_t)(r * nbt_this + b) * L.pw[p];
+  uint64_t base = qk_tile_offset(L, chunk, kt) + qk_plane_offset(L, nbt_this, p);
+  uint32_t g = L.pg[p];
+  if (g == 0) return base + (uint64_t)(r * nbt_this + b) * L.pw[p] + o;
+  return base + (uint64_t)b * QK_TILE_ROWS * L.pw[p] + (uint64_t)(o / g) * QK_TILE_ROWS * g +
+         (uint64_t)r * g + (o % g);
 }

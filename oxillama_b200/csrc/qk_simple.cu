@@ -18,7 +18,7 @@ __global__ void qk_repack_kernel(QkLayout L, const uint8_t *__restrict__ raw,
     int p = 0;
     for (int i = 0; i < (int)L.nplanes; i++)
       if (off >= L.po[i] && off < L.po[i] + L.pw[i]) p = i;
-    uint64_t dst = qk_field_offset(L, row, blk, p) + (off - L.po[p]);
+    uint64_t dst = qk_byte_offset(L, row, blk, p, off - L.po[p]);
     *reinterpret_cast<uint16_t *>(tiled + dst) =
         *reinterpret_cast<const uint16_t *>(raw + gblk * L.bb + off);
   }
@@ -143,11 +143,8 @@ __global__ void __launch_bounds__(128)
   float r = roundf(__fmul_rn(v, id));
   int q = (r != r) ? 0 : (r >= 127.f ? 127 : (r <= -128.f ? -128 : (int)r));
   uint8_t *o = out + b * 34;
-  if (lane == 0) {
-    unsigned short h = __half_as_ushort(__float2half_rn(d));
-    o[0] = (uint8_t)(h & 0xFF);
-    o[1] = (uint8_t)(h >> 8);
-  }
+  const unsigned h = __half_as_ushort(__float2half_rn(d));
+  if (lane < 2) o[lane] = (uint8_t)((h >> (8 * lane)) & 0xFFu);  // f16 scale, little-endian
   o[2 + lane] = (uint8_t)(int8_t)q;
 }
 
