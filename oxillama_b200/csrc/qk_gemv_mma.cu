@@ -30,14 +30,16 @@
 //  2. qk_gemv_q4k_mma_kernel, persistent, one CTA per SM: a producer warp
 //     streams 8-row tiles into a ring of shared-memory stages with
 //     cp.async.bulk (mbarrier completion) and brings the x image in with one
-//     more bulk copy; 16 compute warps take one super-block column of the tile
-//     each (header decode in-lane, four MMAs), hand the stage back through an
-//     "empty" mbarrier, and leave their row partials in a small ring that one
-//     warp per chunk sums and writes out.  No CTA-wide barrier in steady state.
+//     more bulk copy; 8 compute warps take two super-block columns of the tile
+//     each (header decode in-lane, four MMAs per column) and leave their row
+//     partials in a small ring; the producer warp sums a chunk's partials, writes
+//     the outputs and then refills the chunk's stages.  No CTA-wide barrier and
+//     no compute warp ever waits for another in steady state.
 // Both kernels use programmatic dependent launch: the weight prefetch of call
 // i+1 (weights are immutable) overlaps the tail of call i; griddepcontrol.wait
 // orders everything that touches x, y or the scratch image.  Every wait on an
-// mbarrier is bounded and reports QK_DEV_TIMEOUT instead of spinning.
+// mbarrier is bounded: when one runs out the warp stops, QK_DEV_TIMEOUT is
+// raised in the status word, and the other warps run into their own bounds.
 #include <cstdlib>
 
 #include "qk_formats.cuh"
@@ -48,15 +50,13 @@ using namespace qkpipe;
 
 namespace {
 
-constexpr int CW = 16;                          // compute warps
-constexpr int NT = (CW + 1) * 32;               // + one producer warp
+constexpr int MAX_CW = 16;                      // compute warps: 8 or 16 (+ one producer warp)
 constexpr uint32_t NBT = QK_TILE_ELEMS / 256;   // super-blocks per full k-tile (16)
 constexpr int MAX_STAGE = 12;
 constexpr int MAX_SLOT = MAX_STAGE + 1;
-static_assert(NBT == CW, "one compute warp per super-block column of a tile");
 
 struct SmemMma {
-  uint32_t full, empty, redfull, xbar, flag;  // mbarriers (8 B each) and the abort flag
+  uint32_t full, redfull, xbar;  // mbarriers (8 B each)
   uint32_t red, ximg, stage;
   uint32_t PS;         // digit plane stride, bytes
   uint32_t xs_off;     // offset of the (sx, Sx) table inside the x image
@@ -128,16 +128,70 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---------------------------------------------------------------- main kernel
-template <int M>
-__global__ void __launch_bounds__(NT, 1)
-    qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W,
+// The same split as qk_xsplit_kernel, done by the compute warps straight into the
+// CTA's shared-memory x image (used when x is small enough that every CTA
+// redoing it is cheaper than a second kernel and a copy).
+template <int M, int CW>
+__device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32_t Kp,
+                              unsigned char *img, uint32_t PS, uint32_t xs_off) {
+  constexpr int CT = CW * 32;  // compute threads
+  const uint32_t quads = Kp / 4, total = (uint32_t)M * quads;
+  constexpr int U = 4;  // quads in flight per thread
+  for (uint32_t base = 0; base < total; base += CT * U) {
+    float v[U][4];
+#pragma unroll
+    for (int j = 0; j < U; j++) {
+      const uint32_t it = base + j * CT + threadIdx.x;
+      const uint32_t m = it / quads, e0 = (it % quads) * 4;
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+        v[j][i] = (it < total && e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < U; j++) {
+      const uint32_t it = base + j * CT + threadIdx.x;
+      if (it >= total) continue;  // warp-uniform: total and CT are multiples of 32
+      const uint32_t m = it / quads, e0 = (it % quads) * 4;
+      float amax = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fmaxf(fabsf(v[j][2]), fabsf(v[j][3])));
+      float s4 = (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        s4 += __shfl_xor_sync(0xffffffffu, s4, o);
+      }
+      if (!(amax < 3.0e38f)) amax = 3.0e38f;
+      const float inv = amax > 0.f ? 127.f / amax : 0.f;
+      uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        float d0 = fminf(fmaxf(rintf(v[j][i] * inv), -127.f), 127.f);
+        float t1 = fmaf(v[j][i], inv, -d0) * 254.f;
+        float d1 = fminf(fmaxf(rintf(t1), -127.f), 127.f);
+        float d2 = fminf(fmaxf(rintf((t1 - d1) * 254.f), -127.f), 127.f);
+        w0 |= ((uint32_t)(int)d0 & 0xFFu) << (8 * i);
+        w1 |= ((uint32_t)(int)d1 & 0xFFu) << (8 * i);
+        w2 |= ((uint32_t)(int)d2 & 0xFFu) << (8 * i);
+      }
+      unsigned char *p = img + (size_t)m * 3 * PS + e0;
+      *reinterpret_cast<uint32_t *>(p) = w0;
+      *reinterpret_cast<uint32_t *>(p + PS) = w1;
+      *reinterpret_cast<uint32_t *>(p + 2 * PS) = w2;
+      if ((threadIdx.x & 7) == 0)
+        *reinterpret_cast<float2 *>(img + xs_off + ((size_t)m * (Kp / 32) + e0 / 32) * 8) =
+            make_float2(amax * (1.f / 127.f), s4);
+    }
+  }
+}
+
+template <int M, bool INCTA, int CW>
+__global__ void __launch_bounds__((CW + 1) * 32, 1)
+    qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
                            uint64_t ldy, unsigned *status, int nstage, int nslot,
                            uint32_t stage_bytes, SmemMma S, uint32_t Kp) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + S.flag);
 
   const uint32_t my_chunks =
       blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -145,11 +199,9 @@ __global__ void __launch_bounds__(NT, 1)
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
     for (int s = 0; s < nstage; s++) {
       mbar_init(sbase + S.full + s * 8, 1);
-      mbar_init(sbase + S.empty + s * 8, CW);
-    }
+          }
     for (int s = 0; s < nslot; s++) mbar_init(sbase + S.redfull + s * 8, CW);
     mbar_init(sbase + S.xbar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -158,29 +210,52 @@ __global__ void __launch_bounds__(NT, 1)
   __syncthreads();
 
   if (warp == CW) {
-    // ================= producer warp (one lane) =================
+    // ================= producer / reducer warp =================
+    // Lane 0 streams tiles; after a chunk's partials are complete the warp sums
+    // them, writes the 8 x M outputs, and only then refills the stages the chunk
+    // occupied.  Gating the refills on the reduction bounds how far the compute
+    // warps can run ahead, which is what makes the ring of `nslot` partial
+    // buffers safe without a second handshake.
+    uint32_t pc = 0, pkt = 0, pst = 0;  // chunk ordinal, k-tile and stage of the next item
+    auto issue = [&]() {                // lane 0 only
+      const uint32_t chunk = blockIdx.x + pc * gridDim.x;
+      const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
+      const uint32_t bar = sbase + S.full + pst * 8;
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(sbase + S.stage + pst * stage_bytes, W + qk_tile_offset(L, chunk, pkt), bytes, bar);
+      if (++pkt == L.ktiles) pkt = 0, pc++;
+      if (++pst == (uint32_t)nstage) pst = 0;
+    };
+    uint32_t item = 0;
     if (lane == 0) {
-      auto issue = [&](uint32_t item) {
-        uint32_t chunk = blockIdx.x + (item / L.ktiles) * gridDim.x, kt = item % L.ktiles;
-        uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, kt) * L.bb;
-        uint32_t st = item % nstage, bar = sbase + S.full + st * 8;
-        mbar_expect_tx(bar, bytes);
-        bulk_g2s(sbase + S.stage + st * stage_bytes, W + qk_tile_offset(L, chunk, kt), bytes, bar);
-      };
       // weights are immutable: their prefetch need not wait for the previous kernel
-      uint32_t item = 0;
-      for (; item < (uint32_t)nstage && item < my_items; item++) issue(item);
-      pdl_wait();  // the x image is the previous kernel's output
+      for (; item < (uint32_t)nstage && item < my_items; item++) issue();
+    }
+    pdl_wait();  // the x image and y belong to the previous kernel until it has finished
+    if (!INCTA && lane == 0) {
       mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
       bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
-      for (; item < my_items; item++) {
-        if (!mbar_wait_bounded(sbase + S.empty + (item % nstage) * 8, ((item / nstage) - 1) & 1)) {
-          *abort_flag = 1;
-          atomicOr(status, QK_DEV_TIMEOUT);
-        }
-        if (*abort_flag) break;
-        issue(item);
+    }
+    uint32_t slot = 0, sph = 0;
+    for (uint32_t c = 0; c < my_chunks; c++) {
+      if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, sph)) {
+        if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
+        break;
       }
+      const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (CW * M * 8);
+      if (lane < 8 * M) {
+        const uint32_t m = lane >> 3, r = lane & 7u;
+        float v = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < CW; wv++) v += red[(wv * M + m) * 8 + r];
+        const uint32_t row = (blockIdx.x + c * gridDim.x) * 8 + r;
+        if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
+      }
+      __syncwarp();
+      if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
+      // every compute warp released the chunk's stages before it posted its partials
+      if (lane == 0)
+        for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
     }
     return;
   }
@@ -188,86 +263,102 @@ __global__ void __launch_bounds__(NT, 1)
   // ================= compute warps =================
   const uint32_t g = lane >> 2, tig = lane & 3;
   // lane-constant routing of the useful C entries (see the header comment); the
-  // x16 of the high-nibble rows is folded into the sub-block scale
+  // x16 of the high-nibble rows is folded into the sub-block scale.  Lanes with
+  // tig == 3 hold only cross terms and the two unused B columns: weight 0.
   const float kA = tig == 0 ? 1.f : tig == 1 ? 1.f / (254.f * 254.f) : tig == 2 ? 1.f / 254.f : 0.f;
   const float kB = tig == 0 ? 1.f / 254.f : tig == 1 ? 1.f : tig == 2 ? 1.f / (254.f * 254.f) : 0.f;
   const bool a_lo = tig < 2, b_lo = tig == 0;
-  const uint32_t b_off = (g % 3) * S.PS + (g >= 3 ? 32u : 0u) + tig * 8;  // B column g of this lane
+  // B column g of this lane: digit g % 3 of sub-block 2p (g < 3) or 2p + 1 (g >= 3);
+  // columns 6 and 7 are never read back, so they may hold anything
+  const uint32_t b_off = (g % 3) * S.PS + (g >= 3 ? 32u : 0u) + tig * 8;
   const uint32_t src_base = lane & ~3u;
+  // header decode constants of this lane (it unpacks sub-blocks 2 tig and 2 tig + 1)
+  const bool hi_half = tig >= 2;
+  const uint32_t m1 = hi_half ? 0x0F0F0F0Fu : 0x3F3F3F3Fu, m2 = hi_half ? 0x30303030u : 0u;
+  const uint32_t sel0 = 0x7540u | (2u * (tig & 1u)), sel1 = sel0 + 1u;
 
-  pdl_wait();  // y may be read or written by the previous kernel
-  if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
-    *abort_flag = 1;
-    atomicOr(status, QK_DEV_TIMEOUT);
+  pdl_wait();  // x may be the previous kernel's output; y may be read or written by it
+  bool dead = false;
+  if (INCTA) {
+    xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off);
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
+  } else if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
+    dead = true;
   }
 
   float accA[M], accB[M], mt[M];
 #pragma unroll
   for (int m = 0; m < M; m++) accA[m] = accB[m] = mt[m] = 0.f;
 
-  for (uint32_t item = 0; item < my_items; item++) {
-    const uint32_t cidx = item / L.ktiles, kt = item % L.ktiles;
-    const uint32_t st = item % nstage, nbt = qk_tile_nb(L, kt);
+  // loop state kept as counters: no integer division on the critical path
+  uint32_t st = 0, fph = 0, kt = 0, slot = 0;
+  for (uint32_t item = 0; item < my_items && !dead; item++) {
+    const uint32_t nbt = qk_tile_nb(L, kt);
     const uint32_t tile = sbase + S.stage + st * stage_bytes;
-    if (!mbar_wait_bounded(sbase + S.full + st * 8, (item / nstage) & 1)) {
-      *abort_flag = 1;
-      atomicOr(status, QK_DEV_TIMEOUT);
+    if (!mbar_wait_bounded(sbase + S.full + st * 8, fph)) {
+      dead = true;
+      break;
     }
-    if (*abort_flag) break;
-
-    if (warp < nbt) {
-      const uint32_t sb = warp;
-      const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
-      // ---- this lane decodes sub-blocks (2 tig, 2 tig + 1) of row g's header
-      float tx[M], ty[M];
-      {
-        uint4 h = lds128(tile + (g * nbt + sb) * 16);
-        const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
-        // reference/q4_k.rs:27-49, four 6-bit fields per word
-        const uint32_t scw = tig < 2 ? (h.y & 0x3F3F3F3Fu)
-                                     : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
-        const uint32_t mnw = tig < 2 ? (h.z & 0x3F3F3F3Fu)
-                                     : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
-        const uint32_t sh = (tig & 1u) * 16;
-        const float ds0 = d * small_int_to_float((scw >> sh) & 0xFF);
-        const float ds1 = d * small_int_to_float((scw >> (sh + 8)) & 0xFF) * (1.f / 16.f);
-        const float dm0 = dmin * small_int_to_float((mnw >> sh) & 0xFF);
-        const float dm1 = dmin * small_int_to_float((mnw >> (sh + 8)) & 0xFF);
 #pragma unroll
-        for (int m = 0; m < M; m++) {
-          float4 s = lds128f(sbase + S.ximg + S.xs_off + (m * (Kp / 32) + sub + 2 * tig) * 8);
-          tx[m] = ds0 * s.x;
-          ty[m] = ds1 * s.z;
-          mt[m] = fmaf(dm0, s.y, mt[m]);
-          mt[m] = fmaf(dm1, s.w, mt[m]);
-        }
-      }
-      // ---- four MMAs: one per 32-byte group of the super-block
+    for (uint32_t sbi = 0; sbi < NBT / CW; sbi++) {
+      const uint32_t sb = warp + sbi * CW;
+      if (sb >= nbt) break;
+      const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
+      // ---- every shared-memory load of this super-block column is issued up front
+      const uint4 h = lds128(tile + (g * nbt + sb) * 16);
       const uint32_t qa = tile + QK_TILE_ROWS * nbt * 16 + sb * 1024 + g * 32 + tig * 8;
+      uint2 w[4];
+#pragma unroll
+      for (int gq = 0; gq < 4; gq++) w[gq] = lds64(qa + gq * 256);
+      float4 xs[M];
+      uint2 b[M][4];
       const uint32_t xb = sbase + S.ximg + sub * 32 + b_off;
 #pragma unroll
-      for (int gq = 0; gq < 4; gq++) {
-        const uint2 w = lds64(qa + gq * 256);
-        const uint32_t a0 = w.x & 0x0F0F0F0Fu, a2 = w.y & 0x0F0F0F0Fu;
-        const uint32_t a1 = w.x & 0xF0F0F0F0u, a3 = w.y & 0xF0F0F0F0u;
+      for (int m = 0; m < M; m++) {
+        xs[m] = lds128f(sbase + S.ximg + S.xs_off + (m * (Kp / 32) + sub + 2 * tig) * 8);
 #pragma unroll
-        for (int m = 0; m < M; m++) {
-          uint2 b = make_uint2(0u, 0u);
-          if (g < 6) b = lds64(xb + m * 3 * S.PS + gq * 64);
-          int c[4];
-          mma_u8s8(c, a0, a1, a2, a3, b.x, b.y);
-          const float sx = __shfl_sync(0xffffffffu, tx[m], src_base + gq);
-          const float sy = __shfl_sync(0xffffffffu, ty[m], src_base + gq);
-          accA[m] = fmaf(a_lo ? sx : sy, small_int_to_float(a_lo ? c[0] : c[2]), accA[m]);
-          accB[m] = fmaf(b_lo ? sx : sy, small_int_to_float(b_lo ? c[1] : c[3]), accB[m]);
+        for (int gq = 0; gq < 4; gq++) b[m][gq] = lds64(xb + m * 3 * S.PS + gq * 64);
+      }
+      // ---- this lane decodes sub-blocks (2 tig, 2 tig + 1) of row g's header:
+      // reference/q4_k.rs:27-49 on four 6-bit fields at a time, then byte -> f32 by
+      // dropping the byte into the mantissa of 2^23
+      const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
+      const uint32_t scw = ((hi_half ? h.w : h.y) & m1) | ((h.y >> 2) & m2);
+      const uint32_t mnw = ((hi_half ? (h.w >> 4) : h.z) & m1) | ((h.z >> 2) & m2);
+      const float ds0 = d * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel0)) - 8388608.f);
+      const float ds1 =
+          d * (1.f / 16.f) * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel1)) - 8388608.f);
+      const float dm0 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel0)) - 8388608.f);
+      const float dm1 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel1)) - 8388608.f);
+      uint32_t a[4][4];
+#pragma unroll
+      for (int gq = 0; gq < 4; gq++) {
+        a[gq][0] = w[gq].x & 0x0F0F0F0Fu, a[gq][1] = w[gq].x & 0xF0F0F0F0u;
+        a[gq][2] = w[gq].y & 0x0F0F0F0Fu, a[gq][3] = w[gq].y & 0xF0F0F0F0u;
+      }
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        const float tx = ds0 * xs[m].x, ty = ds1 * xs[m].z;
+        mt[m] = fmaf(dm0, xs[m].y, mt[m]);
+        mt[m] = fmaf(dm1, xs[m].w, mt[m]);
+        // ---- four MMAs back to back (one per 32-byte group), then their scaling
+        int c[4][4];
+#pragma unroll
+        for (int gq = 0; gq < 4; gq++)
+          mma_u8s8(c[gq], a[gq][0], a[gq][1], a[gq][2], a[gq][3], b[m][gq].x, b[m][gq].y);
+#pragma unroll
+        for (int gq = 0; gq < 4; gq++) {
+          const float sx = __shfl_sync(0xffffffffu, tx, src_base + gq);
+          const float sy = __shfl_sync(0xffffffffu, ty, src_base + gq);
+          accA[m] = fmaf(a_lo ? sx : sy, __int2float_rn(a_lo ? c[gq][0] : c[gq][2]), accA[m]);
+          accB[m] = fmaf(b_lo ? sx : sy, __int2float_rn(b_lo ? c[gq][1] : c[gq][3]), accB[m]);
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(sbase + S.empty + st * 8);  // this warp is done with the stage
+    if (++st == (uint32_t)nstage) st = 0, fph ^= 1;
 
-    if (kt + 1 == L.ktiles) {  // chunk finished: leave the row partials, one warp sums them
-      const uint32_t slot = cidx % nslot;
+    if (++kt == L.ktiles) {  // chunk finished: leave the row partials, one warp sums them
+      kt = 0;
       float *red = reinterpret_cast<float *>(smem + S.red) + slot * (CW * M * 8);
 #pragma unroll
       for (int m = 0; m < M; m++) {
@@ -279,22 +370,10 @@ __global__ void __launch_bounds__(NT, 1)
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(sbase + S.redfull + slot * 8);
-      if (warp == cidx % CW) {
-        if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, (cidx / nslot) & 1)) {
-          *abort_flag = 1;
-          atomicOr(status, QK_DEV_TIMEOUT);
-        }
-        if (lane < 8 * M) {
-          const uint32_t m = lane >> 3, r = lane & 7u;
-          float v = 0.f;
-#pragma unroll
-          for (int wv = 0; wv < CW; wv++) v += red[(wv * M + m) * 8 + r];
-          const uint32_t row = (blockIdx.x + cidx * gridDim.x) * 8 + r;
-          if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
-        }
-      }
+      if (++slot == (uint32_t)nslot) slot = 0;
     }
   }
+  if (dead) atomicOr(status, QK_DEV_TIMEOUT);  // a bounded wait ran out: results are invalid
 }
 
 struct PlanMma {
@@ -311,12 +390,10 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   SmemMma S;
   uint32_t off = 0;
   S.full = off, off += MAX_STAGE * 8;
-  S.empty = off, off += MAX_STAGE * 8;
   S.redfull = off, off += MAX_SLOT * 8;
   S.xbar = off, off += 8;
-  S.flag = off, off += 8;
   off = (off + 127u) & ~127u;
-  S.red = off, off += MAX_SLOT * CW * m * 8 * 4;
+  S.red = off, off += MAX_SLOT * MAX_CW * m * 8 * 4;
   off = (off + 127u) & ~127u;
   S.PS = Kp + 64;
   S.xs_off = m * 3 * S.PS;
@@ -328,16 +405,20 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   if (off + 2 * stage_bytes > budget) return false;
   int nstage = (int)((budget - off) / stage_bytes);
   if (nstage > MAX_STAGE) nstage = MAX_STAGE;
+  if (const char *e = getenv("QK_NSTAGE")) { int v = atoi(e); if (v >= 2 && v < nstage) nstage = v; }
+  // a chunk's stages are refilled only once the whole chunk is reduced: its k-tiles
+  // must all fit in the ring with room to prefetch the next chunk
+  if ((uint32_t)nstage < L.ktiles + 1) return false;
   P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1;
   P->total = off + nstage * stage_bytes;
   return true;
 }
 
-template <int M>
+template <int M, bool INCTA, int CW>
 cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
                        unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
                        cudaStream_t s) {
-  auto kern = qk_gemv_q4k_mma_kernel<M>;
+  auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e =
@@ -354,21 +435,51 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
 
-  const uint32_t quads = (uint32_t)M * P.Kp / 4;
-  cudaLaunchConfig_t c0 = {};
-  c0.gridDim = dim3((quads + 255) / 256), c0.blockDim = dim3(256), c0.stream = s;
-  c0.attrs = at, c0.numAttrs = use_pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&c0, qk_xsplit_kernel, x, (uint32_t)M, L.cols, P.Kp, P.S.PS,
-                                     P.S.xs_off, ximg);
-  if (e != cudaSuccess) return e;
-
+  if (!INCTA) {
+    const uint32_t quads = (uint32_t)M * P.Kp / 4;
+    cudaLaunchConfig_t c0 = {};
+    c0.gridDim = dim3((quads + 255) / 256), c0.blockDim = dim3(256), c0.stream = s;
+    c0.attrs = at, c0.numAttrs = use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&c0, qk_xsplit_kernel, x, (uint32_t)M, L.cols, P.Kp,
+                                       P.S.PS, P.S.xs_off, ximg);
+    if (e != cudaSuccess) return e;
+  }
   uint32_t grid = (uint32_t)sm_count;  // persistent, one CTA per SM
   if (grid > L.chunks) grid = L.chunks;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NT), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1) * 32), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, (const unsigned char *)ximg, y, ldy, status, P.nstage,
-                            P.nslot, P.stage_bytes, P.S, P.Kp);
+  return cudaLaunchKernelEx(&cfg, kern, L, W, x, (const unsigned char *)ximg, y, ldy, status,
+                            P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp);
+}
+
+// Every CTA redoing the split costs ~M*K/512 quads per thread; past this size the
+// separate split kernel plus one bulk copy of its image is cheaper.
+bool split_in_cta(const PlanMma &P, uint32_t m) {
+  static int force = -2;
+  if (force == -2) {
+    const char *e = getenv("QK_XSPLIT");
+    force = e ? atoi(e) : -1;  // 0: always the split kernel, 1: always in-CTA
+  }
+  if (force >= 0) return force == 1;
+  return m * P.Kp <= 8192;
+}
+
+template <int M>
+cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, float *y,
+                         uint64_t ldy, unsigned *status, unsigned char *ximg, int sm_count,
+                         const PlanMma &P, cudaStream_t s) {
+  static int cw = -1;
+  if (cw < 0) {
+    const char *e = getenv("QK_CW");
+    cw = (e && atoi(e) == 16) ? 16 : 8;
+  }
+  if (cw == 16)
+    return split_in_cta(P, M)
+               ? launch_mma<M, true, 16>(L, W, x, y, ldy, status, ximg, sm_count, P, s)
+               : launch_mma<M, false, 16>(L, W, x, y, ldy, status, ximg, sm_count, P, s);
+  return split_in_cta(P, M) ? launch_mma<M, true, 8>(L, W, x, y, ldy, status, ximg, sm_count, P, s)
+                            : launch_mma<M, false, 8>(L, W, x, y, ldy, status, ximg, sm_count, P, s);
 }
 
 }  // namespace
@@ -391,12 +502,12 @@ cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const fl
   if (!make_plan_mma(L, m, &P)) return cudaErrorInvalidConfiguration;
   switch (m) {
     case 1:
-      return launch_mma<1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
     case 2:
-      return launch_mma<2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
     case 3:
-      return launch_mma<3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
     default:
-      return launch_mma<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
   }
 }

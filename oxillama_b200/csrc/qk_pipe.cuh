@@ -6,8 +6,6 @@
 
 namespace qkpipe {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 20;
-
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -37,11 +35,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false if the barrier never flipped.
+// Bounded wait: false if the barrier has not flipped after about a quarter of a
+// second (checked against the global nanosecond timer every 256 polls).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; i++)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 256; i++)
+      if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 > 250000000ull) return false;
+  }
 }
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // u8 x s8
   int d;
