@@ -180,7 +180,7 @@ def run_ours(args):
 
     def step():
         for i in range(RING):
-            dws[i].gemv(x, ys[i], stream=stream)
+            dws[i].gemv(x, ys[i])
             if world > 1:
                 dist.all_gather_into_tensor(gathered, ys[i])
 
@@ -191,10 +191,21 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     with torch.cuda.stream(stream):
-        for _ in range(max(3, args.warmup)):
+        for _ in range(max(3, args.warmup)):  # also the first-use setup of every kernel
             step()
         barrier()
         check_device_status(ctx, stream)
+        # One step is captured once into a CUDA graph and replayed: at ~10 us per matvec
+        # the host would otherwise be the bottleneck of a launch-bound loop.
+        graph = None
+        if world == 1 and not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+        run = graph.replay if graph is not None else step
+        for _ in range(3):
+            run()
+        barrier()
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
@@ -202,22 +213,25 @@ def run_ours(args):
         barrier()
         ev[0].record(stream)
         for _ in range(args.steps):
-            step()
+            run()
         ev[1].record(stream)
         barrier()
         ms = ev[0].elapsed_time(ev[1])
         check_device_status(ctx, stream)
 
         # kernel-only launch time for the roofline (no collective in the region)
-        barrier()
-        e2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        e2[0].record(stream)
-        for _ in range(args.steps):
-            for i in range(RING):
-                dws[i].gemv(x, ys[i], stream=stream)
-        e2[1].record(stream)
-        torch.cuda.synchronize()
-        kernel_ms = e2[0].elapsed_time(e2[1]) / (args.steps * RING)
+        if world == 1:
+            kernel_ms = ms / (args.steps * RING)
+        else:
+            barrier()
+            e2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            e2[0].record(stream)
+            for _ in range(args.steps):
+                for i in range(RING):
+                    dws[i].gemv(x, ys[i])
+            e2[1].record(stream)
+            torch.cuda.synchronize()
+            kernel_ms = e2[0].elapsed_time(e2[1]) / (args.steps * RING)
 
     # ---- end to end through the reference-facing host-pointer call
     kern = CudaQuantKernel(QTYPE, ctx)
@@ -253,6 +267,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": RING * COLS * 4, "d2h_bytes_per_step": RING * ROWS * 4,
                     "note": "qk_gemv host-pointer call per matvec; weights cached on device after first use"},
             "gpu_launches": RING * args.steps,
+            "cuda_graph": graph is not None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "traffic": None, "algorithmic_bytes_per_launch": algo_bytes,
                          "us_per_launch": kernel_ms * 1e3},
@@ -272,6 +287,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-graph", action="store_true", help="launch every matvec from the host")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

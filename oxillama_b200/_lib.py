@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libqk_cuda.so")
+LIB_PATH = os.environ.get("QK_CUDA_LIB") or os.path.join(_HERE, "libqk_cuda.so")
 
 u8p = C.POINTER(C.c_uint8)
 f32p = C.POINTER(C.c_float)

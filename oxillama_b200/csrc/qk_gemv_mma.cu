@@ -9,13 +9,18 @@
 // computes plain row dot products, eight weight rows at a time.
 //
 //   A (16 x 32, u8): rows 0-7  = the eight weight rows, low nibbles of one
-//                                32-byte group  (sub-block 2p,   weights q)
-//                    rows 8-15 = same rows, high nibbles kept in place
-//                                               (sub-block 2p+1, weights 16 q)
-//   B (32 x 8,  s8): cols 0-2 = the three base-254 digits of the activations
-//                               of sub-block 2p, cols 3-5 = those of 2p+1
-//   C (16 x 8, s32): C[r][0..2] and C[8+r][3..5] are the integer dots wanted;
-//                    the cross terms are ignored.
+//                                32-byte group            (sub-block 2p: q)
+//                    rows 8-15 = same rows, the raw bytes (q_lo + 16 q_hi)
+//   B (32 x 8,  s8): even column 2j = digit j of the activations of sub-block 2p,
+//                    odd column 2j+1 = digit j of those of sub-block 2p+1 (j = 0..2;
+//                    columns 6, 7 unused)
+//   C (16 x 8, s32): C[r][2j]     = sum q_lo D_j(2p)              wanted
+//                    C[r][2j+1]   = sum q_lo D_j(2p+1)            cross term
+//                    C[8+r][2j+1] = sum (q_lo + 16 q_hi) D_j(2p+1)
+//                    so 16 * (high-nibble dot) = C[8+r][2j+1] - C[r][2j+1]: the cross
+//                    term pays for not masking the high nibbles.  Every lane of an
+//                    MMA quad then owns digit j = lane % 4 of both sub-blocks in
+//                    fixed registers (no per-lane selects).
 //
 // Activations are split per 32-column block as x ~= sx (D0 + D1/254 + D2/254^2)
 // with |D| <= 127 (error <= amax * 6.1e-8), so the integer dots are exact and
@@ -48,6 +53,24 @@
 
 using namespace qkpipe;
 
+#ifdef QK_TRACE
+// Developer build only: block 0 timestamps its pipeline into a global buffer.
+__device__ unsigned long long *qk_trace_buf = nullptr;
+#define QK_STAMP(cond, idx)                                                        \
+  do {                                                                             \
+    if ((cond) && qk_trace_buf && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {    \
+      unsigned long long t__;                                                      \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                     \
+      qk_trace_buf[idx] = t__;                                                     \
+    }                                                                              \
+  } while (0)
+extern "C" void qk_trace_set(unsigned long long *p) {
+  cudaMemcpyToSymbol(qk_trace_buf, &p, sizeof(p));
+}
+#else
+#define QK_STAMP(cond, idx) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int MAX_CW = 16;                      // compute warps: 8 or 16 (+ one producer warp)
@@ -73,7 +96,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(  // a pure function of its operands: left free for the scheduler to interleave
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%10,%11,%12,%13};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
@@ -183,12 +206,24 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
   }
 }
 
-template <int M, bool INCTA, int CW>
+// One super-block column of a tile as a compute warp holds it in registers:
+// row g's 16-byte header, the lane's 8 bytes of each of the four 32-byte groups,
+// and per activation row the (sx, Sx) pairs and digit fragments that meet them.
+template <int M>
+struct SbData {
+  uint4 h;
+  uint2 w[4];
+  float4 xs[M];
+  uint2 b[M][4];
+};
+
+template <int M, bool INCTA, int CW, int G>
 __global__ void __launch_bounds__((CW + 1) * 32, 1)
     qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
                            uint64_t ldy, unsigned *status, int nstage, int nslot,
                            uint32_t stage_bytes, SmemMma S, uint32_t Kp) {
+  constexpr int WG = CW / G;  // warps per group; a group owns every G-th chunk
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -197,12 +232,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const uint32_t my_items = my_chunks * L.ktiles;
 
+  QK_STAMP(warp == 0, 0);
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < nstage; s++) {
-      mbar_init(sbase + S.full + s * 8, 1);
-          }
-    for (int s = 0; s < nslot; s++) mbar_init(sbase + S.redfull + s * 8, CW);
+    for (int s = 0; s < nstage; s++) mbar_init(sbase + S.full + s * 8, 1);
+    for (int s = 0; s < nslot; s++) mbar_init(sbase + S.redfull + s * 8, WG);
     mbar_init(sbase + S.xbar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -232,6 +266,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       for (; item < (uint32_t)nstage && item < my_items; item++) issue();
     }
     pdl_wait();  // the x image and y belong to the previous kernel until it has finished
+    QK_STAMP(true, 120);
     if (!INCTA && lane == 0) {
       mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
       bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
@@ -242,18 +277,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
         break;
       }
-      const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (CW * M * 8);
+      const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (WG * M * 8);
       if (lane < 8 * M) {
         const uint32_t m = lane >> 3, r = lane & 7u;
         float v = 0.f;
 #pragma unroll
-        for (int wv = 0; wv < CW; wv++) v += red[(wv * M + m) * 8 + r];
+        for (int wv = 0; wv < WG; wv++) v += red[(wv * M + m) * 8 + r];
         const uint32_t row = (blockIdx.x + c * gridDim.x) * 8 + r;
         if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
       }
       __syncwarp();
+      QK_STAMP(c < 30, 64 + c);
       if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
-      // every compute warp released the chunk's stages before it posted its partials
+      // every warp of the owning group released the chunk's stages before it posted
+      // its partials
       if (lane == 0)
         for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
     }
@@ -261,16 +298,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   }
 
   // ================= compute warps =================
+  const uint32_t group = warp / WG, wl = warp % WG;
   const uint32_t g = lane >> 2, tig = lane & 3;
-  // lane-constant routing of the useful C entries (see the header comment); the
-  // x16 of the high-nibble rows is folded into the sub-block scale.  Lanes with
-  // tig == 3 hold only cross terms and the two unused B columns: weight 0.
-  const float kA = tig == 0 ? 1.f : tig == 1 ? 1.f / (254.f * 254.f) : tig == 2 ? 1.f / 254.f : 0.f;
-  const float kB = tig == 0 ? 1.f / 254.f : tig == 1 ? 1.f : tig == 2 ? 1.f / (254.f * 254.f) : 0.f;
-  const bool a_lo = tig < 2, b_lo = tig == 0;
-  // B column g of this lane: digit g % 3 of sub-block 2p (g < 3) or 2p + 1 (g >= 3);
-  // columns 6 and 7 are never read back, so they may hold anything
-  const uint32_t b_off = (g % 3) * S.PS + (g >= 3 ? 32u : 0u) + tig * 8;
+  // lane (g, tig) owns digit j = tig of both sub-blocks of a group (see the header
+  // comment); tig == 3 holds the two unused columns: weight 0.  The x16 of the
+  // high-nibble dot is folded into the sub-block scale.
+  const float kD = tig == 0 ? 1.f : tig == 1 ? 1.f / 254.f : tig == 2 ? 1.f / (254.f * 254.f) : 0.f;
+  // B column g of this lane: digit g / 2 of sub-block 2p (g even) or 2p + 1 (g odd);
+  // columns 6 and 7 are never used, so they may hold anything (digit plane 2 again)
+  const uint32_t b_off = (g < 6 ? (g >> 1) : 2u) * S.PS + (g & 1u) * 32u + tig * 8;
   const uint32_t src_base = lane & ~3u;
   // header decode constants of this lane (it unpacks sub-blocks 2 tig and 2 tig + 1)
   const bool hi_half = tig >= 2;
@@ -278,6 +314,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   const uint32_t sel0 = 0x7540u | (2u * (tig & 1u)), sel1 = sel0 + 1u;
 
   pdl_wait();  // x may be the previous kernel's output; y may be read or written by it
+  QK_STAMP(warp == 0, 121);
   bool dead = false;
   if (INCTA) {
     xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off);
@@ -290,96 +327,119 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 #pragma unroll
   for (int m = 0; m < M; m++) accA[m] = accB[m] = mt[m] = 0.f;
 
-  // loop state kept as counters: no integer division on the critical path
-  uint32_t st = 0, fph = 0, kt = 0, slot = 0;
-  for (uint32_t item = 0; item < my_items && !dead; item++) {
-    const uint32_t nbt = qk_tile_nb(L, kt);
-    const uint32_t tile = sbase + S.stage + st * stage_bytes;
-    if (!mbar_wait_bounded(sbase + S.full + st * 8, fph)) {
-      dead = true;
-      break;
+  // every shared-memory load of one super-block column, issued together
+  auto load_sb = [&](SbData<M> &D, uint32_t tile, uint32_t nbt, uint32_t kt, uint32_t sb) {
+    const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
+    D.h = lds128(tile + (g * nbt + sb) * 16);
+    const uint32_t qa = tile + QK_TILE_ROWS * nbt * 16 + sb * 1024 + g * 32 + tig * 8;
+#pragma unroll
+    for (int gq = 0; gq < 4; gq++) D.w[gq] = lds64(qa + gq * 256);
+    const uint32_t xb = sbase + S.ximg + sub * 32 + b_off;
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+      D.xs[m] = lds128f(sbase + S.ximg + S.xs_off + (m * (Kp / 32) + sub + 2 * tig) * 8);
+#pragma unroll
+      for (int gq = 0; gq < 4; gq++) D.b[m][gq] = lds64(xb + m * 3 * S.PS + gq * 64);
     }
+  };
+  auto compute_sb = [&](const SbData<M> &D) {
+    // this lane decodes sub-blocks (2 tig, 2 tig + 1) of row g's header:
+    // reference/q4_k.rs:27-49 on four 6-bit fields at a time, then byte -> f32 by
+    // dropping the byte into the mantissa of 2^23
+    const uint4 h = D.h;
+    const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
+    const uint32_t scw = ((hi_half ? h.w : h.y) & m1) | ((h.y >> 2) & m2);
+    const uint32_t mnw = ((hi_half ? (h.w >> 4) : h.z) & m1) | ((h.z >> 2) & m2);
+    const float ds0 = d * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel0)) - 8388608.f);
+    const float ds1 =
+        d * (1.f / 16.f) * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel1)) - 8388608.f);
+    const float dm0 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel0)) - 8388608.f);
+    const float dm1 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel1)) - 8388608.f);
 #pragma unroll
-    for (uint32_t sbi = 0; sbi < NBT / CW; sbi++) {
-      const uint32_t sb = warp + sbi * CW;
-      if (sb >= nbt) break;
-      const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
-      // ---- every shared-memory load of this super-block column is issued up front
-      const uint4 h = lds128(tile + (g * nbt + sb) * 16);
-      const uint32_t qa = tile + QK_TILE_ROWS * nbt * 16 + sb * 1024 + g * 32 + tig * 8;
-      uint2 w[4];
+    for (int m = 0; m < M; m++) {
+      const float tx = ds0 * D.xs[m].x, ty = ds1 * D.xs[m].z;
+      mt[m] = fmaf(dm0, D.xs[m].y, mt[m]);
+      mt[m] = fmaf(dm1, D.xs[m].w, mt[m]);
+      // four MMAs back to back (one per 32-byte group), then their scaling
+      int c[4][4];
 #pragma unroll
-      for (int gq = 0; gq < 4; gq++) w[gq] = lds64(qa + gq * 256);
-      float4 xs[M];
-      uint2 b[M][4];
-      const uint32_t xb = sbase + S.ximg + sub * 32 + b_off;
-#pragma unroll
-      for (int m = 0; m < M; m++) {
-        xs[m] = lds128f(sbase + S.ximg + S.xs_off + (m * (Kp / 32) + sub + 2 * tig) * 8);
-#pragma unroll
-        for (int gq = 0; gq < 4; gq++) b[m][gq] = lds64(xb + m * 3 * S.PS + gq * 64);
-      }
-      // ---- this lane decodes sub-blocks (2 tig, 2 tig + 1) of row g's header:
-      // reference/q4_k.rs:27-49 on four 6-bit fields at a time, then byte -> f32 by
-      // dropping the byte into the mantissa of 2^23
-      const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
-      const uint32_t scw = ((hi_half ? h.w : h.y) & m1) | ((h.y >> 2) & m2);
-      const uint32_t mnw = ((hi_half ? (h.w >> 4) : h.z) & m1) | ((h.z >> 2) & m2);
-      const float ds0 = d * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel0)) - 8388608.f);
-      const float ds1 =
-          d * (1.f / 16.f) * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel1)) - 8388608.f);
-      const float dm0 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel0)) - 8388608.f);
-      const float dm1 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel1)) - 8388608.f);
-      uint32_t a[4][4];
+      for (int gq = 0; gq < 4; gq++)
+        mma_u8s8(c[gq], D.w[gq].x & 0x0F0F0F0Fu, D.w[gq].x, D.w[gq].y & 0x0F0F0F0Fu, D.w[gq].y,
+                 D.b[m][gq].x, D.b[m][gq].y);
 #pragma unroll
       for (int gq = 0; gq < 4; gq++) {
-        a[gq][0] = w[gq].x & 0x0F0F0F0Fu, a[gq][1] = w[gq].x & 0xF0F0F0F0u;
-        a[gq][2] = w[gq].y & 0x0F0F0F0Fu, a[gq][3] = w[gq].y & 0xF0F0F0F0u;
+        const float sx = __shfl_sync(0xffffffffu, tx, src_base + gq);
+        const float sy = __shfl_sync(0xffffffffu, ty, src_base + gq);
+        accA[m] = fmaf(sx, __int2float_rn(c[gq][0]), accA[m]);
+        accB[m] = fmaf(sy, __int2float_rn(c[gq][3] - c[gq][1]), accB[m]);
       }
+    }
+  };
+
+  QK_STAMP(warp == 0, 1);
+  // loop state kept as counters: no integer division on the critical path
+  uint32_t st = 0, fph = 0, slot = 0;
+  auto advance_stage = [&](uint32_t n) {
+    st += n;
+    while (st >= (uint32_t)nstage) st -= nstage, fph ^= 1;
+  };
+  advance_stage(group * L.ktiles);
+  slot = group % nslot;
+  uint32_t tstamp = 0;
+  for (uint32_t c = group; c < my_chunks && !dead; c += G) {
+    for (uint32_t kt = 0; kt < L.ktiles; kt++) {
+      const uint32_t nbt = qk_tile_nb(L, kt);
+      const uint32_t tile = sbase + S.stage + st * stage_bytes;
+      if (!mbar_wait_bounded(sbase + S.full + st * 8, fph)) {
+        dead = true;
+        break;
+      }
+      QK_STAMP(warp == 0 && tstamp < 30, 2 + 2 * tstamp);
+      // software pipeline over this warp's columns (fully unrolled, two register
+      // buffers): the next column's loads are in flight while the current one is
+      // decoded, multiplied and scaled
+      {
+        constexpr int NSB = NBT / WG;  // columns of a full tile per warp
+        SbData<M> d0, d1;
+        if (wl < nbt) load_sb(d0, tile, nbt, kt, wl);
 #pragma unroll
-      for (int m = 0; m < M; m++) {
-        const float tx = ds0 * xs[m].x, ty = ds1 * xs[m].z;
-        mt[m] = fmaf(dm0, xs[m].y, mt[m]);
-        mt[m] = fmaf(dm1, xs[m].w, mt[m]);
-        // ---- four MMAs back to back (one per 32-byte group), then their scaling
-        int c[4][4];
-#pragma unroll
-        for (int gq = 0; gq < 4; gq++)
-          mma_u8s8(c[gq], a[gq][0], a[gq][1], a[gq][2], a[gq][3], b[m][gq].x, b[m][gq].y);
-#pragma unroll
-        for (int gq = 0; gq < 4; gq++) {
-          const float sx = __shfl_sync(0xffffffffu, tx, src_base + gq);
-          const float sy = __shfl_sync(0xffffffffu, ty, src_base + gq);
-          accA[m] = fmaf(a_lo ? sx : sy, __int2float_rn(a_lo ? c[gq][0] : c[gq][2]), accA[m]);
-          accB[m] = fmaf(b_lo ? sx : sy, __int2float_rn(b_lo ? c[gq][1] : c[gq][3]), accB[m]);
+        for (int j = 0; j < NSB; j += 2) {
+          const uint32_t sb0 = wl + j * WG, sb1 = sb0 + WG, sb2 = sb1 + WG;
+          if (NSB > 1 && sb1 < nbt) load_sb(d1, tile, nbt, kt, sb1);
+          if (sb0 < nbt) compute_sb(d0);
+          if (j + 2 < NSB && sb2 < nbt) load_sb(d0, tile, nbt, kt, sb2);
+          if (NSB > 1 && sb1 < nbt) compute_sb(d1);
         }
       }
+      QK_STAMP(warp == 0 && tstamp < 30, 3 + 2 * tstamp);
+      tstamp++;
+      advance_stage(1);
     }
-    if (++st == (uint32_t)nstage) st = 0, fph ^= 1;
-
-    if (++kt == L.ktiles) {  // chunk finished: leave the row partials, one warp sums them
-      kt = 0;
-      float *red = reinterpret_cast<float *>(smem + S.red) + slot * (CW * M * 8);
+    if (dead) break;
+    // chunk finished: leave the row partials for the reducer
+    float *red = reinterpret_cast<float *>(smem + S.red) + slot * (WG * M * 8);
 #pragma unroll
-      for (int m = 0; m < M; m++) {
-        float v = fmaf(kA, accA[m], kB * accB[m]) - mt[m];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        if (tig == 0) red[(warp * M + m) * 8 + g] = v;
-        accA[m] = accB[m] = mt[m] = 0.f;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sbase + S.redfull + slot * 8);
-      if (++slot == (uint32_t)nslot) slot = 0;
+    for (int m = 0; m < M; m++) {
+      float v = kD * (accA[m] + accB[m]) - mt[m];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      if (tig == 0) red[(wl * M + m) * 8 + g] = v;
+      accA[m] = accB[m] = mt[m] = 0.f;
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sbase + S.redfull + slot * 8);
+    slot += G;
+    while (slot >= (uint32_t)nslot) slot -= nslot;
+    advance_stage((G - 1) * L.ktiles);
   }
   if (dead) atomicOr(status, QK_DEV_TIMEOUT);  // a bounded wait ran out: results are invalid
+  QK_STAMP(warp == 0, 100);
 }
 
 struct PlanMma {
   SmemMma S;
   uint32_t Kp, stage_bytes, total;
-  int nstage, nslot;
+  int nstage, nslot, groups;
 };
 
 bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
@@ -405,20 +465,35 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   if (off + 2 * stage_bytes > budget) return false;
   int nstage = (int)((budget - off) / stage_bytes);
   if (nstage > MAX_STAGE) nstage = MAX_STAGE;
-  if (const char *e = getenv("QK_NSTAGE")) { int v = atoi(e); if (v >= 2 && v < nstage) nstage = v; }
+  if (const char *e = getenv("QK_NSTAGE")) {  // developer knob: shallower ring
+    int v = atoi(e);
+    if (v >= 2 && v < nstage) nstage = v;
+  }
   // a chunk's stages are refilled only once the whole chunk is reduced: its k-tiles
   // must all fit in the ring with room to prefetch the next chunk
   if ((uint32_t)nstage < L.ktiles + 1) return false;
-  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1;
+  // largest group count whose G * ktiles divides a ring depth we can afford
+  int groups = 1;
+  const char *ge = getenv("QK_GROUPS");
+  const int gmax = ge ? atoi(ge) : 4;
+  for (int gtry = 4; gtry >= 2; gtry >>= 1) {
+    const int unit = gtry * (int)L.ktiles;
+    if (gtry <= gmax && nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1) {
+      groups = gtry;
+      nstage = (nstage / unit) * unit;
+      break;
+    }
+  }
+  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1, P->groups = groups;
   P->total = off + nstage * stage_bytes;
   return true;
 }
 
-template <int M, bool INCTA, int CW>
+template <int M, bool INCTA, int CW, int G>
 cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
                        unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
                        cudaStream_t s) {
-  auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW>;
+  auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW, G>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e =
@@ -469,17 +544,37 @@ template <int M>
 cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, float *y,
                          uint64_t ldy, unsigned *status, unsigned char *ximg, int sm_count,
                          const PlanMma &P, cudaStream_t s) {
+  // Warp groups: a group owns every G-th chunk.  A stage must always be consumed by
+  // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
+  // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
   static int cw = -1;
   if (cw < 0) {
     const char *e = getenv("QK_CW");
-    cw = (e && atoi(e) == 16) ? 16 : 8;
+    cw = (e && atoi(e) == 8) ? 8 : 16;
   }
-  if (cw == 16)
-    return split_in_cta(P, M)
-               ? launch_mma<M, true, 16>(L, W, x, y, ldy, status, ximg, sm_count, P, s)
-               : launch_mma<M, false, 16>(L, W, x, y, ldy, status, ximg, sm_count, P, s);
-  return split_in_cta(P, M) ? launch_mma<M, true, 8>(L, W, x, y, ldy, status, ximg, sm_count, P, s)
-                            : launch_mma<M, false, 8>(L, W, x, y, ldy, status, ximg, sm_count, P, s);
+#define QK_LAUNCH(CWV, GV)                                                                       \
+  return split_in_cta(P, M)                                                                      \
+             ? launch_mma<M, true, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s)       \
+             : launch_mma<M, false, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s)
+  if (cw == 8) {
+    switch (P.groups) {
+      case 4:
+        QK_LAUNCH(8, 4);
+      case 2:
+        QK_LAUNCH(8, 2);
+      default:
+        QK_LAUNCH(8, 1);
+    }
+  }
+  switch (P.groups) {
+    case 4:
+      QK_LAUNCH(16, 4);
+    case 2:
+      QK_LAUNCH(16, 2);
+    default:
+      QK_LAUNCH(16, 1);
+  }
+#undef QK_LAUNCH
 }
 
 }  // namespace
