@@ -40,6 +40,9 @@ ROWS, COLS, QTYPE = 14336, 4096, S.Q4_K
 RING = 16
 METRIC = "q4_k_gemv_weight_bandwidth"
 UNIT = "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the
+# ncu capture summarised in profiles/q4k_gemv_14336x4096_m1_ncu.md
+DRAM_BYTES_PER_LAUNCH = 33082112
 WORKLOAD = "config[1]: Q4_K 14336x4096 matvec, M=1, f32 N(0,1) activations, seed 0"
 
 
@@ -269,7 +272,7 @@ def run_ours(args):
             "gpu_launches": RING * args.steps,
             "cuda_graph": graph is not None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": which, "traffic": None, "algorithmic_bytes_per_launch": algo_bytes,
+                         "peak_source": which, "traffic": DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": algo_bytes,
                          "us_per_launch": kernel_ms * 1e3},
             "clocks": clocks,
         }
@@ -283,7 +286,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
