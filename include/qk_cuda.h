@@ -124,7 +124,7 @@ int qk_weights_free(qk_ctx *ctx, qk_weights *h);
 int qk_weights_info(const qk_weights *h, int *type, size_t *rows, size_t *cols, size_t *bytes);
 
 /* y_dev[0..rows) = W_shard x_dev.  Device pointers; enqueued on `stream`
- * (a cudaStream_t, NULL = the context's own stream); returns without waiting. */
+ * (a cudaStream_t; NULL is the legacy default stream); returns without waiting. */
 int qk_gemv_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_dev, void *stream);
 
 /* y_dev[i*ldy + j] = dot(W_shard row j, x_dev row i), i < m, j < rows.  x_dev is
@@ -142,6 +142,18 @@ int qk_matvec_q8_fused_dev(qk_ctx *ctx, const qk_weights *h, const uint8_t *acts
 
 /* Q8_0 activation encoder on device memory; n a multiple of 32. */
 int qk_quantize_q8_0_dev(qk_ctx *ctx, const float *x_dev, size_t n, uint8_t *out_dev, void *stream);
+
+/* No counterpart in the reference.  qk_gemm_dev for Q4_K shards and m <= 4 that
+ * allocates nothing: for callers that cannot allocate device memory once running
+ * (a server that handed all of HBM to its own pools, a process under a fixed
+ * memory budget, a loop that must not take the allocator lock).  Its scratch is
+ * a 96 KiB array built into the library (held on every GPU that loads it), so
+ * the split activations of a call (about 3.1 bytes per activation) must fit
+ * 96 KiB, else QK_INVALID_ARGUMENT.
+ * The first call on a device resolves the array's address: make it before any
+ * stream capture.  Calls on one device share the array; overlapping calls race. */
+int qk_gemm_dev_noalloc(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_dev,
+                        size_t m, size_t ldy, void *stream);
 
 /* Reads and clears the device-side status word of the context (bounded waits
  * that ran out, range checks that tripped).  Synchronises `stream`. */

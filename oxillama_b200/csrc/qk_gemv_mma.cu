@@ -606,3 +606,32 @@ cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const fl
       return launch_mma_m<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
   }
 }
+
+// Same matvec, always through qk_xsplit_kernel + the x image in `scratch` (never the
+// in-CTA split), for callers that hand in their own scratch.
+cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, const float *x,
+                                     float *y, uint32_t m, uint64_t ldy, unsigned *status,
+                                     unsigned char *scratch, int sm_count, cudaStream_t s) {
+  PlanMma P;
+  if (!make_plan_mma(L, m, &P)) return cudaErrorInvalidConfiguration;
+#define QK_SPLIT(MV)                                                                             \
+  switch (P.groups) {                                                                            \
+    case 4:                                                                                      \
+      return launch_mma<MV, false, 16, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+    case 2:                                                                                      \
+      return launch_mma<MV, false, 16, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+    default:                                                                                     \
+      return launch_mma<MV, false, 16, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+  }
+  switch (m) {
+    case 1:
+      QK_SPLIT(1)
+    case 2:
+      QK_SPLIT(2)
+    case 3:
+      QK_SPLIT(3)
+    default:
+      QK_SPLIT(4)
+  }
+#undef QK_SPLIT
+}

@@ -1,0 +1,38 @@
+// Definitions shared by the translation units that implement the C ABI.
+#pragma once
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "../../include/qk_cuda.h"
+#include "qk_kernels.h"
+
+struct qk_weights {
+  QkLayout L;
+  uint8_t *dev;
+  int device;
+  size_t algo_bytes;
+};
+
+struct qk_ctx {
+  int device;
+  int sm_count;
+  cudaStream_t stream;
+  unsigned *status_dev;
+  // device scratch of the *_dev entry points (split activations); grown on demand,
+  // which synchronises: size it once before capturing into a CUDA graph
+  unsigned char *scratch = nullptr;
+  size_t scratch_cap = 0;
+  std::string err;
+  std::mutex mu;
+  // scratch for the host-pointer entry points
+  void *sa = nullptr, *sb = nullptr;
+  size_t sa_cap = 0, sb_cap = 0;
+  // weight cache for the host-pointer entry points
+  typedef std::tuple<const void *, size_t, int, size_t, size_t, uint64_t> Key;
+  std::map<Key, qk_weights *> cache;
+  size_t cache_bytes = 0, cache_cap = (size_t)64 << 30;
+  bool force_simple = false;
+};
+

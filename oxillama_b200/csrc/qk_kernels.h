@@ -29,6 +29,9 @@ size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                                int sm_count, cudaStream_t s);
+cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, const float *x,
+                                     float *y, uint32_t m, uint64_t ldy, unsigned *status,
+                                     unsigned char *scratch, int sm_count, cudaStream_t s);
 size_t qk_gemv_fast_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                 uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
