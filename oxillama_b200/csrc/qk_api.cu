@@ -292,17 +292,27 @@ static int gemm_dispatch(qk_ctx *c, const qk_weights *h, const float *x, float *
     CK(c, cudaMemset2DAsync(y, ldy * sizeof(float), 0, h->L.rows * sizeof(float), m, s));
     return QK_OK;
   }
+  auto ensure_scratch = [&](size_t need) -> int {
+    if (need <= c->scratch_cap) return QK_OK;
+    CK(c, cudaDeviceSynchronize());
+    cudaFree(c->scratch);
+    c->scratch = nullptr, c->scratch_cap = 0;
+    CK(c, cudaMalloc(&c->scratch, need * 2));
+    c->scratch_cap = need * 2;
+    return QK_OK;
+  };
   if (!c->force_simple && m <= QK_GEMV_MAX_M && qk_gemv_fast_supported(h->L, (uint32_t)m)) {
-    size_t need = qk_gemv_fast_scratch_bytes(h->L, (uint32_t)m);
-    if (need > c->scratch_cap) {
-      CK(c, cudaDeviceSynchronize());
-      cudaFree(c->scratch);
-      c->scratch = nullptr, c->scratch_cap = 0;
-      CK(c, cudaMalloc(&c->scratch, need * 2));
-      c->scratch_cap = need * 2;
-    }
+    int st = ensure_scratch(qk_gemv_fast_scratch_bytes(h->L, (uint32_t)m));
+    if (st) return st;
     CK(c, qk_launch_gemv_fast(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->scratch,
                               c->sm_count, s));
+    return QK_OK;
+  }
+  if (!c->force_simple && m < (1u << 30) && qk_gemm_tc_supported(h->L, (uint32_t)m)) {
+    int st = ensure_scratch(qk_gemm_tc_scratch_bytes(h->L, (uint32_t)m));
+    if (st) return st;
+    CK(c, qk_launch_gemm_tc(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->scratch,
+                            c->sm_count, s));
     return QK_OK;
   }
   CK(c, qk_launch_gemm_simple(h->L, h->dev, x, y, (uint32_t)m, ldy, s));

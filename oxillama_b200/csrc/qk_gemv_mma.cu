@@ -330,8 +330,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   // every shared-memory load of one super-block column, issued together
   auto load_sb = [&](SbData<M> &D, uint32_t tile, uint32_t nbt, uint32_t kt, uint32_t sb) {
     const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
-    D.h = lds128(tile + (g * nbt + sb) * 16);
-    const uint32_t qa = tile + QK_TILE_ROWS * nbt * 16 + sb * 1024 + g * 32 + tig * 8;
+    // block-major tile: super-block column sb = 1152 bytes, 8 headers then 4 x 8 x 32 nibbles
+    D.h = lds128(tile + sb * 1152 + g * 16);
+    const uint32_t qa = tile + sb * 1152 + 128 + g * 32 + tig * 8;
 #pragma unroll
     for (int gq = 0; gq < 4; gq++) D.w[gq] = lds64(qa + gq * 256);
     const uint32_t xb = sbase + S.ximg + sub * 32 + b_off;

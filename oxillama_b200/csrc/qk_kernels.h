@@ -36,3 +36,11 @@ size_t qk_gemv_fast_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                 uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                                 int sm_count, cudaStream_t s);
+
+// Q4_K batched matmul on tcgen05 / TMEM (any m; used for m > QK_GEMV_MAX_M).  `scratch`
+// holds the fp16 copy of the activations: qk_gemm_tc_scratch_bytes(L, m) bytes.
+bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m);
+size_t qk_gemm_tc_scratch_bytes(const QkLayout &L, uint32_t m);
+cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
+                              uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
+                              int sm_count, cudaStream_t s);

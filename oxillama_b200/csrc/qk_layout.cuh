@@ -13,7 +13,7 @@
 //
 //     Q4_0   plane0 nibbles 16 B | plane1 d 2 B
 //     Q8_0   plane0 int8s   32 B | plane1 d 2 B
-//     Q4_K   plane0 d,dmin,scales 16 B | plane1 nibbles 128 B, interleaved by 32
+//     Q4_K   block-major: per block  d,dmin,scales 16 B x 8 rows | nibbles, 4 groups x 8 rows x 32 B
 //     Q6_K   plane0 ql+qh  192 B | plane1 scales 16 B | plane2 d 2 B
 //     IQ4_XS plane0 nibbles 128 B | plane1 d,scales_h,scales_l 8 B
 //
@@ -21,7 +21,10 @@
 //   with granule g: [nbt blocks][width/g granules][8 rows][g bytes].  The
 //   interleaved form puts the same 32-byte group of all 8 rows side by side,
 //   which is exactly one tensor-core B/A fragment row per lane group and reads
-//   from shared memory without bank conflicts.
+//   from shared memory without bank conflicts.  A block-major tile (Q4_K) keeps
+//   all interleaved planes of one block together, [nbt blocks][planes...]: the
+//   8 x 144 = 1152 bytes of one super-block column are then one contiguous span,
+//   which is what the prefill kernel copies per 256-column step.
 //
 // Every plane of every tile starts on a 16-byte boundary for any K and any row
 // count (8 * nbt * width is a multiple of 16 for all widths above), and one
@@ -52,6 +55,7 @@ struct QkLayout {
   uint32_t pw[3];        // plane widths, bytes per block
   uint32_t po[3];        // offset of the plane's field inside the GGUF block
   uint32_t pg[3];        // 0: row-major plane; g > 0: interleaved with granule g bytes
+  uint32_t bm;           // 1: block-major tile (every plane interleaved, planes of a block adjacent)
   uint32_t rows, cols;   // logical shape of this shard
   uint32_t chunks;       // ceil(rows / 8)
   uint64_t chunk_bytes;  // 8 * nb * bb
@@ -73,7 +77,8 @@ static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayo
       break;
     case QK_T_Q4_K:
       l.bs = 256; l.bb = 144; l.nplanes = 2;
-      l.pw[0] = 16; l.po[0] = 0; l.pw[1] = 128; l.po[1] = 16; l.pg[1] = 32;
+      l.pw[0] = 16; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 128; l.po[1] = 16; l.pg[1] = 32;
+      l.bm = 1;
       break;
     case QK_T_Q6_K:
       l.bs = 256; l.bb = 210; l.nplanes = 3;
@@ -126,8 +131,15 @@ __host__ __device__ static inline uint64_t qk_byte_offset(const QkLayout &L, uin
   uint32_t chunk = row / QK_TILE_ROWS, r = row % QK_TILE_ROWS;
   uint32_t kt = blk / L.nbt, b = blk % L.nbt;
   uint32_t nbt_this = qk_tile_nb(L, kt);
-  uint64_t base = qk_tile_offset(L, chunk, kt) + qk_plane_offset(L, nbt_this, p);
   uint32_t g = L.pg[p];
+  if (L.bm) {  // [block][plane][granule][row][g bytes]
+    uint32_t before = 0;
+    for (int i = 0; i < p; i++) before += L.pw[i];
+    return qk_tile_offset(L, chunk, kt) + (uint64_t)b * QK_TILE_ROWS * L.bb +
+           (uint64_t)QK_TILE_ROWS * before + (uint64_t)(o / g) * QK_TILE_ROWS * g + (uint64_t)r * g +
+           (o % g);
+  }
+  uint64_t base = qk_tile_offset(L, chunk, kt) + qk_plane_offset(L, nbt_this, p);
   if (g == 0) return base + (uint64_t)(r * nbt_this + b) * L.pw[p] + o;
   return base + (uint64_t)b * QK_TILE_ROWS * L.pw[p] + (uint64_t)(o / g) * QK_TILE_ROWS * g +
          (uint64_t)r * g + (o % g);

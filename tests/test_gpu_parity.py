@@ -92,7 +92,9 @@ def test_gemm_matches_oracle(K, disp, t, m):
     disp.get_kernel(t).gemm(K.QuantTensor(w, (rows, cols), t), x, y, m, rows, cols)
     st, ref = O.gemm(t, w, x, m, rows, cols)
     assert st == 0
-    tol = TOL_F32 if m <= 2 else 1e-4  # two-digit activations for m = 3, 4
+    # m <= 2: three-digit activations; m = 3, 4: two digits; larger m may take the fp16
+    # tensor-core path (operands rounded to fp16): the path's stated 1e-3
+    tol = TOL_F32 if m <= 2 else (1e-4 if m <= 4 else TOL)
     assert rel_inf(y, ref) <= tol, rel_inf(y, ref)
 
 
@@ -297,9 +299,14 @@ def _check_config(K, disp, t, rows, cols, m, seed, tol, row_cap=None):
     err = rel_inf(y[:, :rc], ref)
     assert err <= tol, err
     assert np.all(np.isfinite(y))
-    # linearity, at full size: W(2x) == 2 W(x) exactly (scaling by 2 is exact in every step)
+    # linearity, at full size: W(2x) == 2 W(x); exact for the integer-digit decode kernels
+    # (scaling by 2 is exact in every step), to rounding of fp16 subnormal activations for
+    # the tensor-core path
     dw.gemm(xd * 2, yd, m)
-    assert np.array_equal(yd.cpu().numpy(), 2 * y)
+    if m <= 4:
+        assert np.array_equal(yd.cpu().numpy(), 2 * y)
+    else:
+        assert np.abs(yd.cpu().numpy() - 2 * y).max() <= 1e-4 * np.abs(y).max()
     dw.free()
 
 
