@@ -3,30 +3,35 @@
 //
 //   y[t][n] = sum_k  w(n, k) * x[t][k]          w = d sc q - dmin mn   (reference/q4_k.rs:79-93)
 //
-// A real dense contraction, so it goes to the tensor cores: the 128 weight rows
-// of a tile are the MMA's M dimension, BN activation rows (tokens) its N
-// dimension, fp16 operands with f32 accumulation in TMEM (kind::f16).
+// A real dense contraction, so it goes to the tensor cores: 128 weight rows are
+// the MMA's M dimension, BN activation rows (tokens) its N dimension, fp16
+// operands with f32 accumulation in TMEM (kind::f16).
 //
-// One CTA per SM, persistent over (128-row block) x (BN-token block) tiles.
-//   warp 0      producer: per 256-column step, 16 bulk copies (8 rows x 144 B
-//               each, contiguous in the block-major tile layout) bring the packed
-//               super-blocks of the 128 rows into a 2-stage ring; per 64-column
-//               step one TMA tile load (128-byte swizzle, no multicast) brings
-//               the fp16 activations of the BN tokens
-//   warp 1      allocates TMEM, then one elected thread issues four
-//               tcgen05.mma (K = 16 each) per 64-column stage and commits them to
-//               the stage's "empty" mbarrier
-//   warps 2-9   two threads per weight row: decode the 6-bit scales, turn 16
-//               bytes of nibbles each into 32 fp16 weights (magic-number nibble ->
-//               half2, one HFMA2 and one HSUB2 per pair) and store them as one
-//               128-byte row of the swizzled K-major A tile; after a tile's last
-//               stage the same warps read the accumulator with tcgen05.ld and
-//               store y (lanes = consecutive weight rows = consecutive addresses)
+// One CTA per SM, persistent over (128 RH-row block) x (BN-token block) tiles; a
+// tile walks K in super-blocks of 256 columns = four 64-column steps.
+//   warps 0-3   MMA issuers.  Warp j issues the MMAs of 64-column group j of every
+//               super-block: two K = 16 MMAs per 32-column half-stage unit, then a
+//               tcgen05.commit to the unit's "empty" barrier.  Measured on B200: an
+//               MMA holds the tensor pipe for 128 cycles whatever M <= 128 and
+//               N <= 256 are, and holds its issuing thread meanwhile, with the
+//               thread's barrier polls not hidden behind it; four issuers keep the
+//               pipe fed.  All accumulate into the same TMEM columns.
+//   warp 4      activation producer: one TMA tile load (128-byte swizzle, no
+//               multicast) per step brings the fp16 activations of the BN tokens
+//   warps 5-20  four groups of four warps; group g expands columns [64 g, 64 g + 64)
+//               of every super-block, one thread per weight row: 16 + 32 packed bytes
+//               straight from global memory (a super-block ahead in registers, six
+//               ahead as L2 prefetches), 6-bit scales decoded, nibbles turned into
+//               fp16 (magic-number nibble -> half2, one HFMA2 and one HSUB2 per
+//               pair) and stored as 64-byte rows of two K-major units with 64-byte
+//               swizzle.  The same warps run the epilogue (tcgen05.ld, store y with
+//               lanes = consecutive weight rows = consecutive addresses, zero the
+//               columns), in pieces between the super-blocks of the next tile.
 //
 // The activations are converted to fp16 once per call by qk_x16_kernel, with
 // the columns of every 64-group permuted into the order in which a packed word
 // yields its nibbles (both operands use the same order, so the sum is
-// unchanged).  fp16 operands put the result at ~3e-4 of the output's inf-norm
+// unchanged).  fp16 operands put the result at ~5e-4 of the output's inf-norm
 // against the f32 reference (its stated tolerance is 1e-3).
 //
 // Every mbarrier wait is time-bounded; a wait that runs out raises
@@ -45,18 +50,34 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per tile (UMMA M)
 constexpr int BK = 64;             // columns per stage: one 128-byte swizzle row of fp16
-constexpr int NDW = 8;              // dequant / epilogue warps: two threads per weight row
-constexpr int NTHREADS = 64 + NDW * 32;  // + producer warp + MMA warp
-constexpr int MAX_PK_STAGES = 8;   // ring of packed super-block slabs (depth chosen per tile shape)
-constexpr uint32_t PK_CHUNK = 1152 + 32;  // one chunk's super-block column, padded against bank aliasing
-constexpr uint32_t PK_BYTES = 16 * PK_CHUNK;
+constexpr int NDW = 16;            // dequant / epilogue warps: four groups of four, group g owns A stage g
+constexpr int NI = 4;              // MMA-issuing warps 0..3: warp j issues the steps of A stage j
+constexpr int FIRST_DW = 5;        // warp 4: activation producer
+constexpr int NTHREADS = (FIRST_DW + NDW) * 32;
+constexpr int MAX_RING = 8;        // most stages of the activation ring
+constexpr uint32_t A_HALF = BM * 64;  // bytes of one A half-stage: 128 rows of 32 fp16
 
 struct GemmSmem {
-  uint32_t ab_full, ab_empty, pk_full, pk_empty, acc_full, acc_empty, tmem_slot;
-  uint32_t pk, a, b;  // ring bases (a, b 1024-byte aligned)
+  uint32_t a_full, a_empty, b_full, b_empty, acc_full, acc_empty, tmem_slot;
+  uint32_t a, b;  // ring bases, 1024-byte aligned
   uint32_t a_stage, b_stage;
-  int stages, pk_stages;
+  int b_stages;
 };
+
+#ifdef QK_TRACE
+// Developer build only: block 0 timestamps its pipeline into a global buffer.
+__device__ unsigned long long *qk_gemm_trace_buf = nullptr;
+#define QK_GSTAMP(cond, idx)                                                          \
+  do {                                                                                \
+    if ((cond) && qk_gemm_trace_buf && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {  \
+      unsigned long long t__;                                                         \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                        \
+      qk_gemm_trace_buf[idx] = t__;                                                   \
+    }                                                                                 \
+  } while (0)
+#else
+#define QK_GSTAMP(cond, idx) do {} while (0)
+#endif
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -73,6 +94,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// K-major operand tile of 32 fp16 per row: 64-byte swizzle, rows 64 bytes apart, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
 }
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                          uint32_t idesc, uint32_t accumulate) {
@@ -120,7 +146,9 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---------------------------------------------------------------- main kernel
-template <int BN>
+// BN: tokens per tile (the MMA's N).  RH: 128-row halves per tile; with RH = 2 one
+// activation stage feeds the MMAs of both halves.
+template <int BN, int RH>
 __global__ void __launch_bounds__(NTHREADS, 1)
     qk_gemm_q4k_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
                           const __grid_constant__ CUtensorMap xmap, float *__restrict__ y,
@@ -129,31 +157,38 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int NS = S.stages;
+  const uint32_t NB = (uint32_t)S.b_stages;
   const uint32_t nsb = L.nb;            // super-blocks along K
   const uint32_t steps = nsb * 4;       // 64-column stages per tile
   const uint32_t n_tiles = tok_blocks * row_blocks;
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  // Accumulators: RH of BN columns per tile.  Where tensor memory holds two sets, the
+  // MMAs of tile i+1 overlap the epilogue of tile i.  Every MMA accumulates; the
+  // epilogue leaves the columns it has read zeroed.
+  constexpr uint32_t NBUF = 2 * RH * BN <= 512 ? 2 : 1;
+  constexpr uint32_t TMEM_COLS = NBUF * RH * BN < 32 ? 32 : NBUF * RH * BN;
+  constexpr int NAU = 8 * RH;  // A half-stage units: unit ((g RH + rh) 2 + hf)
 
   pdl_launch_dependents();
+  QK_GSTAMP(threadIdx.x == 0, 0);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NS; s++) {
-      mbar_init(sbase + S.ab_full + s * 8, NDW + 1);  // dequant warps + the producer's expect_tx
-      mbar_init(sbase + S.ab_empty + s * 8, 1);  // tcgen05.commit
+    for (int s = 0; s < NAU; s++) {
+      mbar_init(sbase + S.a_full + s * 8, 4);   // the four warps of the owning group
+      mbar_init(sbase + S.a_empty + s * 8, 1);  // tcgen05.commit
     }
-    for (int s = 0; s < S.pk_stages; s++) {
-      mbar_init(sbase + S.pk_full + s * 8, 1);
-      mbar_init(sbase + S.pk_empty + s * 8, NDW);
+    for (uint32_t s = 0; s < 2 * MAX_RING; s++) mbar_init(sbase + S.b_full + s * 8, 1);  // expect_tx
+    for (uint32_t s = 0; s < NB; s++) mbar_init(sbase + S.b_empty + s * 8, 1);           // tcgen05.commit
+    for (int s = 0; s < 2; s++) {
+      mbar_init(sbase + S.acc_full + s * 8, NI);  // one commit per issuing warp
+      mbar_init(sbase + S.acc_empty + s * 8, NDW);
     }
-    mbar_init(sbase + S.acc_full, 1);
-    mbar_init(sbase + S.acc_empty, NDW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {  // tensor memory for the BN accumulator columns
+  if (warp == 0) {  // tensor memory for the accumulator columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      sbase + S.tmem_slot),
-                 "r"((uint32_t)(BN < 32 ? 32 : BN))
+                 "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -161,189 +196,306 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + S.tmem_slot);
+  if (warp >= FIRST_DW && warp < FIRST_DW + 4) {  // zero the accumulators: lanes 32 (warp % 4) ..
+    for (uint32_t c = 0; c < TMEM_COLS; c += 8)
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(
+                       tmem_base + ((32 * (warp & 3u)) << 16) + c),
+                   "r"(0u)
+                   : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
   pdl_wait();  // X16 and y belong to the previous kernel until it has finished
+  QK_GSTAMP(threadIdx.x == 0, 1);
 
   bool dead = false;
-  if (warp == 0) {
-    // ======================= producer =======================
+  if (warp == NI) {
+    // ======================= activation producer =======================
+    // Stage s is refilled when the MMAs of its previous use have retired.  Its "full"
+    // barrier alternates between two per stage (by use parity), so that a consumer
+    // waiting for use u can never mistake the completion of use u - 2 for it.
     if (lane == 0) {
-      uint32_t st = 0, eph = 0, first_round = 1;  // A/B stage ring
-      uint32_t ps = 0, pph = 0, pk_first = 1;     // packed ring
+      uint32_t st = 0, use = 0, gstep = 0;
       for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x) {
-        const uint32_t rb = t / tok_blocks, tb = t % tok_blocks;
-        for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++) {
-          // ---- packed super-block slab of the tile's 16 row chunks
-          if (!pk_first && !mbar_wait_bounded(sbase + S.pk_empty + ps * 8, pph ^ 1)) dead = true;
-          if (dead) break;
-          {
-            const uint32_t kt = sbk / L.nbt, b = sbk % L.nbt;
-            uint32_t nvalid = 0;
-            for (uint32_t c = 0; c < 16; c++)
-              if (rb * 16 + c < L.chunks) nvalid++;
-            const uint32_t bar = sbase + S.pk_full + ps * 8;
-            mbar_expect_tx(bar, nvalid * 1152);
-            for (uint32_t c = 0; c < 16; c++) {
-              const uint32_t chunk = rb * 16 + c;
-              if (chunk >= L.chunks) break;
-              bulk_g2s(sbase + S.pk + ps * PK_BYTES + c * PK_CHUNK,
-                       W + qk_tile_offset(L, chunk, kt) + (uint64_t)b * 1152, 1152, bar);
-            }
-          }
-          if (++ps == (uint32_t)S.pk_stages) ps = 0, pph ^= 1, pk_first = 0;
-          // ---- four 64-column activation tiles
-          for (uint32_t gq = 0; gq < 4; gq++) {
-            if (!first_round && !mbar_wait_bounded(sbase + S.ab_empty + st * 8, eph ^ 1)) {
-              dead = true;
-              break;
-            }
-            const uint32_t bar = sbase + S.ab_full + st * 8;
-            mbar_expect_tx(bar, BN * 128);
-            tma_load_2d(sbase + S.b + st * S.b_stage, &xmap, (int)(sbk * 256 + gq * 64),
-                        (int)(tb * BN), bar);
-            if (++st == (uint32_t)NS) st = 0, eph ^= 1, first_round = 0;
-          }
-        }
-      }
-      if (dead) atomicOr(status, QK_DEV_TIMEOUT);
-    }
-  } else if (warp == 1) {
-    // ======================= MMA issuer =======================
-    if (lane == 0) {
-      uint32_t st = 0, fph = 0, aph = 0, first_tile = 1;
-      for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x) {
-        // the epilogue of the previous tile must have drained the accumulator
-        if (!first_tile && !mbar_wait_bounded(sbase + S.acc_empty, aph)) dead = true;
-        if (!first_tile) aph ^= 1;
-        first_tile = 0;
-        if (dead) break;
-        tc_fence_after();
-        for (uint32_t step = 0; step < steps; step++) {
-          if (!mbar_wait_bounded(sbase + S.ab_full + st * 8, fph)) {
+        const uint32_t tb = t % tok_blocks;
+        for (uint32_t step = 0; step < steps; step++, gstep++) {
+          if (use >= 1 && !mbar_wait_bounded(sbase + S.b_empty + st * 8, (use - 1) & 1u)) {
             dead = true;
             break;
           }
-          tc_fence_after();
-          const uint32_t a0 = sbase + S.a + st * S.a_stage, b0 = sbase + S.b + st * S.b_stage;
-#pragma unroll
-          for (int k = 0; k < BK / 16; k++)
-            umma_f16(tmem_base, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC,
-                     (step | (uint32_t)k) ? 1u : 0u);
-          umma_commit(sbase + S.ab_empty + st * 8);  // frees the stage when these MMAs retire
-          if (++st == (uint32_t)NS) st = 0, fph ^= 1;
+          const uint32_t bar = sbase + S.b_full + ((use & 1u) * MAX_RING + st) * 8;
+          mbar_expect_tx(bar, BN * 128);
+          tma_load_2d(sbase + S.b + st * S.b_stage, &xmap, (int)(step * 64), (int)(tb * BN), bar);
+          QK_GSTAMP(gstep < 256, 256 + gstep);
+          if (++st == NB) st = 0, use++;
         }
-        if (dead) break;
-        umma_commit(sbase + S.acc_full);  // accumulator complete
       }
       if (dead) atomicOr(status, QK_DEV_TIMEOUT);
     }
-  } else {
-    // ======================= dequant + epilogue warps =======================
-    const uint32_t r = (threadIdx.x - 64) & 127u;  // weight row inside the tile
-    const uint32_t half = (threadIdx.x - 64) >> 7; // which 16 of the 32 group bytes this thread expands
-    const uint32_t chunk_in_tile = r >> 3, rr = r & 7u;
-    uint32_t st = 0, eph = 0, first_round = 1, ps = 0, pph = 0, accph = 0;
-    for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x) {
-      const uint32_t rb = t / tok_blocks, tb = t % tok_blocks;
-      for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(sbase + S.pk_full + ps * 8, pph))) {
-          dead = true;  // warp-uniform: these warps execute .aligned tcgen05 instructions later
+  } else if (warp < NI) {
+    // ======================= MMA issuers =======================
+    // A tcgen05.mma occupies the tensor pipe for the same 128 cycles whatever its M and
+    // N, and the thread that issues it is held until the pipe has taken it, its barrier
+    // polls not hidden behind its own MMAs.  So four warps issue, warp j the steps of
+    // 64-column group j of every super-block: while one is held, the others poll or
+    // queue behind it, and the pipe never waits for a poll.  All accumulate into the
+    // same columns (a tile's sum does not depend on the order).
+    if (lane == 0) {
+      const uint32_t me = warp;
+      uint32_t bst = me % NB, buse = me / NB, usea = 0, i = 0;
+      const uint32_t abar = sbase + S.a_full + me * RH * 2 * 8, aebar = sbase + S.a_empty + me * RH * 2 * 8;
+      const uint32_t a0 = sbase + S.a + me * RH * 2 * A_HALF;
+      for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x, i++) {
+        const uint32_t buf = i % NBUF, use = i / NBUF;
+        // the epilogue of the tile that last used these accumulators must have drained and zeroed them
+        if (use >= 1 && !mbar_wait_bounded(sbase + S.acc_empty + buf * 8, (use - 1) & 1u)) {
+          dead = true;
           break;
         }
-        const uint32_t slab = sbase + S.pk + ps * PK_BYTES + chunk_in_tile * PK_CHUNK;
-        // header of this row's super-block: d, dmin and the 6-bit fields (reference/q4_k.rs:27-49)
-        const uint4 h = lds128(slab + rr * 16);
-        const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
-        const uint32_t sc[2] = {h.y & 0x3F3F3F3Fu, (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)};
-        const uint32_t mn[2] = {h.z & 0x3F3F3F3Fu,
-                                ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)};
-#pragma unroll
-        for (int gq = 0; gq < 4; gq++) {
-          // sub-blocks 2 gq (low nibbles) and 2 gq + 1 (high nibbles)
-          const uint32_t sh = (gq & 1) * 16;
-          const float ds_lo = d * (float)((sc[gq >> 1] >> sh) & 0xFF);
-          const float ds_hi = d * (float)((sc[gq >> 1] >> (sh + 8)) & 0xFF);
-          const float dm_lo = dmin * (float)((mn[gq >> 1] >> sh) & 0xFF);
-          const float dm_hi = dmin * (float)((mn[gq >> 1] >> (sh + 8)) & 0xFF);
-          const __half2 s_lo = __float2half2_rn(ds_lo), s_hi = __float2half2_rn(ds_hi);
-          // (1024 + q) * s - 1024 * s is exact in the FMA, so q * s is rounded once
-          const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.f));
-          const __half2 c_hi = __hmul2(s_hi, __float2half2_rn(-1024.f));
-          const __half2 m_lo = __float2half2_rn(dm_lo), m_hi = __float2half2_rn(dm_hi);
-          const uint4 q0 = lds128(slab + 128 + gq * 256 + rr * 32 + half * 16);
-          const uint32_t w[4] = {q0.x, q0.y, q0.z, q0.w};
-          if (!first_round &&
-              !__all_sync(0xffffffffu, mbar_wait_bounded(sbase + S.ab_empty + st * 8, eph ^ 1))) {
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * RH * BN;
+        for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, usea++) {
+          const uint32_t apar = usea & 1u;
+          const uint32_t bbar = sbase + S.b_full + ((buse & 1u) * MAX_RING + bst) * 8, bpar = (buse >> 1) & 1u;
+          // both polls in flight together; the slow path only when one is not ready yet
+          const bool a_ok = mbar_try_wait(abar, apar), b_ok = mbar_try_wait(bbar, bpar);
+          if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar, apar) || !mbar_wait_bounded(bbar, bpar))) {
             dead = true;
             break;
           }
-          const uint32_t arow = sbase + S.a + st * S.a_stage + r * 128;
+          QK_GSTAMP(usea < 64, 512 + usea * 4 + me);
+          const uint32_t b0 = sbase + S.b + bst * S.b_stage;
 #pragma unroll
-          for (int i = 0; i < 4; i++) {
-            // one packed word -> 8 fp16 weights = one 16-byte chunk of the row
-            uint32_t e[4] = {(w[i] & 0x000F000Fu) | 0x64006400u, ((w[i] >> 8) & 0x000F000Fu) | 0x64006400u,
-                             ((w[i] >> 4) & 0x000F000Fu) | 0x64006400u,
-                             ((w[i] >> 12) & 0x000F000Fu) | 0x64006400u};
-            uint32_t o[4];
+          for (int rh = 0; rh < RH; rh++) {
 #pragma unroll
-            for (int p = 0; p < 4; p++) {
-              const __half2 q = *reinterpret_cast<__half2 *>(&e[p]);
-              const __half2 v = p < 2 ? __hsub2(__hfma2(q, s_lo, c_lo), m_lo)
-                                      : __hsub2(__hfma2(q, s_hi, c_hi), m_hi);
-              o[p] = *reinterpret_cast<const uint32_t *>(&v);
+            for (int hf = 0; hf < 2; hf++) {
+              const int unit = rh * 2 + hf;
+              if (unit > 0 && !mbar_wait_bounded(abar + unit * 8, apar)) {
+                dead = true;
+                break;
+              }
+              const uint32_t au = a0 + unit * A_HALF;
+              umma_f16(tmem_d + rh * BN, umma_desc_sw64(au), umma_desc(b0 + hf * 64), IDESC, 1u);
+              umma_f16(tmem_d + rh * BN, umma_desc_sw64(au + 32), umma_desc(b0 + hf * 64 + 32), IDESC, 1u);
+              umma_commit(aebar + unit * 8);  // the unit is free when these two retire
             }
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(arow + (((uint32_t)(i + 4 * half) ^ rr) << 4)),
-                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                         : "memory");
+            if (dead) break;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> MMA reads
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sbase + S.ab_full + st * 8);
-          if (++st == (uint32_t)NS) st = 0, eph ^= 1, first_round = 0;
+          if (dead) break;
+          umma_commit(sbase + S.b_empty + bst * 8);
+          bst += NI;
+          while (bst >= NB) bst -= NB, buse++;
         }
         if (dead) break;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sbase + S.pk_empty + ps * 8);  // this warp is done with the slab
-        if (++ps == (uint32_t)S.pk_stages) ps = 0, pph ^= 1;
+        umma_commit(sbase + S.acc_full + buf * 8);  // this warp's share of the tile has retired
       }
-      if (dead) break;
-      // ---- epilogue: accumulator row (32 * (warp % 4) + lane) of the tile, all BN tokens
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(sbase + S.acc_full, accph))) {
-        dead = true;
-        break;
+      if (dead) atomicOr(status, QK_DEV_TIMEOUT);
+    }
+  } else if (warp >= FIRST_DW) {
+    // ======================= dequant + epilogue warps =======================
+    const uint32_t grp = (warp - FIRST_DW) >> 2;  // columns [64 grp, 64 grp + 64) of every super-block
+    const uint32_t r = 32 * (warp & 3u) + lane;   // weight row inside a 128-row half = accumulator lane (a warp reads lanes 32 (warp % 4) ..)
+    const uint32_t chunk_in_half = r >> 3, rr = r & 7u;
+    // this row in the group's half-stage units: 64-byte rows, 16-byte chunk c at c ^ ((r >> 1) & 3)
+    const uint32_t arow = sbase + S.a + grp * RH * 2 * A_HALF + r * 64, asw = (r >> 1) & 3u;
+    const uint32_t aaddr[4] = {arow + ((0u ^ asw) << 4), arow + ((1u ^ asw) << 4), arow + ((2u ^ asw) << 4),
+                               arow + ((3u ^ asw) << 4)};
+    const uint32_t a_full = sbase + S.a_full + grp * RH * 2 * 8, a_empty = sbase + S.a_empty + grp * RH * 2 * 8;
+    // Epilogue of a finished tile, in pieces of 16 columns.  With two accumulator sets the
+    // pieces go between the super-blocks of the next tile, so that the stores are spread
+    // out and the MMAs stay fed; with one set the next tile's MMAs wait for them, so they
+    // all go after the next tile's first super-block.  This warp reads accumulator lanes
+    // 32 (warp % 4) .. + 32 and its group's share of the columns of every row half.
+    constexpr int CPG = BN >= 128 ? BN / 4 : 32;  // columns per group
+    constexpr uint32_t NCH = RH * CPG / 16;       // pieces per tile
+    bool epi_active = false;
+    uint32_t epi_it = 0, epi_rb = 0, epi_tb = 0, epi_next = 0;
+    auto epi_piece = [&]() -> bool {
+      const uint32_t buf = epi_it % NBUF;
+      if (epi_next == 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(sbase + S.acc_full + buf * 8, (epi_it / NBUF) & 1u)))
+          return false;
+        tc_fence_after();
+        QK_GSTAMP(grp == 0 && (warp & 3u) == 0 && epi_it < 16, 1900 + epi_it);
       }
-      accph ^= 1;
-      tc_fence_after();
-      const uint32_t lane_row = 32 * (warp & 3u) + lane;
-      const uint32_t row = rb * BM + lane_row;
-      const uint32_t taddr = tmem_base + ((32 * (warp & 3u)) << 16);
-      const int c_begin = BN >= 64 ? (int)half * (BN / 2) : 0;
-      const int c_end = BN >= 64 ? c_begin + BN / 2 : (half == 0 ? BN : 0);
-#pragma unroll 1
-      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-        uint32_t v[32];
+      const uint32_t rh = epi_next / (CPG / 16);
+      const int c0 = (int)grp * CPG + (int)(epi_next % (CPG / 16)) * 16;
+      if ((int)grp * CPG < BN) {
+        const uint32_t row = (epi_rb * RH + rh) * BM + r;
+        const uint32_t taddr = tmem_base + ((32 * (warp & 3u)) << 16) + (buf * RH + rh) * BN + (uint32_t)c0;
+        uint32_t v[16];
         asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-              "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-              "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-              "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(taddr + (uint32_t)c0));
+              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+              "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < L.rows) {
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const uint32_t tok = tb * BN + c0 + j;
-            if (tok < m_tokens) y[(uint64_t)tok * ldy + row] = __uint_as_float(v[j]);
-          }
+        for (int c = 0; c < 16; c += 8)  // leave the columns zeroed for their next tile
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(
+                           taddr + (uint32_t)c),
+                       "r"(0u)
+                       : "memory");
+        if (row < L.rows) {
+          float *yp = y + (uint64_t)(epi_tb * BN + c0) * ldy + row;
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            if (epi_tb * BN + c0 + j < m_tokens) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sbase + S.acc_empty);
+      if (++epi_next == NCH) {
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sbase + S.acc_empty + buf * 8);
+        QK_GSTAMP(grp == 0 && (warp & 3u) == 0 && epi_it < 16, 1920 + epi_it);
+        epi_active = false;
+      }
+      return true;
+    };
+
+    // Packed weights come straight from global memory, one super-block ahead in registers
+    // and PF_AHEAD super-blocks ahead as L2 prefetches.  A row of the block-major tile:
+    // 16 header bytes at [8 rows][16], then per 64-column group 32 bytes at [8 rows][32].
+    constexpr uint32_t PF_AHEAD = 6;
+    auto row_ptr = [&](uint32_t t, int rh) -> const uint8_t * {
+      uint32_t chunk = ((t / tok_blocks) * RH + rh) * 16 + chunk_in_half;
+      if (chunk >= L.chunks) chunk = L.chunks - 1;  // rows past the end: valid bytes, results unused
+      return W + (uint64_t)chunk * L.chunk_bytes;
+    };
+    auto ldg16 = [](const uint8_t *p) -> uint4 {
+      uint4 v;
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "l"(p));
+      return v;
+    };
+    const uint32_t hoff = rr * 16, qoff = 128 + grp * 256 + rr * 32;
+    uint32_t it = 0, u = 0;  // u: super-blocks done = uses of each of this group's A units
+    // cursor of the next super-block to load, and of the next one to prefetch (byte offset inside the rows)
+    uint32_t lt = blockIdx.x, lsb = 0, pt = blockIdx.x, psb = 0;
+    const uint8_t *lp[RH], *pp[RH];
+    uint4 nh[RH], nq0[RH], nq1[RH];
+#pragma unroll
+    for (int rh = 0; rh < RH; rh++) {
+      lp[rh] = pp[rh] = lt < n_tiles ? row_ptr(lt, rh) : W;
+      nh[rh] = nq0[rh] = nq1[rh] = make_uint4(0, 0, 0, 0);
     }
+    auto load_next = [&]() {
+      if (lt >= n_tiles) return;
+#pragma unroll
+      for (int rh = 0; rh < RH; rh++) {
+        const uint8_t *p = lp[rh] + lsb * 1152u;
+        nh[rh] = ldg16(p + hoff), nq0[rh] = ldg16(p + qoff), nq1[rh] = ldg16(p + qoff + 16);
+      }
+      if (++lsb == nsb) {
+        lsb = 0, lt += gridDim.x;
+        if (lt < n_tiles) {
+#pragma unroll
+          for (int rh = 0; rh < RH; rh++) lp[rh] = row_ptr(lt, rh);
+        }
+      }
+    };
+    auto prefetch_next = [&](bool issue) {
+      if (pt >= n_tiles) return;
+      if (issue) {
+#pragma unroll
+        for (int rh = 0; rh < RH; rh++) {
+          const uint8_t *p = pp[rh] + psb * 1152u;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p + qoff));
+          if (grp == 0 && rr == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+      }
+      if (++psb == nsb) {
+        psb = 0, pt += gridDim.x;
+        if (pt < n_tiles) {
+#pragma unroll
+          for (int rh = 0; rh < RH; rh++) pp[rh] = row_ptr(pt, rh);
+        }
+      }
+    };
+    load_next();
+    for (uint32_t k = 0; k <= PF_AHEAD; k++) prefetch_next(k > 0);
+
+    for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x, it++) {
+      const uint32_t rb = t / tok_blocks, tb = t % tok_blocks;
+      for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, u++) {
+        uint4 h[RH], q0[RH], q1[RH];
+#pragma unroll
+        for (int rh = 0; rh < RH; rh++) h[rh] = nh[rh], q0[rh] = nq0[rh], q1[rh] = nq1[rh];
+        load_next();
+        prefetch_next(true);
+#pragma unroll
+        for (int rh = 0; rh < RH; rh++) {
+          // header of this row's super-block: d, dmin and the 6-bit fields (reference/q4_k.rs:27-49)
+          const float d = h2f_bits(h[rh].x), dmin = h2f_bits(h[rh].x >> 16);
+          // sub-blocks 2 grp (low nibbles) and 2 grp + 1 (high nibbles)
+          const uint32_t scw = grp < 2 ? (h[rh].y & 0x3F3F3F3Fu)
+                                       : ((h[rh].w & 0x0F0F0F0Fu) | ((h[rh].y >> 2) & 0x30303030u));
+          const uint32_t mnw = grp < 2 ? (h[rh].z & 0x3F3F3F3Fu)
+                                       : (((h[rh].w >> 4) & 0x0F0F0F0Fu) | ((h[rh].z >> 2) & 0x30303030u));
+          const uint32_t sh = (grp & 1u) * 16;
+          const float ds_lo = d * (float)((scw >> sh) & 0xFF), ds_hi = d * (float)((scw >> (sh + 8)) & 0xFF);
+          const float dm_lo = dmin * (float)((mnw >> sh) & 0xFF), dm_hi = dmin * (float)((mnw >> (sh + 8)) & 0xFF);
+          const __half2 s_lo = __float2half2_rn(ds_lo), s_hi = __float2half2_rn(ds_hi);
+          const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.f));
+          const __half2 c_hi = __hmul2(s_hi, __float2half2_rn(-64.f));
+          const __half2 m_lo = __float2half2_rn(dm_lo), m_hi = __float2half2_rn(dm_hi);
+          const uint32_t w[8] = {q0[rh].x, q0[rh].y, q0[rh].z, q0[rh].w, q1[rh].x, q1[rh].y, q1[rh].z, q1[rh].w};
+#pragma unroll
+          for (int hf = 0; hf < 2; hf++) {
+            const int unit = rh * 2 + hf;
+            // the MMAs that read this unit's previous contents must have retired
+            if (u > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(a_empty + unit * 8, (u - 1) & 1u))) {
+              dead = true;  // warp-uniform: these warps execute .aligned tcgen05 instructions later
+              break;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              // one packed word -> 8 fp16 weights = one 16-byte chunk of the row.  A nibble q
+              // becomes the half 1024 + q (low nibbles, 0x6400 | q) or 64 + q (high nibbles,
+              // 0x5400 | q << 4, no shift needed); (K + q) * s - K * s is exact in the FMA, so
+              // q * s is rounded once.
+              const uint32_t wi = w[4 * hf + i], wj = wi >> 8;
+              const uint32_t e[4] = {(wi & 0x000F000Fu) | 0x64006400u, (wj & 0x000F000Fu) | 0x64006400u,
+                                     (wi & 0x00F000F0u) | 0x54005400u, (wj & 0x00F000F0u) | 0x54005400u};
+              uint32_t o[4];
+#pragma unroll
+              for (int p = 0; p < 4; p++) {
+                const __half2 q = *reinterpret_cast<const __half2 *>(&e[p]);
+                const __half2 v = p < 2 ? __hsub2(__hfma2(q, s_lo, c_lo), m_lo)
+                                        : __hsub2(__hfma2(q, s_hi, c_hi), m_hi);
+                o[p] = *reinterpret_cast<const uint32_t *>(&v);
+              }
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(aaddr[i] + unit * A_HALF), "r"(o[0]),
+                           "r"(o[1]), "r"(o[2]), "r"(o[3])
+                           : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> MMA reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_full + unit * 8);
+          }
+          if (dead) break;
+        }
+        if (dead) break;
+        // pieces of the previous tile's epilogue, once this tile's first stages are under way
+        if (NBUF == 1) {
+          while (epi_active && !dead)
+            if (!epi_piece()) dead = true;
+        } else if (epi_active && sbk >= 1 && !epi_piece()) {
+          dead = true;
+        }
+      }
+      while (epi_active && !dead)  // a tile too short to have carried all the pieces
+        if (!epi_piece()) dead = true;
+      epi_active = true, epi_it = it, epi_rb = rb, epi_tb = tb, epi_next = 0;
+    }
+    while (epi_active && !dead)
+      if (!epi_piece()) dead = true;
     if (dead && lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
   }
 
@@ -351,9 +503,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1)
+  if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)(BN < 32 ? 32 : BN))
+                 "r"(TMEM_COLS)
                  : "memory");
 }
 
@@ -375,43 +527,46 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-bool plan_gemm(int bn, GemmSmem *S, uint32_t *total) {
+bool plan_gemm(int bn, int rh, GemmSmem *S, uint32_t *total) {
   uint32_t off = 0;
   GemmSmem s;
-  s.ab_full = off, off += 8 * 8;
-  s.ab_empty = off, off += 8 * 8;
-  s.pk_full = off, off += MAX_PK_STAGES * 8;
-  s.pk_empty = off, off += MAX_PK_STAGES * 8;
-  s.acc_full = off, off += 8;
-  s.acc_empty = off, off += 8;
+  s.a_full = off, off += 16 * 8;
+  s.a_empty = off, off += 16 * 8;
+  s.b_full = off, off += 2 * MAX_RING * 8;
+  s.b_empty = off, off += MAX_RING * 8;
+  s.acc_full = off, off += 16;
+  s.acc_empty = off, off += 16;
   s.tmem_slot = off, off += 16;
-  off = (off + 127u) & ~127u;
-  s.a_stage = BM * 128;
-  s.b_stage = (uint32_t)bn * 128;
-  // Shared memory is split between the fp16 operand ring (>= 3 stages) and the ring
-  // of packed slabs, which is what hides HBM latency: as deep as fits, up to 8.
-  const uint32_t budget = 227u * 1024u - 2048u;
-  int stages = bn >= 256 ? 3 : 4;
-  int pk_stages = (int)((budget - off - 1024u - stages * (s.a_stage + s.b_stage)) / PK_BYTES);
-  if (pk_stages > MAX_PK_STAGES) pk_stages = MAX_PK_STAGES;
-  if (pk_stages < 2) return false;
-  s.stages = stages, s.pk_stages = pk_stages;
-  s.pk = off, off += pk_stages * PK_BYTES;
   off = (off + 1023u) & ~1023u;
-  s.a = off, off += stages * s.a_stage;
-  s.b = off, off += stages * s.b_stage;
+  s.a_stage = A_HALF;
+  s.b_stage = (uint32_t)bn * 128;
+  // What the fp16 weight units leave goes to the activation ring: a stage is refilled
+  // only after the MMAs that read it have retired, so its depth is what hides the L2
+  // latency of the tile loads.
+  const uint32_t budget = 227u * 1024u;
+  const uint32_t a_bytes = 8u * rh * A_HALF;
+  int b_stages = (int)((budget - off - a_bytes) / s.b_stage);
+  if (b_stages > MAX_RING) b_stages = MAX_RING;
+  if (const char *e = getenv("QK_GEMM_BSTAGES")) {
+    const int v = atoi(e);
+    if (v >= 2 && v <= b_stages) b_stages = v;
+  }
+  if (b_stages < 2) return false;
+  s.b_stages = b_stages;
+  s.a = off, off += a_bytes;
+  s.b = off, off += b_stages * s.b_stage;
   *S = s, *total = off;
   return true;
 }
 
-template <int BN>
+template <int BN, int RH>
 cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint32_t m,
                         uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
                         cudaStream_t s) {
   GemmSmem S;
   uint32_t total;
-  if (!plan_gemm(BN, &S, &total)) return cudaErrorInvalidConfiguration;
-  auto kern = qk_gemm_q4k_tc_kernel<BN>;
+  if (!plan_gemm(BN, RH, &S, &total)) return cudaErrorInvalidConfiguration;
+  auto kern = qk_gemm_q4k_tc_kernel<BN, RH>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -422,7 +577,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   if (!enc) return cudaErrorNotSupported;
   const uint32_t Kp = L.nb * 256u;
   const uint32_t tok_blocks = (m + BN - 1) / BN, m_pad = tok_blocks * BN;
-  const uint32_t row_blocks = (L.rows + BM - 1) / BM;
+  const uint32_t row_blocks = (L.rows + RH * BM - 1) / (RH * BM);
   __half *x16 = reinterpret_cast<__half *>(scratch);
 
   CUtensorMap map;
@@ -457,6 +612,12 @@ int pick_bn(uint32_t m) { return m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 
 
 }  // namespace
 
+#ifdef QK_TRACE
+extern "C" void qk_gemm_trace_set(unsigned long long *p) {
+  cudaMemcpyToSymbol(qk_gemm_trace_buf, &p, sizeof(p));
+}
+#endif
+
 bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m) {
   return L.type == QK_T_Q4_K && m >= 1 && L.rows >= 1 && L.nb >= 1;
 }
@@ -472,12 +633,15 @@ cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const flo
                               int sm_count, cudaStream_t s) {
   switch (pick_bn(m)) {
     case 32:
-      return launch_gemm<32>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<32, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
     case 64:
-      return launch_gemm<64>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<64, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
     case 128:
-      return launch_gemm<128>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<128, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
     default:
-      return launch_gemm<256>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      // RH = 2 (256-row tiles, half the activation traffic per MMA) measured slower on
+      // B200 (76 us against 61 us at 14336 x 4096, 512 tokens): its activation ring is only
+      // three stages deep.  The kernel keeps the parameter; only RH = 1 is built.
+      return launch_gemm<256, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
   }
 }

@@ -35,6 +35,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same poll, letting the hardware park the thread for up to `hint_ns` while the
+// phase is pending (it is woken when the phase completes), so that a waiting warp
+// does not spend issue slots on its polling loop.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: false if the barrier has not flipped after about a quarter of a
 // second (checked against the global nanosecond timer every 256 polls).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
@@ -43,7 +57,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
     for (int i = 0; i < 256; i++)
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     if (t - t0 > 250000000ull) return false;
