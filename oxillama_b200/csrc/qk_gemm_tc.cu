@@ -121,9 +121,264 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- weight formats
+// What differs between the formats is how a thread fetches the packed bytes of one
+// row-step (one weight row x 64 columns: group g of a 256-column super-block) and
+// expands them into 64 fp16 values, 8 chunks of 8.  Each format expands in the order
+// its packed words yield values; SRC(p) names the column (inside the super-block) that
+// lands at position p, and the activations are laid out in the same order, so the
+// contraction is unchanged.
+//
+//   Pk        the packed bytes of one row-step, held in registers a super-block ahead
+//   load      fetch Pk for (chunk, row-in-chunk rr, group g, super-block s)
+//   prefetch  the same bytes as L2 prefetches
+//   expand    half hf (32 columns) of the row-step -> four 16-byte chunks
+template <int T>
+struct WFmt;
+
+__device__ __forceinline__ uint4 ldg16(const uint8_t *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void pf_l2(const uint8_t *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// Four nibble pairs of one packed word -> 8 halves: low nibbles q become 1024 + q
+// (0x6400 | q), high nibbles 64 + q (0x5400 | q << 4, no shift needed); values come out
+// as pairs (byte 0, byte 2), (byte 1, byte 3) of the low nibbles, then of the high ones.
+__device__ __forceinline__ void nibbles_to_magic(uint32_t w, uint32_t e[4]) {
+  const uint32_t wj = w >> 8;
+  e[0] = (w & 0x000F000Fu) | 0x64006400u, e[1] = (wj & 0x000F000Fu) | 0x64006400u;
+  e[2] = (w & 0x00F000F0u) | 0x54005400u, e[3] = (wj & 0x00F000F0u) | 0x54005400u;
+}
+// Four unsigned bytes -> halves 1024 + b, in byte order.
+__device__ __forceinline__ void bytes_to_magic(uint32_t w, uint32_t &lo, uint32_t &hi) {
+  lo = prmt(w, 0x64646464u, 0x4140), hi = prmt(w, 0x64646464u, 0x4342);
+}
+// Where block-of-32 formats keep rows of a k-tile: plane p, row rr, block b (row-major planes).
+__device__ __forceinline__ const uint8_t *rm_addr(const QkLayout &L, const uint8_t *W, uint32_t chunk,
+                                                  uint32_t kt, uint32_t nbt_this, uint32_t plane_off,
+                                                  uint32_t rr, uint32_t b, uint32_t pw) {
+  return W + qk_tile_offset(L, chunk, kt) + (uint64_t)QK_TILE_ROWS * nbt_this * plane_off +
+         (uint64_t)(rr * nbt_this + b) * pw;
+}
+
+template <>
+struct WFmt<QK_T_Q4_K> {  // super-block of 256: d, dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles (reference/q4_k.rs:27-102)
+  struct Pk { uint4 h, q0, q1; };
+  // position 8 i + j of a row-step <- column 4 i + {0,2,1,3}[j & 3] + 32 (j >> 2): byte 4 i + b of
+  // the group's 32 holds column 4 i + b (low nibble) and 32 + 4 i + b (high nibble)
+  __host__ __device__ static uint32_t src(uint32_t p) {
+    const uint32_t g = p >> 6, i = (p >> 3) & 7u, j = p & 7u, jj = j & 3u;
+    return 64 * g + 4 * i + (jj == 1 ? 2 : jj == 2 ? 1 : jj) + 32 * (j >> 2);
+  }
+  __device__ static const uint8_t *base(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t s) {
+    return W + (uint64_t)chunk * L.chunk_bytes + (uint64_t)s * 1152u;  // block-major: [super-block][8 rows x 16 | 4 x 8 rows x 32]
+  }
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
+                              uint32_t g, uint32_t s) {
+    const uint8_t *p = base(L, W, chunk, s);
+    k.h = ldg16(p + rr * 16), k.q0 = ldg16(p + 128 + g * 256 + rr * 32), k.q1 = ldg16(p + 128 + g * 256 + rr * 32 + 16);
+  }
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
+                                  uint32_t s) {
+    const uint8_t *p = base(L, W, chunk, s);
+    pf_l2(p + 128 + g * 256 + rr * 32);
+    if (g == 0 && rr == 0) pf_l2(p);
+  }
+  struct Sc { __half2 s_lo, s_hi, c_lo, c_hi, m_lo, m_hi; };
+  __device__ static void scales(const Pk &k, uint32_t g, Sc &c) {
+    const float d = h2f_bits(k.h.x), dmin = h2f_bits(k.h.x >> 16);
+    // sub-blocks 2 g (low nibbles) and 2 g + 1 (high nibbles)
+    const uint32_t scw = g < 2 ? (k.h.y & 0x3F3F3F3Fu) : ((k.h.w & 0x0F0F0F0Fu) | ((k.h.y >> 2) & 0x30303030u));
+    const uint32_t mnw = g < 2 ? (k.h.z & 0x3F3F3F3Fu) : (((k.h.w >> 4) & 0x0F0F0F0Fu) | ((k.h.z >> 2) & 0x30303030u));
+    const uint32_t sh = (g & 1u) * 16;
+    c.s_lo = __float2half2_rn(d * (float)((scw >> sh) & 0xFF)), c.s_hi = __float2half2_rn(d * (float)((scw >> (sh + 8)) & 0xFF));
+    c.m_lo = __float2half2_rn(dmin * (float)((mnw >> sh) & 0xFF)), c.m_hi = __float2half2_rn(dmin * (float)((mnw >> (sh + 8)) & 0xFF));
+    // (K + q) * s - K * s is exact in the FMA, so q * s is rounded once
+    c.c_lo = __hmul2(c.s_lo, __float2half2_rn(-1024.f)), c.c_hi = __hmul2(c.s_hi, __float2half2_rn(-64.f));
+  }
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t g, int hf, uint32_t o[4][4]) {
+    const uint4 q = hf ? k.q1 : k.q0;
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint32_t e[4];
+      nibbles_to_magic(w[i], e);
+      o[i][0] = h2_bits(__hsub2(__hfma2(bits_h2(e[0]), c.s_lo, c.c_lo), c.m_lo));
+      o[i][1] = h2_bits(__hsub2(__hfma2(bits_h2(e[1]), c.s_lo, c.c_lo), c.m_lo));
+      o[i][2] = h2_bits(__hsub2(__hfma2(bits_h2(e[2]), c.s_hi, c.c_hi), c.m_hi));
+      o[i][3] = h2_bits(__hsub2(__hfma2(bits_h2(e[3]), c.s_hi, c.c_hi), c.m_hi));
+    }
+  }
+};
+
+template <>
+struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
+  struct Pk { uint4 q[4]; uint32_t d2; };
+  __host__ __device__ static uint32_t src(uint32_t p) { return p; }
+  __device__ static void where(const QkLayout &L, uint32_t g, uint32_t s, uint32_t &kt, uint32_t &b, uint32_t &nbt_this) {
+    const uint32_t gb = 8 * s + 2 * g;  // first of the row-step's two blocks
+    kt = gb / L.nbt, b = gb % L.nbt, nbt_this = qk_tile_nb(L, kt);
+  }
+  // Blocks past the end of the row (a last super-block that is not full) read as d = 0, q = 0.
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
+                              uint32_t g, uint32_t s) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    k.q[0] = k.q[1] = k.q[2] = k.q[3] = z, k.d2 = 0;
+    if (8 * s + 2 * g >= L.nb) return;
+    uint32_t kt, b, nt;
+    where(L, g, s, kt, b, nt);
+    const uint8_t *pq = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 32);
+    const unsigned short *pd = reinterpret_cast<const unsigned short *>(rm_addr(L, W, chunk, kt, nt, 32, rr, b, 2));
+    k.q[0] = ldg16(pq), k.q[1] = ldg16(pq + 16), k.d2 = __ldg(pd);
+    if (b + 1 < nt) k.q[2] = ldg16(pq + 32), k.q[3] = ldg16(pq + 48), k.d2 |= (uint32_t)__ldg(pd + 1) << 16;
+  }
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
+                                  uint32_t s) {
+    if (8 * s + 2 * g >= L.nb) return;
+    uint32_t kt, b, nt;
+    where(L, g, s, kt, b, nt);
+    pf_l2(rm_addr(L, W, chunk, kt, nt, 0, rr, b, 32));
+  }
+  struct Sc { __half2 d[2]; };
+  __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
+    c.d[0] = bits_h2((k.d2 & 0xFFFFu) * 0x10001u), c.d[1] = bits_h2((k.d2 >> 16) * 0x10001u);
+  }
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4]) {
+    const __half2 off = __float2half2_rn(1152.f);  // 1024 + 128: (1024 + (q ^ 0x80)) - 1152 = q, exact; q * d rounded once
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint4 q = k.q[2 * hf + (i >> 1)];
+      const uint32_t w0 = ((i & 1) ? q.z : q.x) ^ 0x80808080u, w1 = ((i & 1) ? q.w : q.y) ^ 0x80808080u;
+      uint32_t a, b2;
+      bytes_to_magic(w0, a, b2);
+      o[i][0] = h2_bits(__hmul2(__hsub2(bits_h2(a), off), c.d[hf]));
+      o[i][1] = h2_bits(__hmul2(__hsub2(bits_h2(b2), off), c.d[hf]));
+      bytes_to_magic(w1, a, b2);
+      o[i][2] = h2_bits(__hmul2(__hsub2(bits_h2(a), off), c.d[hf]));
+      o[i][3] = h2_bits(__hmul2(__hsub2(bits_h2(b2), off), c.d[hf]));
+    }
+  }
+};
+
+template <>
+struct WFmt<QK_T_Q4_0> {  // block of 32: f16 d, 16 bytes; byte j = elements 2 j (low nibble) and 2 j + 1 (high) (reference/q4_0.rs:36-46)
+  struct Pk { uint4 q[2]; uint32_t d2; };
+  // chunk c of a row-step is word c & 3 of block c >> 2; a word yields its elements as
+  // (byte 0, byte 2), (byte 1, byte 3) low nibbles, then the same of the high nibbles
+  __host__ __device__ static uint32_t src(uint32_t p) {
+    const uint32_t c = (p >> 3) & 7u, j = p & 7u;
+    const uint32_t order = 0x73516240u;  // positions 0..7 <- elements 0, 4, 2, 6, 1, 5, 3, 7 of the word
+    return (p & ~63u) + 32 * (c >> 2) + 8 * (c & 3u) + ((order >> (4 * j)) & 7u);
+  }
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
+                              uint32_t g, uint32_t s) {
+    k.q[0] = k.q[1] = make_uint4(0, 0, 0, 0), k.d2 = 0;
+    if (8 * s + 2 * g >= L.nb) return;
+    uint32_t kt, b, nt;
+    WFmt<QK_T_Q8_0>::where(L, g, s, kt, b, nt);
+    const uint8_t *pq = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 16);
+    const unsigned short *pd = reinterpret_cast<const unsigned short *>(rm_addr(L, W, chunk, kt, nt, 16, rr, b, 2));
+    k.q[0] = ldg16(pq), k.d2 = __ldg(pd);
+    if (b + 1 < nt) k.q[1] = ldg16(pq + 16), k.d2 |= (uint32_t)__ldg(pd + 1) << 16;
+  }
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
+                                  uint32_t s) {
+    if (8 * s + 2 * g >= L.nb) return;
+    uint32_t kt, b, nt;
+    WFmt<QK_T_Q8_0>::where(L, g, s, kt, b, nt);
+    pf_l2(rm_addr(L, W, chunk, kt, nt, 0, rr, b, 16));
+  }
+  using Sc = WFmt<QK_T_Q8_0>::Sc;
+  __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
+    c.d[0] = bits_h2((k.d2 & 0xFFFFu) * 0x10001u), c.d[1] = bits_h2((k.d2 >> 16) * 0x10001u);
+  }
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4]) {
+    const __half2 off_lo = __float2half2_rn(1032.f), off_hi = __float2half2_rn(72.f);  // K + 8: (K + q) - (K + 8) = q - 8, exact
+    const uint4 q = k.q[hf];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint32_t e[4];
+      nibbles_to_magic(w[i], e);
+      o[i][0] = h2_bits(__hmul2(__hsub2(bits_h2(e[0]), off_lo), c.d[hf]));
+      o[i][1] = h2_bits(__hmul2(__hsub2(bits_h2(e[1]), off_lo), c.d[hf]));
+      o[i][2] = h2_bits(__hmul2(__hsub2(bits_h2(e[2]), off_hi), c.d[hf]));
+      o[i][3] = h2_bits(__hmul2(__hsub2(bits_h2(e[3]), off_hi), c.d[hf]));
+    }
+  }
+};
+
+template <>
+struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, f16 d (reference/q6_k.rs)
+  // group g: half hh = g >> 1 of the super-block, nibble n = g & 1 of ql[64 hh ..], bit pairs 4 n + {0, 2} of qh[32 hh ..]
+  struct Pk { uint4 ql[4], qh[2]; uint32_t sc4, d; };
+  __host__ __device__ static uint32_t src(uint32_t p) { return p; }
+  __device__ static void where(const QkLayout &L, uint32_t s, uint32_t &kt, uint32_t &b, uint32_t &nbt_this) {
+    kt = s / L.nbt, b = s % L.nbt, nbt_this = qk_tile_nb(L, kt);
+  }
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
+                              uint32_t g, uint32_t s) {
+    uint32_t kt, b, nt;
+    where(L, s, kt, b, nt);
+    const uint32_t hh = g >> 1;
+    const uint8_t *p0 = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 192);
+#pragma unroll
+    for (int i = 0; i < 4; i++) k.ql[i] = ldg16(p0 + 64 * hh + 16 * i);
+    k.qh[0] = ldg16(p0 + 128 + 32 * hh), k.qh[1] = ldg16(p0 + 128 + 32 * hh + 16);
+    k.sc4 = __ldg(reinterpret_cast<const uint32_t *>(rm_addr(L, W, chunk, kt, nt, 192, rr, b, 16) + 8 * hh + 4 * (g & 1u)));
+    k.d = __ldg(reinterpret_cast<const unsigned short *>(rm_addr(L, W, chunk, kt, nt, 208, rr, b, 2)));
+  }
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
+                                  uint32_t s) {
+    uint32_t kt, b, nt;
+    where(L, s, kt, b, nt);
+    const uint8_t *p0 = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 192);
+    if (g == 0) pf_l2(p0);  // the row's 192 bytes span two or three lines
+    else if (g == 1) pf_l2(p0 + 96);
+    else if (g == 2) pf_l2(p0 + 191);
+  }
+  struct Sc { __half2 s[4]; };
+  __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
+    const float d = h2f_bits(k.d);
+#pragma unroll
+    for (int i = 0; i < 4; i++) c.s[i] = __float2half2_rn(d * (float)(int)(signed char)((k.sc4 >> (8 * i)) & 0xFF));
+  }
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t g, int hf, uint32_t o[4][4]) {
+    // half hf of the row-step = columns 32 hf .. + 32 of the group: ql bytes 32 hf + l, qh byte l, bit pair 4 n + 2 hf
+    const __half2 off = __float2half2_rn(1056.f);  // (1024 + q) - 1056 = q - 32, exact; then one rounding in the product
+    const uint32_t nsh = 4 * (g & 1u), hsh = 4 * (g & 1u) + 2 * hf;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint4 l4 = k.ql[2 * hf + (i >> 1)], h4 = k.qh[i >> 1];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const uint32_t lw = (i & 1) ? (e ? l4.w : l4.z) : (e ? l4.y : l4.x);
+        const uint32_t hw = (i & 1) ? (e ? h4.w : h4.z) : (e ? h4.y : h4.x);
+        const uint32_t q6 = ((lw >> nsh) & 0x0F0F0F0Fu) | (((hw >> hsh) & 0x03030303u) << 4);
+        uint32_t a, b2;
+        bytes_to_magic(q6, a, b2);
+        const __half2 sc = c.s[2 * hf + ((2 * i + e) >> 2)];  // 16 columns per scale
+        o[i][2 * e + 0] = h2_bits(__hmul2(__hsub2(bits_h2(a), off), sc));
+        o[i][2 * e + 1] = h2_bits(__hmul2(__hsub2(bits_h2(b2), off), sc));
+      }
+    }
+  }
+};
+
 // ---------------------------------------------------------------- activations -> fp16
-// X16[t][64 g + 8 i + j] = x[t][64 g + 4 i + {0,2,1,3}[j & 3] + 32 (j >> 2)]; rows t >= m and
-// columns >= cols are zero.  One thread per 8 output halves (one 16-byte store).
+// X16[t][256 s + p] = x[t][256 s + SRC(p)] in fp16; rows t >= m and columns >= cols are
+// zero.  One thread per 8 output halves (one 16-byte store).
+template <int T>
 __global__ void __launch_bounds__(256)
     qk_x16_kernel(const float *__restrict__ x, uint32_t m, uint32_t cols, uint32_t m_pad,
                   uint32_t Kp, __half *__restrict__ out) {
@@ -133,11 +388,11 @@ __global__ void __launch_bounds__(256)
   const uint64_t total = (uint64_t)m_pad * per_row;
   for (uint64_t it = blockIdx.x * 256ull + threadIdx.x; it < total; it += (uint64_t)gridDim.x * 256) {
     const uint32_t t = (uint32_t)(it / per_row), c = (uint32_t)(it % per_row);
-    const uint32_t g = c >> 3, i = c & 7u;
     __align__(16) __half h[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-      const uint32_t k = 64 * g + 4 * i + ((j & 3) == 1 ? 2 : (j & 3) == 2 ? 1 : (j & 3)) + 32 * (j >> 2);
+      const uint32_t p = 8 * c + j;
+      const uint32_t k = (p & ~255u) + WFmt<T>::src(p & 255u);
       const float v = (t < m && k < cols) ? __ldg(x + (uint64_t)t * cols + k) : 0.f;
       h[j] = __float2half_rn(v);
     }
@@ -146,11 +401,11 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---------------------------------------------------------------- main kernel
-// BN: tokens per tile (the MMA's N).  RH: 128-row halves per tile; with RH = 2 one
-// activation stage feeds the MMAs of both halves.
-template <int BN, int RH>
+// T: weight format.  BN: tokens per tile (the MMA's N).  RH: 128-row halves per tile;
+// with RH = 2 one activation stage feeds the MMAs of both halves.
+template <int T, int BN, int RH>
 __global__ void __launch_bounds__(NTHREADS, 1)
-    qk_gemm_q4k_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
+    qk_gemm_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
                           const __grid_constant__ CUtensorMap xmap, float *__restrict__ y,
                           uint64_t ldy, uint32_t m_tokens, uint32_t tok_blocks, uint32_t row_blocks,
                           unsigned *status, GemmSmem S) {
@@ -158,7 +413,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t NB = (uint32_t)S.b_stages;
-  const uint32_t nsb = L.nb;            // super-blocks along K
+  const uint32_t nsb = (L.cols + 255u) / 256u;  // super-blocks (256 columns) along K
   const uint32_t steps = nsb * 4;       // 64-column stages per tile
   const uint32_t n_tiles = tok_blocks * row_blocks;
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -359,64 +614,30 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     };
 
     // Packed weights come straight from global memory, one super-block ahead in registers
-    // and PF_AHEAD super-blocks ahead as L2 prefetches.  A row of the block-major tile:
-    // 16 header bytes at [8 rows][16], then per 64-column group 32 bytes at [8 rows][32].
+    // and PF_AHEAD super-blocks ahead as L2 prefetches.
+    using F = WFmt<T>;
     constexpr uint32_t PF_AHEAD = 6;
-    auto row_ptr = [&](uint32_t t, int rh) -> const uint8_t * {
-      uint32_t chunk = ((t / tok_blocks) * RH + rh) * 16 + chunk_in_half;
-      if (chunk >= L.chunks) chunk = L.chunks - 1;  // rows past the end: valid bytes, results unused
-      return W + (uint64_t)chunk * L.chunk_bytes;
+    auto chunk_of = [&](uint32_t t, int rh) -> uint32_t {
+      const uint32_t chunk = ((t / tok_blocks) * RH + rh) * 16 + chunk_in_half;
+      return chunk < L.chunks ? chunk : L.chunks - 1;  // rows past the end: valid bytes, results unused
     };
-    auto ldg16 = [](const uint8_t *p) -> uint4 {
-      uint4 v;
-      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                   : "l"(p));
-      return v;
-    };
-    const uint32_t hoff = rr * 16, qoff = 128 + grp * 256 + rr * 32;
     uint32_t it = 0, u = 0;  // u: super-blocks done = uses of each of this group's A units
-    // cursor of the next super-block to load, and of the next one to prefetch (byte offset inside the rows)
+    // cursor of the next super-block to load, and of the next one to prefetch
     uint32_t lt = blockIdx.x, lsb = 0, pt = blockIdx.x, psb = 0;
-    const uint8_t *lp[RH], *pp[RH];
-    uint4 nh[RH], nq0[RH], nq1[RH];
-#pragma unroll
-    for (int rh = 0; rh < RH; rh++) {
-      lp[rh] = pp[rh] = lt < n_tiles ? row_ptr(lt, rh) : W;
-      nh[rh] = nq0[rh] = nq1[rh] = make_uint4(0, 0, 0, 0);
-    }
+    typename F::Pk nk[RH];
     auto load_next = [&]() {
       if (lt >= n_tiles) return;
 #pragma unroll
-      for (int rh = 0; rh < RH; rh++) {
-        const uint8_t *p = lp[rh] + lsb * 1152u;
-        nh[rh] = ldg16(p + hoff), nq0[rh] = ldg16(p + qoff), nq1[rh] = ldg16(p + qoff + 16);
-      }
-      if (++lsb == nsb) {
-        lsb = 0, lt += gridDim.x;
-        if (lt < n_tiles) {
-#pragma unroll
-          for (int rh = 0; rh < RH; rh++) lp[rh] = row_ptr(lt, rh);
-        }
-      }
+      for (int rh = 0; rh < RH; rh++) F::load(nk[rh], L, W, chunk_of(lt, rh), rr, grp, lsb);
+      if (++lsb == nsb) lsb = 0, lt += gridDim.x;
     };
     auto prefetch_next = [&](bool issue) {
       if (pt >= n_tiles) return;
       if (issue) {
 #pragma unroll
-        for (int rh = 0; rh < RH; rh++) {
-          const uint8_t *p = pp[rh] + psb * 1152u;
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(p + qoff));
-          if (grp == 0 && rr == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-        }
+        for (int rh = 0; rh < RH; rh++) F::prefetch(L, W, chunk_of(pt, rh), rr, grp, psb);
       }
-      if (++psb == nsb) {
-        psb = 0, pt += gridDim.x;
-        if (pt < n_tiles) {
-#pragma unroll
-          for (int rh = 0; rh < RH; rh++) pp[rh] = row_ptr(pt, rh);
-        }
-      }
+      if (++psb == nsb) psb = 0, pt += gridDim.x;
     };
     load_next();
     for (uint32_t k = 0; k <= PF_AHEAD; k++) prefetch_next(k > 0);
@@ -424,57 +645,30 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x, it++) {
       const uint32_t rb = t / tok_blocks, tb = t % tok_blocks;
       for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, u++) {
-        uint4 h[RH], q0[RH], q1[RH];
+        typename F::Pk pk[RH];
 #pragma unroll
-        for (int rh = 0; rh < RH; rh++) h[rh] = nh[rh], q0[rh] = nq0[rh], q1[rh] = nq1[rh];
+        for (int rh = 0; rh < RH; rh++) pk[rh] = nk[rh];
         load_next();
         prefetch_next(true);
 #pragma unroll
         for (int rh = 0; rh < RH; rh++) {
-          // header of this row's super-block: d, dmin and the 6-bit fields (reference/q4_k.rs:27-49)
-          const float d = h2f_bits(h[rh].x), dmin = h2f_bits(h[rh].x >> 16);
-          // sub-blocks 2 grp (low nibbles) and 2 grp + 1 (high nibbles)
-          const uint32_t scw = grp < 2 ? (h[rh].y & 0x3F3F3F3Fu)
-                                       : ((h[rh].w & 0x0F0F0F0Fu) | ((h[rh].y >> 2) & 0x30303030u));
-          const uint32_t mnw = grp < 2 ? (h[rh].z & 0x3F3F3F3Fu)
-                                       : (((h[rh].w >> 4) & 0x0F0F0F0Fu) | ((h[rh].z >> 2) & 0x30303030u));
-          const uint32_t sh = (grp & 1u) * 16;
-          const float ds_lo = d * (float)((scw >> sh) & 0xFF), ds_hi = d * (float)((scw >> (sh + 8)) & 0xFF);
-          const float dm_lo = dmin * (float)((mnw >> sh) & 0xFF), dm_hi = dmin * (float)((mnw >> (sh + 8)) & 0xFF);
-          const __half2 s_lo = __float2half2_rn(ds_lo), s_hi = __float2half2_rn(ds_hi);
-          const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.f));
-          const __half2 c_hi = __hmul2(s_hi, __float2half2_rn(-64.f));
-          const __half2 m_lo = __float2half2_rn(dm_lo), m_hi = __float2half2_rn(dm_hi);
-          const uint32_t w[8] = {q0[rh].x, q0[rh].y, q0[rh].z, q0[rh].w, q1[rh].x, q1[rh].y, q1[rh].z, q1[rh].w};
+          typename F::Sc sc;
+          F::scales(pk[rh], grp, sc);
 #pragma unroll
           for (int hf = 0; hf < 2; hf++) {
             const int unit = rh * 2 + hf;
+            uint32_t o[4][4];
+            F::expand(pk[rh], sc, grp, hf, o);
             // the MMAs that read this unit's previous contents must have retired
             if (u > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(a_empty + unit * 8, (u - 1) & 1u))) {
               dead = true;  // warp-uniform: these warps execute .aligned tcgen05 instructions later
               break;
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-              // one packed word -> 8 fp16 weights = one 16-byte chunk of the row.  A nibble q
-              // becomes the half 1024 + q (low nibbles, 0x6400 | q) or 64 + q (high nibbles,
-              // 0x5400 | q << 4, no shift needed); (K + q) * s - K * s is exact in the FMA, so
-              // q * s is rounded once.
-              const uint32_t wi = w[4 * hf + i], wj = wi >> 8;
-              const uint32_t e[4] = {(wi & 0x000F000Fu) | 0x64006400u, (wj & 0x000F000Fu) | 0x64006400u,
-                                     (wi & 0x00F000F0u) | 0x54005400u, (wj & 0x00F000F0u) | 0x54005400u};
-              uint32_t o[4];
-#pragma unroll
-              for (int p = 0; p < 4; p++) {
-                const __half2 q = *reinterpret_cast<const __half2 *>(&e[p]);
-                const __half2 v = p < 2 ? __hsub2(__hfma2(q, s_lo, c_lo), m_lo)
-                                        : __hsub2(__hfma2(q, s_hi, c_hi), m_hi);
-                o[p] = *reinterpret_cast<const uint32_t *>(&v);
-              }
-              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(aaddr[i] + unit * A_HALF), "r"(o[0]),
-                           "r"(o[1]), "r"(o[2]), "r"(o[3])
+            for (int i = 0; i < 4; i++)
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(aaddr[i] + unit * A_HALF), "r"(o[i][0]),
+                           "r"(o[i][1]), "r"(o[i][2]), "r"(o[i][3])
                            : "memory");
-            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> MMA reads
             __syncwarp();
             if (lane == 0) mbar_arrive(a_full + unit * 8);
@@ -559,14 +753,18 @@ bool plan_gemm(int bn, int rh, GemmSmem *S, uint32_t *total) {
   return true;
 }
 
-template <int BN, int RH>
+template <int T, int BN>
 cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint32_t m,
                         uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
                         cudaStream_t s) {
+  // RH = 2 (256-row tiles, half the activation traffic per MMA) measured slower on B200
+  // (76 us against 61 us at Q4_K 14336 x 4096, 512 tokens): its activation ring is only
+  // three stages deep.  The kernel keeps the parameter; only RH = 1 is built.
+  constexpr int RH = 1;
   GemmSmem S;
   uint32_t total;
   if (!plan_gemm(BN, RH, &S, &total)) return cudaErrorInvalidConfiguration;
-  auto kern = qk_gemm_q4k_tc_kernel<BN, RH>;
+  auto kern = qk_gemm_tc_kernel<T, BN, RH>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -575,7 +773,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   }
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
-  const uint32_t Kp = L.nb * 256u;
+  const uint32_t Kp = ((L.cols + 255u) / 256u) * 256u;
   const uint32_t tok_blocks = (m + BN - 1) / BN, m_pad = tok_blocks * BN;
   const uint32_t row_blocks = (L.rows + RH * BM - 1) / (RH * BM);
   __half *x16 = reinterpret_cast<__half *>(scratch);
@@ -597,7 +795,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   cudaLaunchConfig_t c0 = {};
   c0.gridDim = dim3((unsigned)((n8 + 255) / 256 > 148 * 8 ? 148 * 8 : (n8 + 255) / 256));
   c0.blockDim = dim3(256), c0.stream = s, c0.attrs = at, c0.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel, x, m, L.cols, m_pad, Kp, x16);
+  cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16);
   if (e != cudaSuccess) return e;
 
   uint32_t grid = tok_blocks * row_blocks;
@@ -610,6 +808,22 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
 
 int pick_bn(uint32_t m) { return m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
 
+template <int T>
+cudaError_t launch_fmt(const QkLayout &L, const uint8_t *tiled, const float *x, float *y, uint32_t m,
+                       uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
+                       cudaStream_t s) {
+  switch (pick_bn(m)) {
+    case 32:
+      return launch_gemm<T, 32>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    case 64:
+      return launch_gemm<T, 64>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    case 128:
+      return launch_gemm<T, 128>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    default:
+      return launch_gemm<T, 256>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+  }
+}
+
 }  // namespace
 
 #ifdef QK_TRACE
@@ -619,29 +833,29 @@ extern "C" void qk_gemm_trace_set(unsigned long long *p) {
 #endif
 
 bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m) {
-  return L.type == QK_T_Q4_K && m >= 1 && L.rows >= 1 && L.nb >= 1;
+  const bool fmt = L.type == QK_T_Q4_K || L.type == QK_T_Q8_0 || L.type == QK_T_Q4_0 || L.type == QK_T_Q6_K;
+  return fmt && m >= 1 && L.rows >= 1 && L.nb >= 1;
 }
 
 size_t qk_gemm_tc_scratch_bytes(const QkLayout &L, uint32_t m) {
   const int bn = pick_bn(m);
   const uint64_t m_pad = ((m + bn - 1) / bn) * (uint64_t)bn;
-  return (size_t)(m_pad * L.nb * 256ull * 2ull);
+  return (size_t)(m_pad * ((L.cols + 255ull) / 256ull) * 256ull * 2ull);
 }
 
 cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                               uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                               int sm_count, cudaStream_t s) {
-  switch (pick_bn(m)) {
-    case 32:
-      return launch_gemm<32, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    case 64:
-      return launch_gemm<64, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    case 128:
-      return launch_gemm<128, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+  switch (L.type) {
+    case QK_T_Q4_K:
+      return launch_fmt<QK_T_Q4_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    case QK_T_Q8_0:
+      return launch_fmt<QK_T_Q8_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    case QK_T_Q4_0:
+      return launch_fmt<QK_T_Q4_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    case QK_T_Q6_K:
+      return launch_fmt<QK_T_Q6_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
     default:
-      // RH = 2 (256-row tiles, half the activation traffic per MMA) measured slower on
-      // B200 (76 us against 61 us at 14336 x 4096, 512 tokens): its activation ring is only
-      // three stages deep.  The kernel keeps the parameter; only RH = 1 is built.
-      return launch_gemm<256, 1>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return cudaErrorNotSupported;
   }
 }
