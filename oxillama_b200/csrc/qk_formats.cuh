@@ -55,11 +55,11 @@ __device__ __forceinline__ float qk_dequant_elem(const QkLayout &L, const uint8_
       return __fsub_rn(__fmul_rn(d1, (float)q), m1);
     }
     case QK_T_Q6_K: {  // reference/q6_k.rs:39-71
-      const uint8_t *p0 = at(0, 0), *sc = at(1, 0);
+      const uint8_t *sc = at(1, 0);
       float d = qk_h2f(at(2, 0));
       int g = i >> 7, rem = i & 127, k = rem >> 5, l = rem & 31, is = l >> 4;
-      uint8_t qlb = p0[64 * g + l + ((k & 1) ? 32 : 0)];
-      uint8_t qhb = p0[128 + 32 * g + l];
+      uint8_t qlb = *at(0, 64 * g + l + ((k & 1) ? 32 : 0));
+      uint8_t qhb = *at(0, 128 + 32 * g + l);
       int nib = (k & 2) ? (qlb >> 4) : (qlb & 0x0F);
       int q = (nib | (((qhb >> (2 * k)) & 3) << 4)) - 32;
       float s = (float)(int8_t)sc[8 * g + is + 2 * k];

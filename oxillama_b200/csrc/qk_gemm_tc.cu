@@ -163,12 +163,11 @@ __device__ __forceinline__ void nibbles_to_magic(uint32_t w, uint32_t e[4]) {
 __device__ __forceinline__ void bytes_to_magic(uint32_t w, uint32_t &lo, uint32_t &hi) {
   lo = prmt(w, 0x64646464u, 0x4140), hi = prmt(w, 0x64646464u, 0x4342);
 }
-// Where block-of-32 formats keep rows of a k-tile: plane p, row rr, block b (row-major planes).
-__device__ __forceinline__ const uint8_t *rm_addr(const QkLayout &L, const uint8_t *W, uint32_t chunk,
-                                                  uint32_t kt, uint32_t nbt_this, uint32_t plane_off,
-                                                  uint32_t rr, uint32_t b, uint32_t pw) {
-  return W + qk_tile_offset(L, chunk, kt) + (uint64_t)QK_TILE_ROWS * nbt_this * plane_off +
-         (uint64_t)(rr * nbt_this + b) * pw;
+// Start of block `blk` (of the row) in the 8-row chunk: tiles are block-major, so the
+// 8 x bb bytes of one block column are one span and block columns follow one another.
+__device__ __forceinline__ const uint8_t *blk_addr(const QkLayout &L, const uint8_t *W, uint32_t chunk,
+                                                   uint32_t blk) {
+  return W + (uint64_t)chunk * L.chunk_bytes + (uint64_t)blk * (QK_TILE_ROWS * L.bb);
 }
 
 template <>
@@ -181,7 +180,7 @@ struct WFmt<QK_T_Q4_K> {  // super-block of 256: d, dmin, 12 bytes of 6-bit scal
     return 64 * g + 4 * i + (jj == 1 ? 2 : jj == 2 ? 1 : jj) + 32 * (j >> 2);
   }
   __device__ static const uint8_t *base(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t s) {
-    return W + (uint64_t)chunk * L.chunk_bytes + (uint64_t)s * 1152u;  // block-major: [super-block][8 rows x 16 | 4 x 8 rows x 32]
+    return blk_addr(L, W, chunk, s);  // [8 rows x 16 header | 4 groups x 8 rows x 32 nibble bytes]
   }
   __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
                               uint32_t g, uint32_t s) {
@@ -225,29 +224,27 @@ template <>
 struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
   struct Pk { uint4 q[4]; uint32_t d2; };
   __host__ __device__ static uint32_t src(uint32_t p) { return p; }
-  __device__ static void where(const QkLayout &L, uint32_t g, uint32_t s, uint32_t &kt, uint32_t &b, uint32_t &nbt_this) {
-    const uint32_t gb = 8 * s + 2 * g;  // first of the row-step's two blocks
-    kt = gb / L.nbt, b = gb % L.nbt, nbt_this = qk_tile_nb(L, kt);
-  }
   // Blocks past the end of the row (a last super-block that is not full) read as d = 0, q = 0.
+  // A block's 8 rows: [2 granules x 8 rows x 16 int8][8 x d].
   __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
                               uint32_t g, uint32_t s) {
     const uint4 z = make_uint4(0, 0, 0, 0);
     k.q[0] = k.q[1] = k.q[2] = k.q[3] = z, k.d2 = 0;
-    if (8 * s + 2 * g >= L.nb) return;
-    uint32_t kt, b, nt;
-    where(L, g, s, kt, b, nt);
-    const uint8_t *pq = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 32);
-    const unsigned short *pd = reinterpret_cast<const unsigned short *>(rm_addr(L, W, chunk, kt, nt, 32, rr, b, 2));
-    k.q[0] = ldg16(pq), k.q[1] = ldg16(pq + 16), k.d2 = __ldg(pd);
-    if (b + 1 < nt) k.q[2] = ldg16(pq + 32), k.q[3] = ldg16(pq + 48), k.d2 |= (uint32_t)__ldg(pd + 1) << 16;
+    const uint32_t b = 8 * s + 2 * g;  // first of the row-step's two blocks
+    if (b >= L.nb) return;
+    const uint8_t *p = blk_addr(L, W, chunk, b);
+    k.q[0] = ldg16(p + rr * 16), k.q[1] = ldg16(p + 128 + rr * 16);
+    k.d2 = __ldg(reinterpret_cast<const unsigned short *>(p + 256) + rr);
+    if (b + 1 < L.nb) {
+      k.q[2] = ldg16(p + 272 + rr * 16), k.q[3] = ldg16(p + 272 + 128 + rr * 16);
+      k.d2 |= (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p + 272 + 256) + rr) << 16;
+    }
   }
   __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
                                   uint32_t s) {
-    if (8 * s + 2 * g >= L.nb) return;
-    uint32_t kt, b, nt;
-    where(L, g, s, kt, b, nt);
-    pf_l2(rm_addr(L, W, chunk, kt, nt, 0, rr, b, 32));
+    const uint32_t b = 8 * s + 2 * g;
+    if (b >= L.nb || rr >= 5) return;
+    pf_l2(blk_addr(L, W, chunk, b) + rr * 128);  // two blocks = 544 bytes = up to five lines
   }
   struct Sc { __half2 d[2]; };
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
@@ -280,23 +277,24 @@ struct WFmt<QK_T_Q4_0> {  // block of 32: f16 d, 16 bytes; byte j = elements 2 j
     const uint32_t order = 0x73516240u;  // positions 0..7 <- elements 0, 4, 2, 6, 1, 5, 3, 7 of the word
     return (p & ~63u) + 32 * (c >> 2) + 8 * (c & 3u) + ((order >> (4 * j)) & 7u);
   }
+  // A block's 8 rows: [8 rows x 16 nibble bytes][8 x d].
   __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
                               uint32_t g, uint32_t s) {
     k.q[0] = k.q[1] = make_uint4(0, 0, 0, 0), k.d2 = 0;
-    if (8 * s + 2 * g >= L.nb) return;
-    uint32_t kt, b, nt;
-    WFmt<QK_T_Q8_0>::where(L, g, s, kt, b, nt);
-    const uint8_t *pq = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 16);
-    const unsigned short *pd = reinterpret_cast<const unsigned short *>(rm_addr(L, W, chunk, kt, nt, 16, rr, b, 2));
-    k.q[0] = ldg16(pq), k.d2 = __ldg(pd);
-    if (b + 1 < nt) k.q[1] = ldg16(pq + 16), k.d2 |= (uint32_t)__ldg(pd + 1) << 16;
+    const uint32_t b = 8 * s + 2 * g;
+    if (b >= L.nb) return;
+    const uint8_t *p = blk_addr(L, W, chunk, b);
+    k.q[0] = ldg16(p + rr * 16), k.d2 = __ldg(reinterpret_cast<const unsigned short *>(p + 128) + rr);
+    if (b + 1 < L.nb) {
+      k.q[1] = ldg16(p + 144 + rr * 16);
+      k.d2 |= (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p + 144 + 128) + rr) << 16;
+    }
   }
   __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
                                   uint32_t s) {
-    if (8 * s + 2 * g >= L.nb) return;
-    uint32_t kt, b, nt;
-    WFmt<QK_T_Q8_0>::where(L, g, s, kt, b, nt);
-    pf_l2(rm_addr(L, W, chunk, kt, nt, 0, rr, b, 16));
+    const uint32_t b = 8 * s + 2 * g;
+    if (b >= L.nb || rr >= 3) return;
+    pf_l2(blk_addr(L, W, chunk, b) + rr * 128);  // two blocks = 288 bytes
   }
   using Sc = WFmt<QK_T_Q8_0>::Sc;
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
@@ -323,29 +321,21 @@ struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, 
   // group g: half hh = g >> 1 of the super-block, nibble n = g & 1 of ql[64 hh ..], bit pairs 4 n + {0, 2} of qh[32 hh ..]
   struct Pk { uint4 ql[4], qh[2]; uint32_t sc4, d; };
   __host__ __device__ static uint32_t src(uint32_t p) { return p; }
-  __device__ static void where(const QkLayout &L, uint32_t s, uint32_t &kt, uint32_t &b, uint32_t &nbt_this) {
-    kt = s / L.nbt, b = s % L.nbt, nbt_this = qk_tile_nb(L, kt);
-  }
+  // A block's 8 rows: [12 granules x 8 rows x 16 bytes of ql+qh][8 rows x 16 scales][8 x d].
   __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
                               uint32_t g, uint32_t s) {
-    uint32_t kt, b, nt;
-    where(L, s, kt, b, nt);
     const uint32_t hh = g >> 1;
-    const uint8_t *p0 = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 192);
+    const uint8_t *p = blk_addr(L, W, chunk, s) + rr * 16;
 #pragma unroll
-    for (int i = 0; i < 4; i++) k.ql[i] = ldg16(p0 + 64 * hh + 16 * i);
-    k.qh[0] = ldg16(p0 + 128 + 32 * hh), k.qh[1] = ldg16(p0 + 128 + 32 * hh + 16);
-    k.sc4 = __ldg(reinterpret_cast<const uint32_t *>(rm_addr(L, W, chunk, kt, nt, 192, rr, b, 16) + 8 * hh + 4 * (g & 1u)));
-    k.d = __ldg(reinterpret_cast<const unsigned short *>(rm_addr(L, W, chunk, kt, nt, 208, rr, b, 2)));
+    for (int i = 0; i < 4; i++) k.ql[i] = ldg16(p + (4 * hh + i) * 128);
+    k.qh[0] = ldg16(p + (8 + 2 * hh) * 128), k.qh[1] = ldg16(p + (9 + 2 * hh) * 128);
+    k.sc4 = __ldg(reinterpret_cast<const uint32_t *>(p + 1536 + 8 * hh + 4 * (g & 1u)));
+    k.d = __ldg(reinterpret_cast<const unsigned short *>(p - rr * 16 + 1664) + rr);
   }
   __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
                                   uint32_t s) {
-    uint32_t kt, b, nt;
-    where(L, s, kt, b, nt);
-    const uint8_t *p0 = rm_addr(L, W, chunk, kt, nt, 0, rr, b, 192);
-    if (g == 0) pf_l2(p0);  // the row's 192 bytes span two or three lines
-    else if (g == 1) pf_l2(p0 + 96);
-    else if (g == 2) pf_l2(p0 + 191);
+    const uint32_t line = g * 8 + rr;  // 1680 bytes = up to 14 lines, one per thread of the row group
+    if (line < 14) pf_l2(blk_addr(L, W, chunk, s) + line * 128);
   }
   struct Sc { __half2 s[4]; };
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {

@@ -125,11 +125,15 @@ __global__ void __launch_bounds__(NT)
                    float *__restrict__ y, uint64_t ldy, unsigned *status, int nstage,
                    uint32_t stage_bytes, Smem S, uint32_t Kp) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int RPT = 8 / RS;             // rows per thread
-  constexpr int WPS = NWARP / RS;         // warps per row split
+  // Eight neighbouring lanes take the eight rows of a chunk and the same 64-weight unit:
+  // their 16-byte weight reads are one 128-byte span of the block-major tile (no bank
+  // conflict) and their activation reads one broadcast.
+  static_assert(RS == 8, "one row per lane");
+  constexpr int RPT = 1;                  // rows per thread
+  constexpr int UL = NT / 8;              // units in flight per pass of the CTA
   const uint32_t sbase = smem_u32(smem);  // S.* are offsets from here (S.bars == 0)
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t split = warp % RS, ulane = (warp / RS) * 32 + lane;
+  const uint32_t split = lane & 7u, ulane = threadIdx.x >> 3;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + S.flag);
 
   const uint32_t my_chunks =
@@ -172,11 +176,11 @@ __global__ void __launch_bounds__(NT)
 
     // ---- per-tile scale decode into floats (one thread per block of the tile)
     if (TYPE == QK_T_Q6_K) {
-      const uint32_t p1 = tile + 8 * nbt * 192, p2 = p1 + 8 * nbt * 16;
-      for (uint32_t i = threadIdx.x; i < 8 * nbt; i += NT) {
-        uint4 s = lds128(p1 + i * 16);
-        uint32_t dw = lds32((p2 + i * 2) & ~3u);
-        float d = h2f_bits((i & 1) ? (dw >> 16) : dw);
+      for (uint32_t i = threadIdx.x; i < 8 * nbt; i += NT) {  // i = r * nbt + sb
+        const uint32_t blk = tile + (i % nbt) * 1680u, ri = i / nbt;  // block-major: ql+qh 1536 | scales 128 | d 16
+        uint4 s = lds128(blk + 1536 + ri * 16);
+        uint32_t dw = lds32(blk + 1664 + (ri & ~1u) * 2);
+        float d = h2f_bits((ri & 1) ? (dw >> 16) : dw);
         uint32_t w[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
         for (int u = 0; u < 4; u++) {  // unit u = 2G + is needs scales 8G + is + 2k
@@ -186,7 +190,7 @@ __global__ void __launch_bounds__(NT)
           o.y = d * (float)(int8_t)(w[2 * G] >> (8 * (is + 2)));
           o.z = d * (float)(int8_t)(w[2 * G + 1] >> (8 * is));
           o.w = d * (float)(int8_t)(w[2 * G + 1] >> (8 * (is + 2)));
-          *reinterpret_cast<float4 *>(smem + S.dec + (i * 4 + u) * 16) = o;
+          *reinterpret_cast<float4 *>(smem + S.dec + (((i % nbt) * 4 + u) * 8 + ri) * 16) = o;  // [sb][unit][row]
         }
       }
       __syncthreads();
@@ -195,7 +199,7 @@ __global__ void __launch_bounds__(NT)
     // ---- main: units of 64 weights, RPT rows each
     const uint32_t units = nbt * (L.bs == 32 ? 1u : 8u) / 2u;  // 64-weight units per row in this tile
     const uint32_t kbase = kt * QK_TILE_ELEMS;                 // first column of the tile
-    for (uint32_t u = ulane; u < units; u += WPS * 32) {
+    for (uint32_t u = ulane; u < units; u += UL) {
       // digit registers for this unit: 16 words per (m, d)
       uint32_t xw[M][D][16];
       const uint32_t xoff = kbase + u * 64, sw = ((xoff >> 6) >> 1) & 3u;
@@ -213,16 +217,17 @@ __global__ void __launch_bounds__(NT)
       for (int rr = 0; rr < RPT; rr++) {
         const uint32_t r = split * RPT + rr;
         if (TYPE == QK_T_Q4_0 || TYPE == QK_T_Q8_0) {
-          const uint32_t qw = TYPE == QK_T_Q4_0 ? 16u : 32u;
+          // block-major: a block's 8 rows are [nibbles or int8s, 16-byte granules x 8 rows][d, 8 x 2]
+          const uint32_t bsz = TYPE == QK_T_Q4_0 ? 144u : 272u, doff = TYPE == QK_T_Q4_0 ? 128u : 256u;
           const uint32_t b0 = 2 * u;  // blocks 2u, 2u+1 of this row in the tile
-          const uint32_t p1 = tile + 8 * nbt * qw;
-          uint32_t dd = lds32(p1 + (r * nbt + b0) * 2);
 #pragma unroll
           for (int j = 0; j < 2; j++) {
             if (b0 + j >= nbt) break;
-            float dj = h2f_bits(j ? (dd >> 16) : dd);
+            const uint32_t blk = tile + (b0 + j) * bsz;
+            const uint32_t dw = lds32(blk + doff + (r & ~1u) * 2);
+            float dj = h2f_bits((r & 1u) ? (dw >> 16) : dw);
             if (TYPE == QK_T_Q4_0) {
-              uint4 q = lds128(tile + (r * nbt + b0 + j) * 16);
+              uint4 q = lds128(blk + r * 16);
               uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
               for (int m = 0; m < M; m++) {
@@ -242,8 +247,8 @@ __global__ void __launch_bounds__(NT)
                 acc[m][rr] = fmaf(dj, fmaf(-8.f, s.y, p), acc[m][rr]);  // (q - 8) zero point
               }
             } else {
-              uint4 q0 = lds128(tile + (r * nbt + b0 + j) * 32);
-              uint4 q1 = lds128(tile + (r * nbt + b0 + j) * 32 + 16);
+              uint4 q0 = lds128(blk + r * 16);
+              uint4 q1 = lds128(blk + 128 + r * 16);
               uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
               for (int m = 0; m < M; m++) {
@@ -262,10 +267,10 @@ __global__ void __launch_bounds__(NT)
           }
         } else {  // Q6_K: unit = (sb, G, is); strips k = 0..3 of 16 columns each
           const uint32_t sb = u >> 2, G = (u >> 1) & 1u, is = u & 1u;
-          const uint32_t qb = tile + (r * nbt + sb) * 192;
-          uint4 a = lds128(qb + 64 * G + 16 * is), b = lds128(qb + 64 * G + 32 + 16 * is);
-          uint4 h = lds128(qb + 128 + 32 * G + 16 * is);
-          float4 sc = lds128f(sbase + S.dec + ((r * nbt + sb) * 4 + (u & 3u)) * 16);
+          const uint32_t qb = tile + sb * 1680u + r * 16;  // byte o of ql+qh: granule o / 16 of the block
+          uint4 a = lds128(qb + (4 * G + is) * 128), b = lds128(qb + (4 * G + 2 + is) * 128);
+          uint4 h = lds128(qb + (8 + 2 * G + is) * 128);
+          float4 sc = lds128f(sbase + S.dec + ((sb * 4 + (u & 3u)) * 8 + r) * 16);
           uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
           uint32_t hw[4] = {h.x, h.y, h.z, h.w};
           uint32_t q[4][4];  // [strip][word], reference/q6_k.rs:55-60
@@ -308,24 +313,21 @@ __global__ void __launch_bounds__(NT)
 
     if (kt + 1 == L.ktiles) {  // chunk finished: reduce and write 8 rows x M
       const uint32_t red_parity = (item / L.ktiles) & 1;  // double-buffered
-      float *red = reinterpret_cast<float *>(smem + S.red) + red_parity * (NWARP * M * RPT);
+      float *red = reinterpret_cast<float *>(smem + S.red) + red_parity * (NWARP * M * 8);
 #pragma unroll
-      for (int m = 0; m < M; m++)
-#pragma unroll
-        for (int r = 0; r < RPT; r++) {
-          float v = acc[m][r];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-          if (lane == 0) red[warp * (M * RPT) + m * RPT + r] = v;
-          acc[m][r] = 0.f;
-        }
+      for (int m = 0; m < M; m++) {
+        float v = acc[m][0];
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);  // lanes 0..7: this warp's sum for rows 0..7
+        if (lane < 8) red[warp * (M * 8) + m * 8 + lane] = v;
+        acc[m][0] = 0.f;
+      }
       __syncthreads();
       if (threadIdx.x < 8 * M) {
         uint32_t m = threadIdx.x / 8, r = threadIdx.x % 8;
-        uint32_t sp = r / RPT, rr = r % RPT;
         float v = 0.f;
 #pragma unroll
-        for (int wv = 0; wv < WPS; wv++) v += red[(wv * RS + sp) * (M * RPT) + m * RPT + rr];
+        for (int wv = 0; wv < NWARP; wv++) v += red[wv * (M * 8) + m * 8 + r];
         uint32_t row = chunk * 8 + r;
         if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
       }
@@ -419,24 +421,15 @@ int pick_rs(const QkLayout &L) {
   uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
   uint32_t units = nbt_max * (L.bs == 32 ? 1u : 8u) / 2u;
   if (units == 0) units = 1;
-  int rs = 1;
-  while (rs < 8 && units * rs < NT) rs *= 2;
-  return rs;
+  (void)units;
+  return 8;  // one row per lane
 }
 
 template <int TYPE, int M, int D>
 cudaError_t launch_rs(int rs, const QkLayout &L, const uint8_t *W, const float *x, float *y,
                       uint64_t ldy, unsigned *status, int sm_count, const Plan &P, cudaStream_t s) {
-  switch (rs) {
-    case 1:
-      return launch_one<TYPE, M, D, 1>(L, W, x, y, ldy, status, sm_count, P, s);
-    case 2:
-      return launch_one<TYPE, M, D, 2>(L, W, x, y, ldy, status, sm_count, P, s);
-    case 4:
-      return launch_one<TYPE, M, D, 4>(L, W, x, y, ldy, status, sm_count, P, s);
-    default:
-      return launch_one<TYPE, M, D, 8>(L, W, x, y, ldy, status, sm_count, P, s);
-  }
+  (void)rs;
+  return launch_one<TYPE, M, D, 8>(L, W, x, y, ldy, status, sm_count, P, s);
 }
 
 template <int TYPE>

@@ -8,26 +8,26 @@
 //
 //   tile  = 8 consecutive rows x up to QK_TILE_ELEMS consecutive columns
 //   chunk = the tiles of one 8-row group, k-tile after k-tile
-//   inside a tile the fields of its blocks are split into planes, each plane
-//   holding one fixed-width field of every block of the tile:
+//   inside a tile the blocks follow one another (block-major), and inside a
+//   block the fields of its 8 rows are split into planes, each plane cut into
+//   granules of g bytes with the same granule of all 8 rows side by side:
+//   [nbt blocks][planes][width/g granules][8 rows][g bytes]
 //
-//     Q4_0   plane0 nibbles 16 B | plane1 d 2 B
-//     Q8_0   plane0 int8s   32 B | plane1 d 2 B
-//     Q4_K   block-major: per block  d,dmin,scales 16 B x 8 rows | nibbles, 4 groups x 8 rows x 32 B
-//     Q6_K   plane0 ql+qh  192 B | plane1 scales 16 B | plane2 d 2 B
-//     IQ4_XS plane0 nibbles 128 B | plane1 d,scales_h,scales_l 8 B
+//     Q4_0   nibbles 16 B (g 16)          | d 2 B (g 2)                  8 x 18  = 144 B per block
+//     Q8_0   int8s   32 B (g 16)          | d 2 B (g 2)                  8 x 34  = 272 B
+//     Q4_K   d,dmin,scales 16 B (g 16)    | nibbles 128 B (g 32)         8 x 144 = 1152 B
+//     Q6_K   ql+qh  192 B (g 16) | scales 16 B (g 16) | d 2 B (g 2)      8 x 210 = 1680 B
+//     IQ4_XS nibbles 128 B (g 16)         | d,scales_h,scales_l 8 B (g 8) 8 x 136 = 1088 B
 //
-//   A plane is either row-major, [8 rows][nbt blocks][width], or interleaved
-//   with granule g: [nbt blocks][width/g granules][8 rows][g bytes].  The
-//   interleaved form puts the same 32-byte group of all 8 rows side by side,
-//   which is exactly one tensor-core B/A fragment row per lane group and reads
-//   from shared memory without bank conflicts.  A block-major tile (Q4_K) keeps
-//   all interleaved planes of one block together, [nbt blocks][planes...]: the
-//   8 x 144 = 1152 bytes of one super-block column are then one contiguous span,
-//   which is what the prefill kernel copies per 256-column step.
+//   The same 16- or 32-byte group of all 8 rows lies in one 128- or 256-byte
+//   span: eight lanes that hold the eight rows read it from HBM as full sectors
+//   and from shared memory without bank conflicts, and it is one tensor-core
+//   fragment row per lane group.  The 8 x bb bytes of one block column are one
+//   contiguous span.  (The accessors below also understand row-major planes,
+//   [8 rows][nbt blocks][width], which no format uses any more.)
 //
-// Every plane of every tile starts on a 16-byte boundary for any K and any row
-// count (8 * nbt * width is a multiple of 16 for all widths above), and one
+// Every block and every plane of it starts on a 16-byte boundary for any K and
+// any row count (8 * width is a multiple of 16 for all widths above), and one
 // tile is one contiguous span of HBM, so a single bulk copy stages it.
 // Rows are padded up to a multiple of 8 with all-zero blocks (scale 0: they
 // contribute exactly 0 and are never written out).
@@ -69,11 +69,13 @@ static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayo
   switch (type) {
     case QK_T_Q4_0:
       l.bs = 32; l.bb = 18; l.nplanes = 2;
-      l.pw[0] = 16; l.po[0] = 2; l.pw[1] = 2; l.po[1] = 0;
+      l.pw[0] = 16; l.po[0] = 2; l.pg[0] = 16; l.pw[1] = 2; l.po[1] = 0; l.pg[1] = 2;
+      l.bm = 1;
       break;
     case QK_T_Q8_0:
       l.bs = 32; l.bb = 34; l.nplanes = 2;
-      l.pw[0] = 32; l.po[0] = 2; l.pw[1] = 2; l.po[1] = 0;
+      l.pw[0] = 32; l.po[0] = 2; l.pg[0] = 16; l.pw[1] = 2; l.po[1] = 0; l.pg[1] = 2;
+      l.bm = 1;
       break;
     case QK_T_Q4_K:
       l.bs = 256; l.bb = 144; l.nplanes = 2;
@@ -82,11 +84,14 @@ static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayo
       break;
     case QK_T_Q6_K:
       l.bs = 256; l.bb = 210; l.nplanes = 3;
-      l.pw[0] = 192; l.po[0] = 0; l.pw[1] = 16; l.po[1] = 192; l.pw[2] = 2; l.po[2] = 208;
+      l.pw[0] = 192; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 16; l.po[1] = 192; l.pg[1] = 16;
+      l.pw[2] = 2; l.po[2] = 208; l.pg[2] = 2;
+      l.bm = 1;
       break;
     case QK_T_IQ4_XS:
       l.bs = 256; l.bb = 136; l.nplanes = 2;
-      l.pw[0] = 128; l.po[0] = 8; l.pw[1] = 8; l.po[1] = 0;
+      l.pw[0] = 128; l.po[0] = 8; l.pg[0] = 16; l.pw[1] = 8; l.po[1] = 0; l.pg[1] = 8;
+      l.bm = 1;
       break;
     default:
       return false;
