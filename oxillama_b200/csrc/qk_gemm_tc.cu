@@ -130,7 +130,7 @@ __device__ __forceinline__ void tc_fence_after() {
 // contraction is unchanged.
 //
 //   Pk        the packed bytes of one row-step, held in registers a super-block ahead
-//   load      fetch Pk for (chunk, row-in-chunk rr, group g, super-block s)
+//   load      fetch Pk for (8-row chunk at cb, row-in-chunk rr, group g, super-block s)
 //   prefetch  the same bytes as L2 prefetches
 //   expand    half hf (32 columns) of the row-step -> four 16-byte chunks
 template <int T>
@@ -165,9 +165,12 @@ __device__ __forceinline__ void bytes_to_magic(uint32_t w, uint32_t &lo, uint32_
 }
 // Start of block `blk` (of the row) in the 8-row chunk: tiles are block-major, so the
 // 8 x bb bytes of one block column are one span and block columns follow one another.
-__device__ __forceinline__ const uint8_t *blk_addr(const QkLayout &L, const uint8_t *W, uint32_t chunk,
-                                                   uint32_t blk) {
-  return W + (uint64_t)chunk * L.chunk_bytes + (uint64_t)blk * (QK_TILE_ROWS * L.bb);
+__device__ __forceinline__ const uint8_t *chunk_addr(const QkLayout &L, const uint8_t *W, uint32_t chunk) {
+  return W + (uint64_t)chunk * L.chunk_bytes;
+}
+template <uint32_t BB>
+__device__ __forceinline__ const uint8_t *blk_addr(const uint8_t *chunk_base, uint32_t blk) {
+  return chunk_base + (size_t)(blk * (QK_TILE_ROWS * BB));
 }
 
 template <>
@@ -179,17 +182,16 @@ struct WFmt<QK_T_Q4_K> {  // super-block of 256: d, dmin, 12 bytes of 6-bit scal
     const uint32_t g = p >> 6, i = (p >> 3) & 7u, j = p & 7u, jj = j & 3u;
     return 64 * g + 4 * i + (jj == 1 ? 2 : jj == 2 ? 1 : jj) + 32 * (j >> 2);
   }
-  __device__ static const uint8_t *base(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t s) {
-    return blk_addr(L, W, chunk, s);  // [8 rows x 16 header | 4 groups x 8 rows x 32 nibble bytes]
+  __device__ static const uint8_t *base(const uint8_t *cb, uint32_t s) {
+    return blk_addr<144>(cb, s);  // [8 rows x 16 header | 4 groups x 8 rows x 32 nibble bytes]
   }
-  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
-                              uint32_t g, uint32_t s) {
-    const uint8_t *p = base(L, W, chunk, s);
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g,
+                              uint32_t s) {
+    const uint8_t *p = base(cb, s);
     k.h = ldg16(p + rr * 16), k.q0 = ldg16(p + 128 + g * 256 + rr * 32), k.q1 = ldg16(p + 128 + g * 256 + rr * 32 + 16);
   }
-  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
-                                  uint32_t s) {
-    const uint8_t *p = base(L, W, chunk, s);
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g, uint32_t s) {
+    const uint8_t *p = base(cb, s);
     pf_l2(p + 128 + g * 256 + rr * 32);
     if (g == 0 && rr == 0) pf_l2(p);
   }
@@ -226,13 +228,13 @@ struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
   __host__ __device__ static uint32_t src(uint32_t p) { return p; }
   // Blocks past the end of the row (a last super-block that is not full) read as d = 0, q = 0.
   // A block's 8 rows: [2 granules x 8 rows x 16 int8][8 x d].
-  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
-                              uint32_t g, uint32_t s) {
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g,
+                              uint32_t s) {
     const uint4 z = make_uint4(0, 0, 0, 0);
     k.q[0] = k.q[1] = k.q[2] = k.q[3] = z, k.d2 = 0;
     const uint32_t b = 8 * s + 2 * g;  // first of the row-step's two blocks
     if (b >= L.nb) return;
-    const uint8_t *p = blk_addr(L, W, chunk, b);
+    const uint8_t *p = blk_addr<34>(cb, b);
     k.q[0] = ldg16(p + rr * 16), k.q[1] = ldg16(p + 128 + rr * 16);
     k.d2 = __ldg(reinterpret_cast<const unsigned short *>(p + 256) + rr);
     if (b + 1 < L.nb) {
@@ -240,11 +242,10 @@ struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
       k.d2 |= (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p + 272 + 256) + rr) << 16;
     }
   }
-  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
-                                  uint32_t s) {
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g, uint32_t s) {
     const uint32_t b = 8 * s + 2 * g;
     if (b >= L.nb || rr >= 5) return;
-    pf_l2(blk_addr(L, W, chunk, b) + rr * 128);  // two blocks = 544 bytes = up to five lines
+    pf_l2(blk_addr<34>(cb, b) + rr * 128);  // two blocks = 544 bytes = up to five lines
   }
   struct Sc { __half2 d[2]; };
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
@@ -278,23 +279,22 @@ struct WFmt<QK_T_Q4_0> {  // block of 32: f16 d, 16 bytes; byte j = elements 2 j
     return (p & ~63u) + 32 * (c >> 2) + 8 * (c & 3u) + ((order >> (4 * j)) & 7u);
   }
   // A block's 8 rows: [8 rows x 16 nibble bytes][8 x d].
-  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
-                              uint32_t g, uint32_t s) {
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g,
+                              uint32_t s) {
     k.q[0] = k.q[1] = make_uint4(0, 0, 0, 0), k.d2 = 0;
     const uint32_t b = 8 * s + 2 * g;
     if (b >= L.nb) return;
-    const uint8_t *p = blk_addr(L, W, chunk, b);
+    const uint8_t *p = blk_addr<18>(cb, b);
     k.q[0] = ldg16(p + rr * 16), k.d2 = __ldg(reinterpret_cast<const unsigned short *>(p + 128) + rr);
     if (b + 1 < L.nb) {
       k.q[1] = ldg16(p + 144 + rr * 16);
       k.d2 |= (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p + 144 + 128) + rr) << 16;
     }
   }
-  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
-                                  uint32_t s) {
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g, uint32_t s) {
     const uint32_t b = 8 * s + 2 * g;
     if (b >= L.nb || rr >= 3) return;
-    pf_l2(blk_addr(L, W, chunk, b) + rr * 128);  // two blocks = 288 bytes
+    pf_l2(blk_addr<18>(cb, b) + rr * 128);  // two blocks = 288 bytes
   }
   using Sc = WFmt<QK_T_Q8_0>::Sc;
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
@@ -322,20 +322,19 @@ struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, 
   struct Pk { uint4 ql[4], qh[2]; uint32_t sc4, d; };
   __host__ __device__ static uint32_t src(uint32_t p) { return p; }
   // A block's 8 rows: [12 granules x 8 rows x 16 bytes of ql+qh][8 rows x 16 scales][8 x d].
-  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr,
-                              uint32_t g, uint32_t s) {
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g,
+                              uint32_t s) {
     const uint32_t hh = g >> 1;
-    const uint8_t *p = blk_addr(L, W, chunk, s) + rr * 16;
+    const uint8_t *p = blk_addr<210>(cb, s) + rr * 16;
 #pragma unroll
     for (int i = 0; i < 4; i++) k.ql[i] = ldg16(p + (4 * hh + i) * 128);
     k.qh[0] = ldg16(p + (8 + 2 * hh) * 128), k.qh[1] = ldg16(p + (9 + 2 * hh) * 128);
     k.sc4 = __ldg(reinterpret_cast<const uint32_t *>(p + 1536 + 8 * hh + 4 * (g & 1u)));
     k.d = __ldg(reinterpret_cast<const unsigned short *>(p - rr * 16 + 1664) + rr);
   }
-  __device__ static void prefetch(const QkLayout &L, const uint8_t *W, uint32_t chunk, uint32_t rr, uint32_t g,
-                                  uint32_t s) {
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g, uint32_t s) {
     const uint32_t line = g * 8 + rr;  // 1680 bytes = up to 14 lines, one per thread of the row group
-    if (line < 14) pf_l2(blk_addr(L, W, chunk, s) + line * 128);
+    if (line < 14) pf_l2(blk_addr<210>(cb, s) + line * 128);
   }
   struct Sc { __half2 s[4]; };
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
@@ -368,12 +367,20 @@ struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, 
 // ---------------------------------------------------------------- activations -> fp16
 // X16[t][256 s + p] = x[t][256 s + SRC(p)] in fp16; rows t >= m and columns >= cols are
 // zero.  One thread per 8 output halves (one 16-byte store).
+// With zero_rows != 0 it also clears y[m][zero_rows] (row stride ldy), for the split-K
+// launches, whose tiles add their partial sums into y.
 template <int T>
 __global__ void __launch_bounds__(256)
     qk_x16_kernel(const float *__restrict__ x, uint32_t m, uint32_t cols, uint32_t m_pad,
-                  uint32_t Kp, __half *__restrict__ out) {
+                  uint32_t Kp, __half *__restrict__ out, float *__restrict__ y, uint64_t ldy,
+                  uint32_t zero_rows) {
   pdl_launch_dependents();
   pdl_wait();
+  if (zero_rows) {
+    const uint64_t nz = (uint64_t)m * zero_rows;
+    for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < nz; i += (uint64_t)gridDim.x * 256)
+      y[(i / zero_rows) * ldy + (i % zero_rows)] = 0.f;
+  }
   const uint32_t per_row = Kp / 8;
   const uint64_t total = (uint64_t)m_pad * per_row;
   for (uint64_t it = blockIdx.x * 256ull + threadIdx.x; it < total; it += (uint64_t)gridDim.x * 256) {
@@ -398,14 +405,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     qk_gemm_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
                           const __grid_constant__ CUtensorMap xmap, float *__restrict__ y,
                           uint64_t ldy, uint32_t m_tokens, uint32_t tok_blocks, uint32_t row_blocks,
-                          unsigned *status, GemmSmem S) {
+                          uint32_t KS, unsigned *status, GemmSmem S) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t NB = (uint32_t)S.b_stages;
-  const uint32_t nsb = (L.cols + 255u) / 256u;  // super-blocks (256 columns) along K
-  const uint32_t steps = nsb * 4;       // 64-column stages per tile
-  const uint32_t n_tiles = tok_blocks * row_blocks;
+  const uint32_t nsb_all = (L.cols + 255u) / 256u;  // super-blocks (256 columns) along K
+  // Work unit t = (tile t % n_tiles, K split t / n_tiles): with KS > 1 a tile's K range is cut
+  // into KS runs of super-blocks, done by different CTAs, which add their partial sums into y.
+  const uint32_t n_tiles = tok_blocks * row_blocks, n_units = n_tiles * KS;
+  auto sb_begin = [&](uint32_t t) { return (t / n_tiles) * nsb_all / KS; };
+  auto sb_end = [&](uint32_t t) { return (t / n_tiles + 1) * nsb_all / KS; };
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   // Accumulators: RH of BN columns per tile.  Where tensor memory holds two sets, the
   // MMAs of tile i+1 overlap the epilogue of tile i.  Every MMA accumulates; the
@@ -463,9 +473,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // waiting for use u can never mistake the completion of use u - 2 for it.
     if (lane == 0) {
       uint32_t st = 0, use = 0, gstep = 0;
-      for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x) {
-        const uint32_t tb = t % tok_blocks;
-        for (uint32_t step = 0; step < steps; step++, gstep++) {
+      for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
+        const uint32_t tb = (t % n_tiles) % tok_blocks;
+        for (uint32_t step = sb_begin(t) * 4; step < sb_end(t) * 4; step++, gstep++) {
           if (use >= 1 && !mbar_wait_bounded(sbase + S.b_empty + st * 8, (use - 1) & 1u)) {
             dead = true;
             break;
@@ -492,8 +502,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       uint32_t bst = me % NB, buse = me / NB, usea = 0, i = 0;
       const uint32_t abar = sbase + S.a_full + me * RH * 2 * 8, aebar = sbase + S.a_empty + me * RH * 2 * 8;
       const uint32_t a0 = sbase + S.a + me * RH * 2 * A_HALF;
-      for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x, i++) {
-        const uint32_t buf = i % NBUF, use = i / NBUF;
+      for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x, i++) {
+        const uint32_t buf = i % NBUF, use = i / NBUF, nsb = sb_end(t) - sb_begin(t);
         // the epilogue of the tile that last used these accumulators must have drained and zeroed them
         if (use >= 1 && !mbar_wait_bounded(sbase + S.acc_empty + buf * 8, (use - 1) & 1u)) {
           dead = true;
@@ -587,9 +597,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                        : "memory");
         if (row < L.rows) {
           float *yp = y + (uint64_t)(epi_tb * BN + c0) * ldy + row;
+          if (KS == 1) {
 #pragma unroll
-          for (int j = 0; j < 16; j++)
-            if (epi_tb * BN + c0 + j < m_tokens) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; j++)
+              if (epi_tb * BN + c0 + j < m_tokens) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+              if (epi_tb * BN + c0 + j < m_tokens) atomicAdd(yp + (uint64_t)j * ldy, __uint_as_float(v[j]));
+          }
         }
       }
       if (++epi_next == NCH) {
@@ -608,32 +624,42 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     using F = WFmt<T>;
     constexpr uint32_t PF_AHEAD = 6;
     auto chunk_of = [&](uint32_t t, int rh) -> uint32_t {
-      const uint32_t chunk = ((t / tok_blocks) * RH + rh) * 16 + chunk_in_half;
+      const uint32_t chunk = (((t % n_tiles) / tok_blocks) * RH + rh) * 16 + chunk_in_half;
       return chunk < L.chunks ? chunk : L.chunks - 1;  // rows past the end: valid bytes, results unused
     };
     uint32_t it = 0, u = 0;  // u: super-blocks done = uses of each of this group's A units
     // cursor of the next super-block to load, and of the next one to prefetch
-    uint32_t lt = blockIdx.x, lsb = 0, pt = blockIdx.x, psb = 0;
+    uint32_t lt = blockIdx.x, pt = blockIdx.x;
+    uint32_t lsb = 0, lse = 0, psb = 0, pse = 0;  // runs [lsb, lse), [psb, pse) of super-blocks
+    const uint8_t *lchunk[RH], *pchunk[RH];       // and where their 8-row chunks start
+    auto enter = [&](uint32_t t, uint32_t &sb, uint32_t &se, const uint8_t **chunk) {
+      if (t >= n_units) return;
+      sb = sb_begin(t), se = sb_end(t);
+#pragma unroll
+      for (int rh = 0; rh < RH; rh++) chunk[rh] = chunk_addr(L, W, chunk_of(t, rh));
+    };
+    enter(lt, lsb, lse, lchunk), enter(pt, psb, pse, pchunk);
     typename F::Pk nk[RH];
     auto load_next = [&]() {
-      if (lt >= n_tiles) return;
+      if (lt >= n_units) return;
 #pragma unroll
-      for (int rh = 0; rh < RH; rh++) F::load(nk[rh], L, W, chunk_of(lt, rh), rr, grp, lsb);
-      if (++lsb == nsb) lsb = 0, lt += gridDim.x;
+      for (int rh = 0; rh < RH; rh++) F::load(nk[rh], L, lchunk[rh], rr, grp, lsb);
+      if (++lsb == lse) lt += gridDim.x, enter(lt, lsb, lse, lchunk);
     };
     auto prefetch_next = [&](bool issue) {
-      if (pt >= n_tiles) return;
+      if (pt >= n_units) return;
       if (issue) {
 #pragma unroll
-        for (int rh = 0; rh < RH; rh++) F::prefetch(L, W, chunk_of(pt, rh), rr, grp, psb);
+        for (int rh = 0; rh < RH; rh++) F::prefetch(L, pchunk[rh], rr, grp, psb);
       }
-      if (++psb == nsb) psb = 0, pt += gridDim.x;
+      if (++psb == pse) pt += gridDim.x, enter(pt, psb, pse, pchunk);
     };
     load_next();
     for (uint32_t k = 0; k <= PF_AHEAD; k++) prefetch_next(k > 0);
 
-    for (uint32_t t = blockIdx.x; t < n_tiles && !dead; t += gridDim.x, it++) {
-      const uint32_t rb = t / tok_blocks, tb = t % tok_blocks;
+    for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x, it++) {
+      const uint32_t rb = (t % n_tiles) / tok_blocks, tb = (t % n_tiles) % tok_blocks;
+      const uint32_t nsb = sb_end(t) - sb_begin(t);
       for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, u++) {
         typename F::Pk pk[RH];
 #pragma unroll
@@ -785,15 +811,28 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   cudaLaunchConfig_t c0 = {};
   c0.gridDim = dim3((unsigned)((n8 + 255) / 256 > 148 * 8 ? 148 * 8 : (n8 + 255) / 256));
   c0.blockDim = dim3(256), c0.stream = s, c0.attrs = at, c0.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16);
+  // Split K when the tiles alone would leave most SMs idle.  Partial sums meet in y
+  // through atomic adds: bit-reproducible for two splits (a + b = b + a), order of
+  // rounding not fixed for more.
+  const uint32_t n_tiles = tok_blocks * row_blocks, nsb = Kp / 256u;
+  uint32_t ks = 1;
+  if (n_tiles * 4 < (uint32_t)sm_count * 3) ks = (uint32_t)sm_count / n_tiles;
+  if (ks > 8) ks = 8;
+  if (ks > nsb) ks = nsb;
+  if (const char *ev = getenv("QK_GEMM_KS")) {
+    const uint32_t v = (uint32_t)atoi(ev);
+    if (v >= 1 && v <= 8 && v <= nsb) ks = v;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16, y, ldy,
+                                     ks > 1 ? L.rows : 0u);
   if (e != cudaSuccess) return e;
 
-  uint32_t grid = tok_blocks * row_blocks;
+  uint32_t grid = n_tiles * ks;
   if (grid > (uint32_t)sm_count) grid = sm_count;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NTHREADS), cfg.dynamicSmemBytes = total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, map, y, ldy, m, tok_blocks, row_blocks, status, S);
+  return cudaLaunchKernelEx(&cfg, kern, L, W, map, y, ldy, m, tok_blocks, row_blocks, ks, status, S);
 }
 
 int pick_bn(uint32_t m) { return m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }

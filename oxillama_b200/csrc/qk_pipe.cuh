@@ -4,6 +4,10 @@
 #include <cstdint>
 #include <cuda_fp16.h>
 
+#ifndef QK_PARK_NS
+#define QK_PARK_NS 20000u  // how long a waiting thread may stay parked per poll
+#endif
+
 namespace qkpipe {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -57,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
     for (int i = 0; i < 256; i++)
-      if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+      if (mbar_try_wait_parked(bar, parity, QK_PARK_NS)) return true;
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     if (t - t0 > 250000000ull) return false;
