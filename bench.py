@@ -53,6 +53,54 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    """Dense 16-bit tensor-core peak (TFLOP/s) for a kernel timed alone: the measured burst figure."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+def prefill_rate(torch, ctx, qtype, rows, cols, m, stream, launches=96):
+    """Batched matmul (prefill) of one weight shape: TFLOP/s over graph-replayed launches that
+    rotate through enough weight copies to exceed L2; everything resident in HBM."""
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    nbytes = S.weight_nbytes(qtype, rows, cols)
+    ring = max(2, min(16, int(300e6 / nbytes) + 1))
+    base = S.gen_weight(qtype, rows, cols, seed=0, stream=97)
+    dws = [DeviceWeights(qtype, base, rows, cols, ctx=ctx) for _ in range(ring)]
+    x = torch.from_numpy(S.gen_acts(m, cols, seed=1)).cuda()
+    y = torch.empty(m, rows, device="cuda")
+    with torch.cuda.stream(stream):
+        for d in dws:
+            d.gemm(x, y, m)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for d in dws:
+                d.gemm(x, y, m)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        iters = max(1, launches // ring)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        check_device_status(ctx, stream)
+    us = e0.elapsed_time(e1) * 1e3 / (iters * ring)
+    for d in dws:
+        d.free()
+    peak, which = tensor_peak()
+    tf = 2.0 * m * rows * cols / us / 1e6
+    return {"workload": f"{S.NAMES[qtype]} {rows}x{cols} weight x {m} tokens (f32 in, f32 out)", "tflops": tf,
+            "us_per_launch": us, "peak_tflops": peak, "peak_source": which, "frac": tf / peak,
+            "operands": "fp16 (weights dequantised in the kernel), f32 accumulation in TMEM",
+            "launches": iters * ring, "ring_copies": ring}
+
+
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -251,6 +299,11 @@ def run_ours(args):
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- prefill (batched matmul) on the tensor cores: reported beside the headline metric
+    prefill = None
+    if rank == 0 and not args.no_prefill:
+        prefill = [prefill_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream),
+                   prefill_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream)]
     t = torch.tensor([ms, e2e_s * 1e3, kernel_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -278,6 +331,7 @@ def run_ours(args):
         }
         if world == 1:
             line["cpu_baseline"] = cpu_gemv_rate(args.cpu_seconds)
+        line["prefill"] = prefill
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -291,6 +345,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-graph", action="store_true", help="launch every matvec from the host")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the batched-matmul measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

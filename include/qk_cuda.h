@@ -143,6 +143,28 @@ int qk_matvec_q8_fused_dev(qk_ctx *ctx, const qk_weights *h, const uint8_t *acts
 /* Q8_0 activation encoder on device memory; n a multiple of 32. */
 int qk_quantize_q8_0_dev(qk_ctx *ctx, const float *x_dev, size_t n, uint8_t *out_dev, void *stream);
 
+/* ---- mixture-of-experts FFN: MoeFfn::forward (crates/oxillama-arch/src/common/moe.rs:184-258) ---- */
+
+/* Routing alone (moe.rs:200-248): per token the softmax over all n_exp logits, the
+ * top_k experts in descending order of probability (ties to the lower expert id) and
+ * their weights renormalised by the selected sum.  ids_dev / wts_dev are
+ * [tokens x top_k]; with top_k > n_exp the extra slots get id -1 and weight 0. */
+int qk_moe_route_dev(qk_ctx *ctx, const float *logits_dev, size_t tokens, size_t n_exp, size_t top_k,
+                     int *ids_dev, float *wts_dev, void *stream);
+
+/* y_dev[tokens x hidden] = sum over the n_local experts held here (global ids
+ * expert_begin .. expert_begin + n_local) of  w(token, e) * down_e(silu(gate_e x) * up_e x)
+ * for the tokens routed to them (Expert::forward, moe.rs:75-126); y_dev is overwritten.
+ * gate[e], up[e] are [inter x hidden] shards, down[e] is [hidden x inter].  With every
+ * expert local this is MoeFfn::forward given the router's logits; an expert-sharded
+ * layer sums the y of its ranks.  logits_dev is [tokens x n_exp], x_dev [tokens x hidden].
+ * The call synchronises `stream` once (the per-expert token counts size its matmuls) and
+ * keeps its own device scratch, grown on first use. */
+int qk_moe_ffn_dev(qk_ctx *ctx, const qk_weights *const *gate, const qk_weights *const *up,
+                   const qk_weights *const *down, size_t n_local, size_t expert_begin, size_t n_exp,
+                   const float *logits_dev, const float *x_dev, float *y_dev, size_t tokens,
+                   size_t top_k, void *stream);
+
 /* No counterpart in the reference.  qk_gemm_dev for Q4_K shards and m <= 4 that
  * allocates nothing: for callers that cannot allocate device memory once running
  * (a server that handed all of HBM to its own pools, a process under a fixed

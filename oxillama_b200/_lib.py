@@ -40,6 +40,8 @@ SIGNATURES = {
     "qk_matvec_q8_fused_dev": (C.c_int, [vp, vp, vp, vp, vp]),
     "qk_quantize_q8_0_dev": (C.c_int, [vp, vp, sz, vp, vp]),
     "qk_gemm_dev_noalloc": (C.c_int, [vp, vp, vp, vp, sz, sz, vp]),
+    "qk_moe_route_dev": (C.c_int, [vp, vp, sz, sz, sz, vp, vp, vp]),
+    "qk_moe_ffn_dev": (C.c_int, [vp, vp, vp, vp, sz, sz, sz, vp, vp, vp, sz, sz, vp]),
     "qk_check_device_status": (C.c_int, [vp, vp]),
 }
 

@@ -10,6 +10,8 @@
 #include <string>
 #include <tuple>
 
+#include <vector>
+
 #include "qk_internal.h"
 
 #define CK(ctx, call)                                                                     \
@@ -117,6 +119,7 @@ extern "C" int qk_shutdown(qk_ctx *c) {
   if (c->sb) cudaFree(c->sb);
   cudaFree(c->status_dev);
   if (c->scratch) cudaFree(c->scratch);
+  if (c->moe) cudaFree(c->moe);
   cudaStreamDestroy(c->stream);
   delete c;
   return QK_OK;
@@ -333,6 +336,77 @@ extern "C" int qk_gemm_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, f
   if (h->device != c->device) return QK_INVALID_ARGUMENT;
   if (ldy < h->L.rows) return QK_DIMENSION_MISMATCH;
   return gemm_dispatch(c, h, x_dev, y_dev, m, ldy, (cudaStream_t)stream);
+}
+
+extern "C" int qk_moe_route_dev(qk_ctx *c, const float *logits_dev, size_t tokens, size_t n_exp,
+                                size_t top_k, int *ids_dev, float *wts_dev, void *stream) {
+  if (!c || !logits_dev || !ids_dev || !wts_dev) return QK_INVALID_ARGUMENT;
+  if (n_exp == 0 || top_k == 0 || n_exp > 4096) return QK_INVALID_ARGUMENT;
+  CK(c, qk_launch_moe_route(logits_dev, (uint32_t)tokens, (uint32_t)n_exp, (uint32_t)top_k, ids_dev, wts_dev,
+                            (cudaStream_t)stream));
+  return QK_OK;
+}
+
+extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk_weights *const *up,
+                              const qk_weights *const *down, size_t n_local, size_t expert_begin,
+                              size_t n_exp, const float *logits_dev, const float *x_dev, float *y_dev,
+                              size_t tokens, size_t top_k, void *stream) {
+  if (!c || !logits_dev || !x_dev || !y_dev || (n_local && (!gate || !up || !down))) return QK_INVALID_ARGUMENT;
+  if (n_exp == 0 || top_k == 0 || n_exp > 4096 || expert_begin + n_local > n_exp) return QK_INVALID_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  size_t hidden = 0, inter = 0;
+  for (size_t e = 0; e < n_local; e++) {
+    if (!gate[e] || !up[e] || !down[e]) return QK_INVALID_ARGUMENT;
+    if (gate[e]->device != c->device || up[e]->device != c->device || down[e]->device != c->device)
+      return QK_INVALID_ARGUMENT;
+    if (e == 0) hidden = gate[e]->L.cols, inter = gate[e]->L.rows;
+    if (gate[e]->L.cols != hidden || gate[e]->L.rows != inter || up[e]->L.cols != hidden ||
+        up[e]->L.rows != inter || down[e]->L.cols != inter || down[e]->L.rows != hidden)
+      return QK_DIMENSION_MISMATCH;
+  }
+  if (n_local == 0 || tokens == 0) return QK_OK;
+  const size_t slots = tokens * top_k;
+  // scratch: ids, wts, counts, lists, then the per-expert activations (sized for every token)
+  auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t o_ids = 0, o_wts = o_ids + al(slots * 4), o_cnt = o_wts + al(slots * 4);
+  const size_t o_lists = o_cnt + al(n_local * 4), o_xe = o_lists + al(n_local * slots * 4);
+  const size_t o_g = o_xe + al(tokens * hidden * 4), o_u = o_g + al(tokens * inter * 4);
+  const size_t o_o = o_u + al(tokens * inter * 4), need = o_o + al(tokens * hidden * 4);
+  if (need > c->moe_cap) {
+    CK(c, cudaDeviceSynchronize());
+    if (c->moe) cudaFree(c->moe);
+    c->moe = nullptr, c->moe_cap = 0;
+    CK(c, cudaMalloc(&c->moe, need));
+    c->moe_cap = need;
+  }
+  unsigned char *base = (unsigned char *)c->moe;
+  int *ids = (int *)(base + o_ids), *cnt = (int *)(base + o_cnt), *lists = (int *)(base + o_lists);
+  float *wts = (float *)(base + o_wts), *xe = (float *)(base + o_xe), *g = (float *)(base + o_g);
+  float *u = (float *)(base + o_u), *o = (float *)(base + o_o);
+
+  CK(c, cudaMemsetAsync(y_dev, 0, tokens * hidden * sizeof(float), s));
+  CK(c, qk_launch_moe_route(logits_dev, (uint32_t)tokens, (uint32_t)n_exp, (uint32_t)top_k, ids, wts, s));
+  CK(c, qk_launch_moe_lists(ids, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)expert_begin, (uint32_t)n_local,
+                            cnt, lists, s));
+  // the token counts size the per-expert matmuls: one small copy and a stream synchronise
+  std::vector<int> counts(n_local);
+  CK(c, cudaMemcpyAsync(counts.data(), cnt, n_local * sizeof(int), cudaMemcpyDeviceToHost, s));
+  CK(c, cudaStreamSynchronize(s));
+  for (size_t e = 0; e < n_local; e++) {
+    const size_t m = (size_t)counts[e];
+    if (m == 0) continue;
+    const int *list = lists + e * slots;
+    CK(c, qk_launch_moe_gather(x_dev, list, (uint32_t)m, (uint32_t)top_k, (uint32_t)hidden, xe, s));
+    int st = gemm_dispatch(c, gate[e], xe, g, m, inter, s);
+    if (st) return st;
+    st = gemm_dispatch(c, up[e], xe, u, m, inter, s);
+    if (st) return st;
+    CK(c, qk_launch_moe_silu_mul(g, u, (uint64_t)m * inter, s));
+    st = gemm_dispatch(c, down[e], u, o, m, hidden, s);
+    if (st) return st;
+    CK(c, qk_launch_moe_scatter(o, list, wts, (uint32_t)m, (uint32_t)top_k, (uint32_t)hidden, y_dev, s));
+  }
+  return QK_OK;
 }
 
 extern "C" int qk_dequant_dev(qk_ctx *c, const qk_weights *h, float *out_dev, void *stream) {

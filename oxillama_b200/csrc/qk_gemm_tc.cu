@@ -39,6 +39,7 @@
 // frees its tensor memory.
 #include <cuda.h>
 
+#include <cfloat>
 #include <cstdlib>
 
 #include "qk_kernels.h"
@@ -365,15 +366,20 @@ struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, 
 };
 
 // ---------------------------------------------------------------- activations -> fp16
-// X16[t][256 s + p] = x[t][256 s + SRC(p)] in fp16; rows t >= m and columns >= cols are
-// zero.  One thread per 8 output halves (one 16-byte store).
+// X16[t][256 s + p] = x[t][256 s + SRC(p)] / scale[t] in fp16, where scale[t] is the power
+// of two that puts the row's largest magnitude in [512, 1024): the division is exact, no
+// activation overflows or falls into fp16's subnormals, and the epilogue multiplies the
+// row of results by scale[t] again (also exact).  Rows t >= m and columns >= cols are
+// zero.  One CTA per token row at a time: a pass for the maximum, a pass to convert.
 // With zero_rows != 0 it also clears y[m][zero_rows] (row stride ldy), for the split-K
 // launches, whose tiles add their partial sums into y.
 template <int T>
 __global__ void __launch_bounds__(256)
     qk_x16_kernel(const float *__restrict__ x, uint32_t m, uint32_t cols, uint32_t m_pad,
-                  uint32_t Kp, __half *__restrict__ out, float *__restrict__ y, uint64_t ldy,
-                  uint32_t zero_rows) {
+                  uint32_t Kp, __half *__restrict__ out, float *__restrict__ scales,
+                  float *__restrict__ y, uint64_t ldy, uint32_t zero_rows, uint32_t cached) {
+  extern __shared__ __align__(16) float row[];  // the row, when it fits (cached != 0)
+  __shared__ float red[8];
   pdl_launch_dependents();
   pdl_wait();
   if (zero_rows) {
@@ -382,18 +388,53 @@ __global__ void __launch_bounds__(256)
       y[(i / zero_rows) * ldy + (i % zero_rows)] = 0.f;
   }
   const uint32_t per_row = Kp / 8;
-  const uint64_t total = (uint64_t)m_pad * per_row;
-  for (uint64_t it = blockIdx.x * 256ull + threadIdx.x; it < total; it += (uint64_t)gridDim.x * 256) {
-    const uint32_t t = (uint32_t)(it / per_row), c = (uint32_t)(it % per_row);
-    __align__(16) __half h[8];
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-      const uint32_t p = 8 * c + j;
-      const uint32_t k = (p & ~255u) + WFmt<T>::src(p & 255u);
-      const float v = (t < m && k < cols) ? __ldg(x + (uint64_t)t * cols + k) : 0.f;
-      h[j] = __float2half_rn(v);
+  const bool vec = (cols & 3u) == 0 && ((uintptr_t)x & 15u) == 0;  // rows start 16-byte aligned
+  for (uint32_t t = blockIdx.x; t < m_pad; t += gridDim.x) {
+    const float *xr = x + (uint64_t)t * cols;
+    float amax = 0.f;
+    __syncthreads();  // the previous row's readers of `row` and `red` are done
+    if (t < m) {
+      if (vec) {
+        for (uint32_t k = threadIdx.x * 4; k < cols; k += 1024) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + k));
+          amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+          if (cached) *reinterpret_cast<float4 *>(row + k) = v;
+        }
+      } else {
+        for (uint32_t k = threadIdx.x; k < cols; k += 256) {
+          const float v = __ldg(xr + k);
+          amax = fmaxf(amax, fabsf(v));
+          if (cached) row[k] = v;
+        }
+      }
     }
-    *reinterpret_cast<uint4 *>(out + (uint64_t)t * Kp + 8ull * c) = *reinterpret_cast<const uint4 *>(h);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) amax = fmaxf(amax, red[w]);
+    float scale = 1.f;
+    if (amax > 0.f && amax <= FLT_MAX) {  // finite and non-zero (a NaN row keeps scale 1 and stays NaN)
+      int e;
+      frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
+      scale = ldexpf(1.f, e - 10);
+    }
+    const float inv = 1.f / scale;  // a power of two: exact
+    if (threadIdx.x == 0) scales[t] = scale;
+    for (uint32_t c = threadIdx.x; c < per_row; c += 256) {
+      __align__(16) __half h[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const uint32_t p = 8 * c + j;
+        const uint32_t k = (p & ~255u) + WFmt<T>::src(p & 255u);
+        float v = 0.f;
+        if (t < m && k < cols) v = (cached ? row[k] : __ldg(xr + k)) * inv;
+        h[j] = __float2half_rn(v);
+      }
+      *reinterpret_cast<uint4 *>(out + (uint64_t)t * Kp + 8ull * c) = *reinterpret_cast<const uint4 *>(h);
+    }
   }
 }
 
@@ -403,8 +444,8 @@ __global__ void __launch_bounds__(256)
 template <int T, int BN, int RH>
 __global__ void __launch_bounds__(NTHREADS, 1)
     qk_gemm_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
-                          const __grid_constant__ CUtensorMap xmap, float *__restrict__ y,
-                          uint64_t ldy, uint32_t m_tokens, uint32_t tok_blocks, uint32_t row_blocks,
+                          const __grid_constant__ CUtensorMap xmap, const float *__restrict__ xscale,
+                          float *__restrict__ y, uint64_t ldy, uint32_t m_tokens, uint32_t tok_blocks, uint32_t row_blocks,
                           uint32_t KS, unsigned *status, GemmSmem S) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -597,14 +638,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                        : "memory");
         if (row < L.rows) {
           float *yp = y + (uint64_t)(epi_tb * BN + c0) * ldy + row;
+          const float *sp = xscale + epi_tb * BN + c0;  // the tokens' activation scales (inside the padded array)
           if (KS == 1) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (epi_tb * BN + c0 + j < m_tokens) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]);
+              if (epi_tb * BN + c0 + j < m_tokens) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]) * __ldg(sp + j);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (epi_tb * BN + c0 + j < m_tokens) atomicAdd(yp + (uint64_t)j * ldy, __uint_as_float(v[j]));
+              if (epi_tb * BN + c0 + j < m_tokens)
+                atomicAdd(yp + (uint64_t)j * ldy, __uint_as_float(v[j]) * __ldg(sp + j));
           }
         }
       }
@@ -793,6 +836,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   const uint32_t tok_blocks = (m + BN - 1) / BN, m_pad = tok_blocks * BN;
   const uint32_t row_blocks = (L.rows + RH * BM - 1) / (RH * BM);
   __half *x16 = reinterpret_cast<__half *>(scratch);
+  float *xscale = reinterpret_cast<float *>(scratch + (((size_t)m_pad * Kp * 2 + 255) & ~(size_t)255));
 
   CUtensorMap map;
   cuuint64_t dims[2] = {Kp, m_pad};
@@ -809,7 +853,8 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   at[0].val.programmaticStreamSerializationAllowed = 1;
   const uint64_t n8 = (uint64_t)m_pad * (Kp / 8);
   cudaLaunchConfig_t c0 = {};
-  c0.gridDim = dim3((unsigned)((n8 + 255) / 256 > 148 * 8 ? 148 * 8 : (n8 + 255) / 256));
+  (void)n8;
+  c0.gridDim = dim3(m_pad > 148u * 8u ? 148u * 8u : m_pad);
   c0.blockDim = dim3(256), c0.stream = s, c0.attrs = at, c0.numAttrs = 1;
   // Split K when the tiles alone would leave most SMs idle.  Partial sums meet in y
   // through atomic adds: bit-reproducible for two splits (a + b = b + a), order of
@@ -823,8 +868,17 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
     const uint32_t v = (uint32_t)atoi(ev);
     if (v >= 1 && v <= 8 && v <= nsb) ks = v;
   }
-  cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16, y, ldy,
-                                     ks > 1 ? L.rows : 0u);
+  // the row is staged in shared memory between the maximum pass and the conversion when it fits
+  const uint32_t row_bytes = L.cols * 4u, cached = row_bytes <= 96u * 1024u ? 1u : 0u;
+  static bool x16_attr = false;
+  if (!x16_attr) {
+    cudaError_t ea = cudaFuncSetAttribute(qk_x16_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (ea != cudaSuccess) return ea;
+    x16_attr = true;
+  }
+  c0.dynamicSmemBytes = cached ? ((row_bytes + 15u) & ~15u) : 0u;
+  cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16, xscale, y, ldy,
+                                     ks > 1 ? L.rows : 0u, cached);
   if (e != cudaSuccess) return e;
 
   uint32_t grid = n_tiles * ks;
@@ -832,7 +886,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NTHREADS), cfg.dynamicSmemBytes = total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, map, y, ldy, m, tok_blocks, row_blocks, ks, status, S);
+  return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_blocks, row_blocks, ks, status, S);
 }
 
 int pick_bn(uint32_t m) { return m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
@@ -869,7 +923,8 @@ bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m) {
 size_t qk_gemm_tc_scratch_bytes(const QkLayout &L, uint32_t m) {
   const int bn = pick_bn(m);
   const uint64_t m_pad = ((m + bn - 1) / bn) * (uint64_t)bn;
-  return (size_t)(m_pad * ((L.cols + 255ull) / 256ull) * 256ull * 2ull);
+  const size_t x16 = (size_t)(m_pad * ((L.cols + 255ull) / 256ull) * 256ull * 2ull);
+  return ((x16 + 255) & ~(size_t)255) + (size_t)m_pad * 4;  // fp16 activations, then one scale per token
 }
 
 cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,

@@ -34,5 +34,8 @@ struct qk_ctx {
   std::map<Key, qk_weights *> cache;
   size_t cache_bytes = 0, cache_cap = (size_t)64 << 30;
   bool force_simple = false;
+  // scratch of qk_moe_ffn_dev (routing tables and per-expert activations); grown on demand
+  void *moe = nullptr;
+  size_t moe_cap = 0;
 };
 

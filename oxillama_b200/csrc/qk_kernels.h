@@ -44,3 +44,14 @@ size_t qk_gemm_tc_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                               uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                               int sm_count, cudaStream_t s);
+
+// Mixture-of-experts glue (routing, token lists, gather, silu * up, weighted scatter-add).
+cudaError_t qk_launch_moe_route(const float *logits, uint32_t tokens, uint32_t n_exp, uint32_t top_k,
+                                int *ids, float *wts, cudaStream_t s);
+cudaError_t qk_launch_moe_lists(const int *ids, uint32_t tokens, uint32_t top_k, uint32_t expert_begin,
+                                uint32_t n_local, int *counts, int *lists, cudaStream_t s);
+cudaError_t qk_launch_moe_gather(const float *x, const int *list, uint32_t n, uint32_t top_k,
+                                 uint32_t hidden, float *xe, cudaStream_t s);
+cudaError_t qk_launch_moe_silu_mul(const float *g, float *u, uint64_t n, cudaStream_t s);
+cudaError_t qk_launch_moe_scatter(const float *o, const int *list, const float *wts, uint32_t n,
+                                  uint32_t top_k, uint32_t hidden, float *y, cudaStream_t s);

@@ -1,0 +1,132 @@
+// Mixture-of-experts FFN around the quantized matmuls (crates/oxillama-arch/src/common/moe.rs:184-258):
+// routing, the per-expert token lists, and the element-wise steps between the three
+// matmuls of an expert (moe.rs:75-126).  The matmuls themselves are the ordinary
+// dequant-matmul kernels, run once per expert on the tokens routed to it.
+#include <cfloat>
+
+#include "qk_kernels.h"
+
+namespace {
+
+// One thread per token: softmax over all experts, the top_k largest in descending order
+// (equal values keep ascending expert order, as a stable sort would), weights
+// renormalised by the selected sum (moe.rs:200-248).
+__global__ void __launch_bounds__(128)
+    qk_moe_route_kernel(const float *__restrict__ logits, uint32_t tokens, uint32_t n_exp,
+                        uint32_t top_k, int *__restrict__ ids, float *__restrict__ wts) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const float *l = logits + (uint64_t)t * n_exp;
+  const uint32_t ek = top_k < n_exp ? top_k : n_exp;
+  float mx = -INFINITY;
+  for (uint32_t i = 0; i < n_exp; i++) mx = fmaxf(mx, l[i]);
+  float es = 0.f;
+  for (uint32_t i = 0; i < n_exp; i++) es = __fadd_rn(es, expf(__fsub_rn(l[i], mx)));
+  auto prob = [&](uint32_t i) {
+    const float e = expf(__fsub_rn(l[i], mx));
+    return es > 0.f ? __fdiv_rn(e, es) : __fdiv_rn(1.f, (float)n_exp);
+  };
+  float ssum = 0.f;
+  for (uint32_t k = 0; k < ek; k++) {  // k-th largest not yet taken; ties to the lower index
+    float best = -1.f;
+    uint32_t bi = 0;
+    for (uint32_t i = 0; i < n_exp; i++) {
+      bool taken = false;
+      for (uint32_t j = 0; j < k; j++) taken |= ids[(uint64_t)t * top_k + j] == (int)i;
+      const float p = prob(i);
+      if (!taken && p > best) best = p, bi = i;
+    }
+    ids[(uint64_t)t * top_k + k] = (int)bi;
+    wts[(uint64_t)t * top_k + k] = best;
+    ssum = __fadd_rn(ssum, best);
+  }
+  for (uint32_t k = 0; k < ek; k++) {
+    float &w = wts[(uint64_t)t * top_k + k];
+    w = ssum > 1e-9f ? __fdiv_rn(w, ssum) : __fdiv_rn(1.f, (float)ek);
+  }
+  for (uint32_t k = ek; k < top_k; k++) ids[(uint64_t)t * top_k + k] = -1, wts[(uint64_t)t * top_k + k] = 0.f;
+}
+
+// One warp per local expert: the (token, slot) pairs routed to it, in token order.
+__global__ void __launch_bounds__(32)
+    qk_moe_lists_kernel(const int *__restrict__ ids, uint32_t tokens, uint32_t top_k,
+                        uint32_t expert_begin, int *__restrict__ counts, int *__restrict__ lists) {
+  const uint32_t e = blockIdx.x, lane = threadIdx.x;
+  const int want = (int)(expert_begin + e);
+  const uint64_t n = (uint64_t)tokens * top_k;
+  uint32_t count = 0;
+  for (uint64_t base = 0; base < n; base += 32) {
+    const uint64_t i = base + lane;
+    const bool hit = i < n && ids[i] == want;
+    const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+    if (hit) lists[(uint64_t)e * n + count + __popc(mask & ((1u << lane) - 1u))] = (int)i;
+    count += __popc(mask);
+  }
+  if (lane == 0) counts[e] = (int)count;
+}
+
+__global__ void __launch_bounds__(256)
+    qk_moe_gather_kernel(const float *__restrict__ x, const int *__restrict__ list, uint32_t n,
+                         uint32_t top_k, uint32_t hidden, float *__restrict__ xe) {
+  const uint32_t i = blockIdx.x;
+  if (i >= n) return;
+  const float *src = x + (uint64_t)(list[i] / (int)top_k) * hidden;
+  for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) xe[(uint64_t)i * hidden + c] = src[c];
+}
+
+// u <- silu(g) * u  (moe.rs:96-112: g * sigmoid(g), then times up)
+__global__ void __launch_bounds__(256)
+    qk_moe_silu_mul_kernel(const float *__restrict__ g, float *__restrict__ u, uint64_t n) {
+  for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += (uint64_t)gridDim.x * 256) {
+    const float v = g[i];
+    const float sig = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v)));
+    u[i] = __fmul_rn(u[i], __fmul_rn(v, sig));
+  }
+}
+
+// y[token] += w * o[i]; a token occurs at most once in one expert's list.
+__global__ void __launch_bounds__(256)
+    qk_moe_scatter_kernel(const float *__restrict__ o, const int *__restrict__ list,
+                          const float *__restrict__ wts, uint32_t n, uint32_t top_k, uint32_t hidden,
+                          float *__restrict__ y) {
+  const uint32_t i = blockIdx.x;
+  if (i >= n) return;
+  const int slot = list[i];
+  const float w = wts[slot];
+  float *dst = y + (uint64_t)(slot / (int)top_k) * hidden;
+  for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x)
+    dst[c] = __fadd_rn(dst[c], __fmul_rn(w, o[(uint64_t)i * hidden + c]));
+}
+
+}  // namespace
+
+cudaError_t qk_launch_moe_route(const float *logits, uint32_t tokens, uint32_t n_exp, uint32_t top_k,
+                                int *ids, float *wts, cudaStream_t s) {
+  if (tokens == 0) return cudaSuccess;
+  qk_moe_route_kernel<<<(tokens + 127) / 128, 128, 0, s>>>(logits, tokens, n_exp, top_k, ids, wts);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_lists(const int *ids, uint32_t tokens, uint32_t top_k, uint32_t expert_begin,
+                                uint32_t n_local, int *counts, int *lists, cudaStream_t s) {
+  if (n_local == 0) return cudaSuccess;
+  qk_moe_lists_kernel<<<n_local, 32, 0, s>>>(ids, tokens, top_k, expert_begin, counts, lists);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_gather(const float *x, const int *list, uint32_t n, uint32_t top_k,
+                                 uint32_t hidden, float *xe, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  qk_moe_gather_kernel<<<n, 256, 0, s>>>(x, list, n, top_k, hidden, xe);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_silu_mul(const float *g, float *u, uint64_t n, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const uint64_t blocks = (n + 255) / 256;
+  qk_moe_silu_mul_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, s>>>(g, u, n);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_scatter(const float *o, const int *list, const float *wts, uint32_t n,
+                                  uint32_t top_k, uint32_t hidden, float *y, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  qk_moe_scatter_kernel<<<n, 256, 0, s>>>(o, list, wts, n, top_k, hidden, y);
+  return cudaGetLastError();
+}

@@ -348,3 +348,56 @@ def test_row_shard_writes_its_column_block(K, disp):
         dw.free()
     st, ref = O.gemm(t, w, x, m, rows, cols)
     assert rel_inf(yd.cpu().numpy(), ref) <= 1e-4
+
+
+# ---------------------------------------------------------------- mixture of experts (moe.rs:75-126, 184-258)
+def _moe_case(t, hidden, inter, n_exp, tokens, seed):
+    gate = [S.gen_weight(t, inter, hidden, seed=seed, stream=3 * e) for e in range(n_exp)]
+    up = [S.gen_weight(t, inter, hidden, seed=seed, stream=3 * e + 1) for e in range(n_exp)]
+    down = [S.gen_weight(t, hidden, inter, seed=seed, stream=3 * e + 2) for e in range(n_exp)]
+    rng = np.random.default_rng(seed)
+    logits = rng.standard_normal((tokens, n_exp)).astype(np.float32)
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    deq = lambda ws, r, c: np.stack([O.dequant_matrix(t, w, r, c) for w in ws])
+    return gate, up, down, logits, x, deq(gate, inter, hidden), deq(up, inter, hidden), deq(down, hidden, inter)
+
+
+def test_moe_route_matches_oracle():
+    import torch
+    from oxillama_b200 import moe
+    rng = np.random.default_rng(5)
+    logits = rng.standard_normal((64, 8)).astype(np.float32)
+    logits[3, :] = 0.25  # all equal: ties go to the lower expert ids
+    for top_k in (1, 2, 3):
+        ids, wts = moe.route(torch.from_numpy(logits).cuda(), top_k)
+        rid, rw = O.moe_route(logits, top_k)
+        assert np.array_equal(ids.cpu().numpy(), rid)
+        assert np.abs(wts.cpu().numpy() - rw).max() <= 1e-6
+
+
+@pytest.mark.parametrize("t", [S.Q4_K, S.IQ4_XS])
+@pytest.mark.parametrize("tokens", [3, 40])
+def test_moe_ffn_matches_oracle(t, tokens):
+    import torch
+    from oxillama_b200 import moe
+    hidden, inter, n_exp, top_k = 256, 512, 4, 2
+    gate, up, down, logits, x, gf, uf, df = _moe_case(t, hidden, inter, n_exp, tokens, seed=61)
+    ref = O.moe_ffn_f32(gf, uf, df, logits, x, top_k)
+    lg, xd = torch.from_numpy(logits).cuda(), torch.from_numpy(x).cuda()
+    ex = moe.MoeExperts(t, gate, up, down, hidden, inter, n_exp)
+    y = torch.full((tokens, hidden), float("nan"), device="cuda")
+    ex.forward(lg, xd, y, top_k)
+    torch.cuda.synchronize()
+    assert rel_inf(y.cpu().numpy(), ref) <= 2 * TOL  # three chained matmuls, the larger batches on fp16 operands
+    # expert sharding: the two halves' contributions add up to the whole
+    parts = []
+    for rank in range(2):
+        b, e = moe.expert_range(n_exp, 2, rank)
+        sh = moe.MoeExperts(t, gate[b:e], up[b:e], down[b:e], hidden, inter, n_exp, expert_begin=b)
+        yp = torch.empty((tokens, hidden), device="cuda")
+        sh.forward(lg, xd, yp, top_k)
+        parts.append(yp)
+        torch.cuda.synchronize()
+        sh.free()
+    assert rel_inf((parts[0] + parts[1]).cpu().numpy(), ref) <= 2 * TOL
+    ex.free()

@@ -1,0 +1,83 @@
+"""Expert sharding of the MoE layer: host-side logic on CPU ranks (gloo, world size 2).
+
+Each rank computes its experts' contribution with a numpy stand-in for the
+device call, the ranks' outputs are summed with a gloo all-reduce, and the
+result must equal the oracle's whole-layer output
+(crates/oxillama-arch/src/common/moe.rs:184-258).
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+import oracle_lib as O  # noqa: E402
+from oxillama_b200 import moe  # noqa: E402
+
+
+def test_expert_range_partitions():
+    for n, w in ((8, 1), (8, 2), (8, 8), (8, 3), (5, 4), (2, 4)):
+        got = [moe.expert_range(n, w, r) for r in range(w)]
+        assert got[0][0] == 0 and got[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(got, got[1:]))
+        sizes = [e - b for b, e in got]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        moe.expert_range(8, 2, 2)
+
+
+def _local_numpy(gate, up, down, begin, end):
+    """Contribution of experts [begin, end) in plain numpy f32, routed by the oracle."""
+    def fwd(logits, x, top_k):
+        lg, xn = logits.numpy(), x.numpy()
+        ids, wts = O.moe_route(lg, top_k)
+        y = np.zeros_like(xn)
+        for t in range(xn.shape[0]):
+            for k in range(top_k):
+                e = int(ids[t, k])
+                if begin <= e < end:
+                    g = gate[e] @ xn[t]
+                    h = (g / (1.0 + np.exp(-g))) * (up[e] @ xn[t])
+                    y[t] += wts[t, k] * (down[e] @ h)
+        return torch.from_numpy(y.astype(np.float32))
+    return fwd
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(9)
+    n_exp, hidden, inter, tokens, top_k = 4, 32, 48, 12, 2
+    gate = rng.standard_normal((n_exp, inter, hidden)).astype(np.float32) * 0.2
+    up = rng.standard_normal((n_exp, inter, hidden)).astype(np.float32) * 0.2
+    down = rng.standard_normal((n_exp, hidden, inter)).astype(np.float32) * 0.2
+    logits = rng.standard_normal((tokens, n_exp)).astype(np.float32)
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    b, e = moe.expert_range(n_exp, world, rank)
+    layer = moe.ExpertShardedMoe(n_exp, world, rank, _local_numpy(gate, up, down, b, e))
+    y = layer.forward(torch.from_numpy(logits), torch.from_numpy(x), top_k).numpy()
+    ref = O.moe_ffn_f32(gate, up, down, logits, x, top_k)
+    q.put((rank, float(np.abs(y - ref).max() / np.abs(ref).max())))
+    dist.destroy_process_group()
+
+
+def test_expert_sharded_moe_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert sorted(r for r, _ in res) == [0, 1]
+    assert all(err <= 1e-5 for _, err in res), res
