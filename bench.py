@@ -228,9 +228,24 @@ def run_ours(args):
     ys = [torch.empty(ROWS, device="cuda") for _ in range(RING)]
     gathered = torch.empty(world * ROWS, device="cuda") if world > 1 else None
     stream = torch.cuda.Stream()
+    # N > 1: every matvec's shard output goes to all ranks.  "peer": the matvec kernel stores
+    # it into every rank's buffer over NVLink and publishes a flag, a bounded wait follows
+    # (two buffers alternate); "nccl": an NCCL all-gather after the matvec.
+    peer = world > 1 and args.collective == "peer"
+    pgs = []
+    if peer:
+        from oxillama_b200.sharded import PeerGather
+        pgs = [PeerGather(ROWS, m_cap=1, ctx=ctx) for _ in range(2)]
 
     def step():
         for i in range(RING):
+            if peer:
+                # as in a decode chain: the kernel waits, under its prologue, until the previous
+                # matvec's blocks from all ranks have arrived, then runs and fans its own out
+                pgs[i & 1].gemm(dws[i], x, 1, after=pgs[(i + 1) & 1])
+                if i == RING - 1:
+                    pgs[i & 1].wait()
+                continue
             dws[i].gemv(x, ys[i])
             if world > 1:
                 dist.all_gather_into_tensor(gathered, ys[i])
@@ -249,7 +264,7 @@ def run_ours(args):
         # One step is captured once into a CUDA graph and replayed: at ~10 us per matvec
         # the host would otherwise be the bottleneck of a launch-bound loop.
         graph = None
-        if world == 1 and not args.no_graph:
+        if (world == 1 or peer) and not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()
@@ -318,7 +333,10 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "ring_copies": RING,
                        "l2": f"{RING} distinct weight copies ({RING * algo_bytes / 1e6:.0f} MB) rotate, larger than L2",
-                       "sharding": "none" if world == 1 else f"{world} row shards of ({world}x14336)x4096, NCCL all-gather of y per matvec"},
+                       "sharding": "none" if world == 1 else
+                       f"{world} row shards of ({world}x14336)x4096; y of every matvec " +
+                       ("stored into every rank by the matvec kernel over NVLink; each matvec waits in-kernel for the previous one's blocks from all ranks" if peer
+                        else "all-gathered by NCCL")},
             "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": RING * COLS * 4, "d2h_bytes_per_step": RING * ROWS * 4,
                     "note": "qk_gemv host-pointer call per matvec; weights cached on device after first use"},
@@ -333,6 +351,8 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_gemv_rate(args.cpu_seconds)
         line["prefill"] = prefill
         print(json.dumps(line))
+    for pg in pgs:
+        pg.free()
     if world > 1:
         dist.destroy_process_group()
 
@@ -346,6 +366,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-graph", action="store_true", help="launch every matvec from the host")
     ap.add_argument("--no-prefill", action="store_true", help="skip the batched-matmul measurements")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the shard outputs reach all ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -165,6 +165,39 @@ int qk_moe_ffn_dev(qk_ctx *ctx, const qk_weights *const *gate, const qk_weights 
                    const float *logits_dev, const float *x_dev, float *y_dev, size_t tokens,
                    size_t top_k, void *stream);
 
+/* ---- row-sharded layers on the GPUs of one node: outputs gathered by peer stores ---- */
+/* (new; stands where a sharded port of QuantLinear::forward would call an all-gather,
+ * crates/oxillama-arch/src/common/linear.rs:77-132) */
+typedef struct qk_gather qk_gather;
+
+/* This rank's [m_cap x world * rows_per_rank] f32 buffer plus its control words.
+ * world <= 8.  The ranks then exchange qk_gather_export handles (128 bytes each) over
+ * any host channel and qk_gather_import each other's. */
+int qk_gather_create(qk_ctx *ctx, size_t rows_per_rank, size_t m_cap, int world, int rank, qk_gather **out);
+int qk_gather_export(qk_ctx *ctx, qk_gather *g, unsigned char *handle, size_t handle_len);
+int qk_gather_import(qk_ctx *ctx, qk_gather *g, int peer_rank, const unsigned char *handle, size_t handle_len);
+int qk_gather_destroy(qk_ctx *ctx, qk_gather *g);
+/* Device pointer of the local buffer: y_full[i * world * rows_per_rank + r * rows_per_rank + j]. */
+float *qk_gather_buffer(qk_gather *g);
+
+/* qk_gemm_dev of this rank's shard (rows == rows_per_rank), with the [m x rows] result
+ * stored into every rank's buffer and the call's epoch published to every rank.  For
+ * Q4_K and m <= 4 the matvec kernel itself does the peer stores; otherwise a push kernel
+ * follows the ordinary one.  Every rank must make the same sequence of calls on a given
+ * qk_gather, and must not start call k + 1 on it before its own qk_gather_wait_dev of
+ * call k has been enqueued (alternate two qk_gather objects to overlap calls). */
+int qk_gemm_gather_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g, void *stream);
+/* The same, for activations that are themselves gathered: x_dev (usually inside
+ * qk_gather_buffer(after)) is read only once every rank's block of the latest call on
+ * `after` has arrived.  Where the matvec kernel does the peer stores it also does this
+ * wait, under its own prologue; otherwise qk_gather_wait_dev(after) is enqueued first.
+ * after == NULL: no wait. */
+int qk_gemm_gather_after_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
+                             qk_gather *after, void *stream);
+/* Enqueues a wait until every rank's block of the latest call has arrived (at most
+ * 0.25 s, then QK_TIMEOUT through qk_check_device_status). */
+int qk_gather_wait_dev(qk_ctx *ctx, qk_gather *g, void *stream);
+
 /* No counterpart in the reference.  qk_gemm_dev for Q4_K shards and m <= 4 that
  * allocates nothing: for callers that cannot allocate device memory once running
  * (a server that handed all of HBM to its own pools, a process under a fixed

@@ -40,6 +40,14 @@ SIGNATURES = {
     "qk_matvec_q8_fused_dev": (C.c_int, [vp, vp, vp, vp, vp]),
     "qk_quantize_q8_0_dev": (C.c_int, [vp, vp, sz, vp, vp]),
     "qk_gemm_dev_noalloc": (C.c_int, [vp, vp, vp, vp, sz, sz, vp]),
+    "qk_gather_create": (C.c_int, [vp, sz, sz, C.c_int, C.c_int, vp]),
+    "qk_gather_export": (C.c_int, [vp, vp, vp, sz]),
+    "qk_gather_import": (C.c_int, [vp, vp, C.c_int, vp, sz]),
+    "qk_gather_destroy": (C.c_int, [vp, vp]),
+    "qk_gather_buffer": (vp, [vp]),
+    "qk_gemm_gather_dev": (C.c_int, [vp, vp, vp, sz, vp, vp]),
+    "qk_gemm_gather_after_dev": (C.c_int, [vp, vp, vp, sz, vp, vp, vp]),
+    "qk_gather_wait_dev": (C.c_int, [vp, vp, vp]),
     "qk_moe_route_dev": (C.c_int, [vp, vp, sz, sz, sz, vp, vp, vp]),
     "qk_moe_ffn_dev": (C.c_int, [vp, vp, vp, vp, sz, sz, sz, vp, vp, vp, sz, sz, vp]),
     "qk_check_device_status": (C.c_int, [vp, vp]),

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libqk_cuda.so")
-SOURCES = ["qk_api.cu", "qk_simple.cu", "qk_gemv.cu", "qk_gemv_mma.cu", "qk_noalloc.cu", "qk_gemm_tc.cu", "qk_moe.cu"]
+SOURCES = ["qk_api.cu", "qk_simple.cu", "qk_gemv.cu", "qk_gemv_mma.cu", "qk_noalloc.cu", "qk_gemm_tc.cu", "qk_moe.cu", "qk_gather.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -111,9 +111,15 @@ __device__ __forceinline__ float small_int_to_float(int v) {
 // [M][3 digit planes of PS bytes, natural column order][M][Kp/32] float2 (sx, Sx)
 __global__ void __launch_bounds__(256)
     qk_xsplit_kernel(const float *__restrict__ x, uint32_t m_rows, uint32_t cols, uint32_t Kp,
-                     uint32_t PS, uint32_t xs_off, unsigned char *__restrict__ img) {
+                     uint32_t PS, uint32_t xs_off, unsigned char *__restrict__ img,
+                     const unsigned *wait_flags, const unsigned *wait_epoch, uint32_t wait_n,
+                     unsigned *status) {
   pdl_launch_dependents();
   pdl_wait();  // x may be the previous kernel's output; the image may still be in use by it
+  if (wait_n) {  // x is gathered from other GPUs: their blocks must have arrived
+    if (!flags_wait_bounded(wait_flags, wait_epoch, wait_n, threadIdx.x)) atomicOr(status, QK_DEV_TIMEOUT);
+    __syncthreads();
+  }
   const uint32_t quads = Kp / 4, total = m_rows * quads;
   const uint32_t it = blockIdx.x * 256 + threadIdx.x;
   if (it >= total) return;  // warp-uniform: total is a multiple of 64
@@ -222,7 +228,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
                            uint64_t ldy, unsigned *status, int nstage, int nslot,
-                           uint32_t stage_bytes, SmemMma S, uint32_t Kp) {
+                           uint32_t stage_bytes, SmemMma S, uint32_t Kp, QkPeers peers) {
   constexpr int WG = CW / G;  // warps per group; a group owns every G-th chunk
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -284,7 +290,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 #pragma unroll
         for (int wv = 0; wv < WG; wv++) v += red[(wv * M + m) * 8 + r];
         const uint32_t row = (blockIdx.x + c * gridDim.x) * 8 + r;
-        if (row < L.rows) y[(uint64_t)m * ldy + row] = v;
+        if (row < L.rows) {
+          if (peers.n == 0) {
+            y[(uint64_t)m * ldy + row] = v;
+          } else {  // the same value into every rank's gathered buffer
+            for (uint32_t p = 0; p < peers.n; p++) peers.y[p][(uint64_t)m * ldy + row] = v;
+          }
+        }
       }
       __syncwarp();
       QK_STAMP(c < 30, 64 + c);
@@ -293,6 +305,21 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       // its partials
       if (lane == 0)
         for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
+    }
+    if (peers.n) {  // this CTA's rows are out; the last CTA of the launch publishes the epoch
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
+          __threadfence();
+          *peers.counter = 0;
+          const unsigned e = *peers.epoch + 1;
+          *peers.epoch = e;
+          __threadfence_system();
+          for (uint32_t p = 0; p < peers.n; p++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(e) : "memory");
+        }
+      }
     }
     return;
   }
@@ -316,6 +343,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   pdl_wait();  // x may be the previous kernel's output; y may be read or written by it
   QK_STAMP(warp == 0, 121);
   bool dead = false;
+  if (INCTA && peers.wait_n) {  // x is gathered from other GPUs: their blocks must have arrived
+    if (!flags_wait_bounded(peers.wait_flags, peers.wait_epoch, peers.wait_n, threadIdx.x))
+      atomicOr(status, QK_DEV_TIMEOUT);
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
+  }
   if (INCTA) {
     xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off);
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
@@ -493,7 +525,7 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
 template <int M, bool INCTA, int CW, int G>
 cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
                        unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
-                       cudaStream_t s) {
+                       cudaStream_t s, const QkPeers *peers = nullptr) {
   auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW, G>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -517,7 +549,8 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
     c0.gridDim = dim3((quads + 255) / 256), c0.blockDim = dim3(256), c0.stream = s;
     c0.attrs = at, c0.numAttrs = use_pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&c0, qk_xsplit_kernel, x, (uint32_t)M, L.cols, P.Kp,
-                                       P.S.PS, P.S.xs_off, ximg);
+                                       P.S.PS, P.S.xs_off, ximg, peers ? peers->wait_flags : nullptr,
+                                       peers ? peers->wait_epoch : nullptr, peers ? peers->wait_n : 0u, status);
     if (e != cudaSuccess) return e;
   }
   uint32_t grid = (uint32_t)sm_count;  // persistent, one CTA per SM
@@ -525,8 +558,10 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1) * 32), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
+  QkPeers pv = {};
+  if (peers) pv = *peers;
   return cudaLaunchKernelEx(&cfg, kern, L, W, x, (const unsigned char *)ximg, y, ldy, status,
-                            P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp);
+                            P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv);
 }
 
 // Every CTA redoing the split costs ~M*K/512 quads per thread; past this size the
@@ -544,7 +579,7 @@ bool split_in_cta(const PlanMma &P, uint32_t m) {
 template <int M>
 cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, float *y,
                          uint64_t ldy, unsigned *status, unsigned char *ximg, int sm_count,
-                         const PlanMma &P, cudaStream_t s) {
+                         const PlanMma &P, cudaStream_t s, const QkPeers *peers) {
   // Warp groups: a group owns every G-th chunk.  A stage must always be consumed by
   // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
   // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
@@ -555,8 +590,8 @@ cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, fl
   }
 #define QK_LAUNCH(CWV, GV)                                                                       \
   return split_in_cta(P, M)                                                                      \
-             ? launch_mma<M, true, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s)       \
-             : launch_mma<M, false, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s)
+             ? launch_mma<M, true, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
+             : launch_mma<M, false, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers)
   if (cw == 8) {
     switch (P.groups) {
       case 4:
@@ -593,18 +628,18 @@ size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m) {
 
 cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
-                               int sm_count, cudaStream_t s) {
+                               int sm_count, cudaStream_t s, const QkPeers *peers) {
   PlanMma P;
   if (!make_plan_mma(L, m, &P)) return cudaErrorInvalidConfiguration;
   switch (m) {
     case 1:
-      return launch_mma_m<1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
     case 2:
-      return launch_mma_m<2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
     case 3:
-      return launch_mma_m<3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
     default:
-      return launch_mma_m<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);
+      return launch_mma_m<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
   }
 }
 

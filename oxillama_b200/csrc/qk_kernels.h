@@ -17,6 +17,24 @@ cudaError_t qk_launch_fused_simple(const QkLayout &L, const uint8_t *tiled, cons
                                    float *out, cudaStream_t s);
 cudaError_t qk_launch_quantize_q8_0(const float *x, uint64_t n, uint8_t *out, cudaStream_t s);
 
+// Output fan-out of a row-sharded matvec: the kernel stores every result into the
+// gathered buffer of each rank of the node (plain peer stores over NVLink; entry `rank`
+// is the local buffer), then the last CTA to finish publishes the call's epoch in every
+// rank's flag array.  n == 0: ordinary local output.
+#define QK_MAX_PEERS 8
+struct QkPeers {
+  float *y[QK_MAX_PEERS];         // each rank's buffer, already offset to this rank's columns
+  unsigned *flags[QK_MAX_PEERS];  // each rank's flag array [n]
+  unsigned *counter;              // local: CTAs finished in this launch (returns to 0)
+  unsigned *epoch;                // local: calls completed so far
+  uint32_t n, rank;
+  // optional: before the kernel reads its activations, wait (bounded) until all wait_n
+  // ranks' flags in wait_flags have reached *wait_epoch (the activations are the gathered
+  // output of an earlier sharded call)
+  const unsigned *wait_flags, *wait_epoch;
+  uint32_t wait_n;
+};
+
 // Bandwidth-bound decode path (m <= QK_GEMV_MAX_M): bulk-copied tiles, integer dot.
 #define QK_GEMV_MAX_M 4
 bool qk_gemv_fast_supported(const QkLayout &L, uint32_t m);
@@ -28,7 +46,7 @@ bool qk_gemv_mma_supported(const QkLayout &L, uint32_t m);
 size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
-                               int sm_count, cudaStream_t s);
+                               int sm_count, cudaStream_t s, const QkPeers *peers = nullptr);
 cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, const float *x,
                                      float *y, uint32_t m, uint64_t ldy, unsigned *status,
                                      unsigned char *scratch, int sm_count, cudaStream_t s);

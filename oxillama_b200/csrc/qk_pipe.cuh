@@ -101,6 +101,25 @@ __device__ __forceinline__ float h2f_bits(uint32_t h) {
 }
 
 
+// Threads 0 .. n-1 of the caller each wait until flags[thread] has reached *epoch (written
+// by another GPU with a system-scope release), for at most a quarter of a second.
+// Returns false on the thread whose wait ran out.
+__device__ __forceinline__ bool flags_wait_bounded(const unsigned *flags, const unsigned *epoch, uint32_t n,
+                                                   uint32_t tid) {
+  if (tid >= n) return true;
+  const unsigned want = *reinterpret_cast<const volatile unsigned *>(epoch);
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
+    if ((int)(v - want) >= 0) return true;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 > 250000000ull) return false;
+  }
+}
+
 // Programmatic dependent launch: lets the next kernel in the stream start its
 // prologue while this grid drains / waits until the previous grid's memory is
 // visible.  Both are no-ops when the launch did not opt in.

@@ -11,6 +11,7 @@ become numpy arrays; `output` arrays are written in place.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -98,9 +99,10 @@ _default_ctx = None
 
 
 def default_context() -> Context:
+    """The process-wide context: on the GPU named by LOCAL_RANK (one process per GPU), else GPU 0."""
     global _default_ctx
     if _default_ctx is None:
-        _default_ctx = Context(0)
+        _default_ctx = Context(int(os.environ.get("LOCAL_RANK", "0")))
     return _default_ctx
 
 

@@ -99,3 +99,72 @@ def assemble(gathered: torch.Tensor, n_rows: int, world: int) -> torch.Tensor:
         b, e = shard_rows(n_rows, world, r)
         parts.append(gathered[r, :, : e - b])
     return torch.cat(parts, dim=1)
+
+
+class _DevPtr:
+    """Lets torch view device memory owned by libqk_cuda.so (`__cuda_array_interface__`)."""
+
+    def __init__(self, ptr: int, shape, typestr="<f4"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 2}
+
+
+class PeerGather:
+    """Gathered outputs of a row-sharded layer over the GPUs of one node, without a
+    collective: every rank's matvec stores its block into every rank's buffer over NVLink
+    and publishes an epoch flag (`qk_gemm_gather_dev`); `wait()` enqueues the bounded
+    wait for all blocks.  The ranks exchange the CUDA IPC handles of their buffers through
+    `torch.distributed` (any host channel would do).
+
+    Every rank must issue the same sequence of calls on a `PeerGather`; alternate two
+    of them if call k + 1 should overlap the consumers of call k.
+    """
+
+    def __init__(self, rows_per_rank: int, m_cap: int = 1, group: Optional[dist.ProcessGroup] = None, ctx=None):
+        import ctypes as C
+        from .kernels import default_context
+        self.ctx = ctx or default_context()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rows, self.m_cap = rows_per_rank, m_cap
+        h = C.c_void_p()
+        self.ctx.check(self.ctx.lib.qk_gather_create(self.ctx.handle, rows_per_rank, m_cap, self.world, self.rank,
+                                                     C.byref(h)))
+        self.handle = h
+        if self.world > 1:
+            buf = (C.c_ubyte * 128)()
+            self.ctx.check(self.ctx.lib.qk_gather_export(self.ctx.handle, h, buf, 128))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(buf), group=group)
+            for r, hb in enumerate(handles):
+                if r != self.rank:
+                    pb = (C.c_ubyte * 128).from_buffer_copy(hb)
+                    self.ctx.check(self.ctx.lib.qk_gather_import(self.ctx.handle, h, r, pb, 128))
+            dist.barrier(group=group)
+        ptr = self.ctx.lib.qk_gather_buffer(h)
+        self.buffer = torch.as_tensor(_DevPtr(ptr, (m_cap, self.world * rows_per_rank)), device="cuda")
+
+    def gemm(self, dw, x: torch.Tensor, m: int = 1, after: "PeerGather | None" = None, stream=None) -> None:
+        """Enqueues this rank's shard matvec with its result fanned out to every rank.
+
+        `after`: x is the gathered output of the latest call on that PeerGather; the kernels
+        wait for all of its blocks before they read x."""
+        import ctypes as C
+        from .device import _stream_ptr
+        self.ctx.check(self.ctx.lib.qk_gemm_gather_after_dev(
+            self.ctx.handle, dw.handle, C.c_void_p(x.data_ptr()), m, self.handle,
+            after.handle if after is not None else None, _stream_ptr(stream)))
+
+    def wait(self, stream=None) -> None:
+        from .device import _stream_ptr
+        self.ctx.check(self.ctx.lib.qk_gather_wait_dev(self.ctx.handle, self.handle, _stream_ptr(stream)))
+
+    def free(self):
+        if self.handle:
+            self.buffer = None
+            if self.world > 1:
+                torch.cuda.synchronize()
+                dist.barrier(group=self.group)  # nobody may still be storing into this rank's buffer
+            self.ctx.lib.qk_gather_destroy(self.ctx.handle, self.handle)
+            self.handle = None

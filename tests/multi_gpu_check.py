@@ -1,0 +1,97 @@
+"""Multi-GPU parity check of the row-sharded layer (run under torchrun, one rank per GPU):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port 29533 tests/multi_gpu_check.py
+
+Every rank uploads its row shard, runs the sharded matvec / small matmul with the
+peer-store gather (`qk_gemm_gather_dev`) and with an NCCL all-gather, and compares both
+with the oracle's result for the whole matrix.  Exits non-zero on a mismatch.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+import oracle_lib as O  # noqa: E402
+from oxillama_b200 import synth as S  # noqa: E402
+from oxillama_b200.device import DeviceWeights, check_device_status  # noqa: E402
+from oxillama_b200.sharded import PeerGather, shard_rows  # noqa: E402
+
+
+def main():
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world, rank = dist.get_world_size(), dist.get_rank()
+    bad = 0
+    for t, rows, cols, m in ((S.Q4_K, 64 * world, 1024, 1), (S.Q4_K, 64 * world, 1024, 3), (S.Q6_K, 32 * world, 512, 1),
+                             (S.Q8_0, 48 * world, 512, 9)):
+        w = S.gen_weight(t, rows, cols, seed=71)
+        x = S.gen_acts(m, cols, seed=71)
+        st, ref = O.gemm(t, w, x, m, rows, cols)
+        b, e = shard_rows(rows, world, rank)
+        dw = DeviceWeights(t, w, rows, cols, b, e)
+        xd = torch.from_numpy(x).cuda()
+        pg = PeerGather(e - b, m_cap=m)
+        for call in range(3):  # the epoch protocol across repeated calls
+            pg.gemm(dw, xd * (call + 1), m)
+            pg.wait()
+            torch.cuda.synchronize()
+            got = pg.buffer[:m].cpu().numpy()
+            err = np.abs(got - ref * (call + 1)).max() / np.abs(ref).max() / (call + 1)
+            tol = 2e-5 if m <= 4 else 1e-3
+            if not err <= tol:
+                bad += 1
+                print(f"rank {rank}: {S.NAMES[t]} m={m} call {call}: gather err {err}", flush=True)
+        check_device_status()
+        # the NCCL route for comparison
+        yl = torch.empty((m, e - b), device="cuda")
+        dw.gemm(xd, yl, m)
+        parts = [torch.empty_like(yl) for _ in range(world)]
+        dist.all_gather(parts, yl)
+        err = np.abs(torch.cat(parts, dim=1).cpu().numpy() - ref).max() / np.abs(ref).max()
+        if not err <= (2e-5 if m <= 4 else 1e-3):
+            bad += 1
+            print(f"rank {rank}: {S.NAMES[t]} m={m}: nccl err {err}", flush=True)
+        pg.free()
+        dw.free()
+    # two chained sharded layers: the second reads the first's gathered output and waits for it in-kernel
+    for t2 in (S.Q4_K, S.Q8_0):
+        n1, k1, n2 = 512, 512, 64 * world
+        w1, w2 = S.gen_weight(S.Q4_K, n1, k1, seed=72), S.gen_weight(t2, n2, n1, seed=73)
+        x = S.gen_acts(1, k1, seed=72)
+        ref1 = O.gemm(S.Q4_K, w1, x, 1, n1, k1)[1]
+        ref2 = O.gemm(t2, w2, ref1, 1, n2, n1)[1]
+        b1, e1 = shard_rows(n1, world, rank)
+        b2, e2 = shard_rows(n2, world, rank)
+        d1, d2 = DeviceWeights(S.Q4_K, w1, n1, k1, b1, e1), DeviceWeights(t2, w2, n2, n1, b2, e2)
+        g1, g2 = PeerGather(e1 - b1), PeerGather(e2 - b2)
+        xd = torch.from_numpy(x).cuda()
+        for call in range(3):
+            g1.gemm(d1, xd, 1)
+            g2.gemm(d2, g1.buffer, 1, after=g1)
+            g2.wait()
+            torch.cuda.synchronize()
+            err = np.abs(g2.buffer[:1].cpu().numpy() - ref2).max() / np.abs(ref2).max()
+            if not err <= 1e-4:
+                bad += 1
+                print(f"rank {rank}: chained {S.NAMES[t2]} call {call}: err {err}", flush=True)
+            dist.barrier()  # nobody starts the next round while a rank still reads this one
+        check_device_status()
+        g1.free(), g2.free(), d1.free(), d2.free()
+    tot = torch.tensor([bad], device="cuda")
+    dist.all_reduce(tot)
+    if rank == 0:
+        print("multi_gpu_check:", "OK" if int(tot) == 0 else f"{int(tot)} mismatches", f"on {world} GPUs", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(tot) == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()
