@@ -366,11 +366,20 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-graph", action="store_true", help="launch every matvec from the host")
     ap.add_argument("--no-prefill", action="store_true", help="skip the batched-matmul measurements")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="N = 1: only the batched-matmul measurements (a short run, e.g. for a profiler)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the shard outputs reach all ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.prefill_only:
+        import torch
+        from oxillama_b200.kernels import Context
+        torch.cuda.set_device(0)
+        ctx, stream = Context(0), torch.cuda.Stream()
+        print(json.dumps({"prefill": [prefill_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream, launches=30),
+                                      prefill_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream, launches=32)]}))
     else:
         run_ours(args)
 
