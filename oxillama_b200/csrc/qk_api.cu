@@ -312,7 +312,9 @@ static int gemm_dispatch(qk_ctx *c, const qk_weights *h, const float *x, float *
     return QK_OK;
   }
   // the tensor-core path rounds its operands to fp16; batches the decode kernels take keep f32 activations
-  if (!c->force_simple && m > QK_GEMV_MAX_M && m < (1u << 30) && qk_gemm_tc_supported(h->L, (uint32_t)m)) {
+  // (IQ4_XS has no decode kernel of its own: every batch size of it goes this way)
+  if (!c->force_simple && (m > QK_GEMV_MAX_M || h->L.type == QK_T_IQ4_XS) && m < (1u << 30) &&
+      qk_gemm_tc_supported(h->L, (uint32_t)m)) {
     int st = ensure_scratch(qk_gemm_tc_scratch_bytes(h->L, (uint32_t)m));
     if (st) return st;
     CK(c, qk_launch_gemm_tc(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->scratch,

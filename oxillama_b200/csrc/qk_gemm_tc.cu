@@ -59,7 +59,7 @@ constexpr int MAX_RING = 8;        // most stages of the activation ring
 constexpr uint32_t A_HALF = BM * 64;  // bytes of one A half-stage: 128 rows of 32 fp16
 
 struct GemmSmem {
-  uint32_t a_full, a_empty, b_full, b_empty, acc_full, acc_empty, tmem_slot;
+  uint32_t a_full, a_empty, b_full, b_empty, acc_full, acc_empty, tmem_slot, lut;
   uint32_t a, b;  // ring bases, 1024-byte aligned
   uint32_t a_stage, b_stage;
   int b_stages;
@@ -175,7 +175,9 @@ __device__ __forceinline__ const uint8_t *blk_addr(const uint8_t *chunk_base, ui
 }
 
 template <>
-struct WFmt<QK_T_Q4_K> {  // super-block of 256: d, dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles (reference/q4_k.rs:27-102)
+struct WFmt<QK_T_Q4_K> {
+  static constexpr bool HAS_LUT = false;
+  __device__ static void fill_lut(uint32_t *, uint32_t, uint32_t) {}  // super-block of 256: d, dmin, 12 bytes of 6-bit scales/mins, 128 bytes of nibbles (reference/q4_k.rs:27-102)
   struct Pk { uint4 h, q0, q1; };
   // position 8 i + j of a row-step <- column 4 i + {0,2,1,3}[j & 3] + 32 (j >> 2): byte 4 i + b of
   // the group's 32 holds column 4 i + b (low nibble) and 32 + 4 i + b (high nibble)
@@ -208,7 +210,7 @@ struct WFmt<QK_T_Q4_K> {  // super-block of 256: d, dmin, 12 bytes of 6-bit scal
     // (K + q) * s - K * s is exact in the FMA, so q * s is rounded once
     c.c_lo = __hmul2(c.s_lo, __float2half2_rn(-1024.f)), c.c_hi = __hmul2(c.s_hi, __float2half2_rn(-64.f));
   }
-  __device__ static void expand(const Pk &k, const Sc &c, uint32_t g, int hf, uint32_t o[4][4]) {
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t g, int hf, uint32_t o[4][4], uint32_t) {
     const uint4 q = hf ? k.q1 : k.q0;
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -224,7 +226,9 @@ struct WFmt<QK_T_Q4_K> {  // super-block of 256: d, dmin, 12 bytes of 6-bit scal
 };
 
 template <>
-struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
+struct WFmt<QK_T_Q8_0> {
+  static constexpr bool HAS_LUT = false;
+  __device__ static void fill_lut(uint32_t *, uint32_t, uint32_t) {}  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
   struct Pk { uint4 q[4]; uint32_t d2; };
   __host__ __device__ static uint32_t src(uint32_t p) { return p; }
   // Blocks past the end of the row (a last super-block that is not full) read as d = 0, q = 0.
@@ -252,7 +256,7 @@ struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
     c.d[0] = bits_h2((k.d2 & 0xFFFFu) * 0x10001u), c.d[1] = bits_h2((k.d2 >> 16) * 0x10001u);
   }
-  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4]) {
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4], uint32_t) {
     const __half2 off = __float2half2_rn(1152.f);  // 1024 + 128: (1024 + (q ^ 0x80)) - 1152 = q, exact; q * d rounded once
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -270,7 +274,9 @@ struct WFmt<QK_T_Q8_0> {  // block of 32: f16 d, 32 int8 (reference/q8_0.rs)
 };
 
 template <>
-struct WFmt<QK_T_Q4_0> {  // block of 32: f16 d, 16 bytes; byte j = elements 2 j (low nibble) and 2 j + 1 (high) (reference/q4_0.rs:36-46)
+struct WFmt<QK_T_Q4_0> {
+  static constexpr bool HAS_LUT = false;
+  __device__ static void fill_lut(uint32_t *, uint32_t, uint32_t) {}  // block of 32: f16 d, 16 bytes; byte j = elements 2 j (low nibble) and 2 j + 1 (high) (reference/q4_0.rs:36-46)
   struct Pk { uint4 q[2]; uint32_t d2; };
   // chunk c of a row-step is word c & 3 of block c >> 2; a word yields its elements as
   // (byte 0, byte 2), (byte 1, byte 3) low nibbles, then the same of the high nibbles
@@ -301,7 +307,7 @@ struct WFmt<QK_T_Q4_0> {  // block of 32: f16 d, 16 bytes; byte j = elements 2 j
   __device__ static void scales(const Pk &k, uint32_t, Sc &c) {
     c.d[0] = bits_h2((k.d2 & 0xFFFFu) * 0x10001u), c.d[1] = bits_h2((k.d2 >> 16) * 0x10001u);
   }
-  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4]) {
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4], uint32_t) {
     const __half2 off_lo = __float2half2_rn(1032.f), off_hi = __float2half2_rn(72.f);  // K + 8: (K + q) - (K + 8) = q - 8, exact
     const uint4 q = k.q[hf];
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -318,7 +324,9 @@ struct WFmt<QK_T_Q4_0> {  // block of 32: f16 d, 16 bytes; byte j = elements 2 j
 };
 
 template <>
-struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, f16 d (reference/q6_k.rs)
+struct WFmt<QK_T_Q6_K> {
+  static constexpr bool HAS_LUT = false;
+  __device__ static void fill_lut(uint32_t *, uint32_t, uint32_t) {}  // super-block of 256: ql 128, qh 64, 16 int8 scales, f16 d (reference/q6_k.rs)
   // group g: half hh = g >> 1 of the super-block, nibble n = g & 1 of ql[64 hh ..], bit pairs 4 n + {0, 2} of qh[32 hh ..]
   struct Pk { uint4 ql[4], qh[2]; uint32_t sc4, d; };
   __host__ __device__ static uint32_t src(uint32_t p) { return p; }
@@ -343,7 +351,7 @@ struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, 
 #pragma unroll
     for (int i = 0; i < 4; i++) c.s[i] = __float2half2_rn(d * (float)(int)(signed char)((k.sc4 >> (8 * i)) & 0xFF));
   }
-  __device__ static void expand(const Pk &k, const Sc &c, uint32_t g, int hf, uint32_t o[4][4]) {
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t g, int hf, uint32_t o[4][4], uint32_t) {
     // half hf of the row-step = columns 32 hf .. + 32 of the group: ql bytes 32 hf + l, qh byte l, bit pair 4 n + 2 hf
     const __half2 off = __float2half2_rn(1056.f);  // (1024 + q) - 1056 = q - 32, exact; then one rounding in the product
     const uint32_t nsh = 4 * (g & 1u), hsh = 4 * (g & 1u) + 2 * hf;
@@ -362,6 +370,56 @@ struct WFmt<QK_T_Q6_K> {  // super-block of 256: ql 128, qh 64, 16 int8 scales, 
         o[i][2 * e + 1] = h2_bits(__hmul2(__hsub2(bits_h2(b2), off), sc));
       }
     }
+  }
+};
+
+template <>
+struct WFmt<QK_T_IQ4_XS> {  // super-block of 256: f16 d, scales_h, scales_l[4], 128 nibble bytes (reference/iq4_xs.rs:47-97)
+  // sub-block s = nibble bytes 16 s ..; byte j holds elements 2 j (low) and 2 j + 1 (high); value =
+  // d (ls - 32) K[nibble] with the non-linear table K (iq_shared.rs:16-18).  A 256-entry table in
+  // shared memory maps a byte straight to the half2 (K[low], K[high]) of its two adjacent elements.
+  struct Pk { uint4 q[2]; uint2 h; };
+  static constexpr bool HAS_LUT = true;
+  __host__ __device__ static uint32_t src(uint32_t p) { return p; }
+  __device__ static void fill_lut(uint32_t *lut, uint32_t tid, uint32_t nthreads) {
+    const int K[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+    for (uint32_t b = tid; b < 256; b += nthreads) {
+      int lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 16; i++) lo = (int)(b & 15u) == i ? K[i] : lo, hi = (int)(b >> 4) == i ? K[i] : hi;
+      lut[b] = h2_bits(__floats2half2_rn((float)lo, (float)hi));
+    }
+  }
+  // A block's 8 rows: [8 granules x 8 rows x 16 nibble bytes][8 rows x 8 header bytes].
+  __device__ static void load(Pk &k, const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g,
+                              uint32_t s) {
+    const uint8_t *p = blk_addr<136>(cb, s);
+    k.q[0] = ldg16(p + (2 * g) * 128 + rr * 16), k.q[1] = ldg16(p + (2 * g + 1) * 128 + rr * 16);
+    k.h = __ldg(reinterpret_cast<const uint2 *>(p + 1024 + rr * 8));
+  }
+  __device__ static void prefetch(const QkLayout &L, const uint8_t *cb, uint32_t rr, uint32_t g, uint32_t s) {
+    const uint32_t line = g * 8 + rr;  // 1088 bytes = up to 9 lines
+    if (line < 9) pf_l2(blk_addr<136>(cb, s) + line * 128);
+  }
+  struct Sc { __half2 dl[2]; };
+  __device__ static void scales(const Pk &k, uint32_t g, Sc &c) {
+    const float d = h2f_bits(k.h.x);
+    const uint32_t sh = k.h.x >> 16, sl = k.h.y;
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+      const uint32_t sb = 2 * g + hf;
+      const int ls = (int)(((sl >> (4 * sb)) & 0xFu) | (((sh >> (2 * sb)) & 3u) << 4));
+      c.dl[hf] = __float2half2_rn(d * (float)(ls - 32));
+    }
+  }
+  __device__ static void expand(const Pk &k, const Sc &c, uint32_t, int hf, uint32_t o[4][4], uint32_t lut) {
+    const uint4 q = k.q[hf];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int b = 0; b < 4; b++)
+        o[i][b] = h2_bits(__hmul2(bits_h2(lds32(lut + (((w[i] >> (8 * b)) & 0xFFu) << 2))), c.dl[hf]));
   }
 };
 
@@ -481,6 +539,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if (WFmt<T>::HAS_LUT) WFmt<T>::fill_lut(reinterpret_cast<uint32_t *>(smem + S.lut), threadIdx.x, NTHREADS);
   if (warp == 0) {  // tensor memory for the accumulator columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      sbase + S.tmem_slot),
@@ -717,7 +776,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           for (int hf = 0; hf < 2; hf++) {
             const int unit = rh * 2 + hf;
             uint32_t o[4][4];
-            F::expand(pk[rh], sc, grp, hf, o);
+            F::expand(pk[rh], sc, grp, hf, o, sbase + S.lut);
             // the MMAs that read this unit's previous contents must have retired
             if (u > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(a_empty + unit * 8, (u - 1) & 1u))) {
               dead = true;  // warp-uniform: these warps execute .aligned tcgen05 instructions later
@@ -790,6 +849,7 @@ bool plan_gemm(int bn, int rh, GemmSmem *S, uint32_t *total) {
   s.acc_full = off, off += 16;
   s.acc_empty = off, off += 16;
   s.tmem_slot = off, off += 16;
+  s.lut = off, off += 1024;  // byte -> half2 table of the formats that need one
   off = (off + 1023u) & ~1023u;
   s.a_stage = A_HALF;
   s.b_stage = (uint32_t)bn * 128;
@@ -916,7 +976,8 @@ extern "C" void qk_gemm_trace_set(unsigned long long *p) {
 #endif
 
 bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m) {
-  const bool fmt = L.type == QK_T_Q4_K || L.type == QK_T_Q8_0 || L.type == QK_T_Q4_0 || L.type == QK_T_Q6_K;
+  const bool fmt = L.type == QK_T_Q4_K || L.type == QK_T_Q8_0 || L.type == QK_T_Q4_0 || L.type == QK_T_Q6_K ||
+                   L.type == QK_T_IQ4_XS;
   return fmt && m >= 1 && L.rows >= 1 && L.nb >= 1;
 }
 
@@ -939,6 +1000,8 @@ cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const flo
       return launch_fmt<QK_T_Q4_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
     case QK_T_Q6_K:
       return launch_fmt<QK_T_Q6_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+    case QK_T_IQ4_XS:
+      return launch_fmt<QK_T_IQ4_XS>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
     default:
       return cudaErrorNotSupported;
   }

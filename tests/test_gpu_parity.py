@@ -18,6 +18,12 @@ TOL = 1e-3        # stated tolerance of the path
 TOL_F32 = 2e-5    # what the integer-digit / f32 kernels are expected to hold
 
 
+def tolf(t, exact=TOL_F32):
+    """Bar for a decode-sized call: IQ4_XS has no integer-digit decode kernel, every batch
+    size of it runs the fp16-operand tensor-core matmul (the path's stated 1e-3)."""
+    return TOL if t == S.IQ4_XS else exact
+
+
 def rel_inf(y, ref):
     den = float(np.abs(ref).max())
     return float(np.abs(y.astype(np.float64) - ref.astype(np.float64)).max()) / (den if den > 0 else 1.0)
@@ -79,7 +85,7 @@ def test_gemv_matches_oracle(K, disp, t, rows, cols):
     disp.get_kernel(t).gemv(K.QuantTensor(w, (rows, cols), t), x, y)
     st, ref = O.gemv(t, w, rows, cols, x)
     assert st == 0
-    assert rel_inf(y, ref) <= TOL_F32, rel_inf(y, ref)
+    assert rel_inf(y, ref) <= tolf(t), rel_inf(y, ref)
 
 
 @pytest.mark.parametrize("t", S.ALL_TYPES)
@@ -94,7 +100,7 @@ def test_gemm_matches_oracle(K, disp, t, m):
     assert st == 0
     # m <= 2: three-digit activations; m = 3, 4: two digits; larger m may take the fp16
     # tensor-core path (operands rounded to fp16): the path's stated 1e-3
-    tol = TOL_F32 if m <= 2 else (1e-4 if m <= 4 else TOL)
+    tol = tolf(t) if m <= 2 else (tolf(t, 1e-4) if m <= 4 else TOL)
     assert rel_inf(y, ref) <= tol, rel_inf(y, ref)
 
 
@@ -129,7 +135,7 @@ def test_against_golden(K, disp, key):
     assert np.array_equal(dq.view(np.uint32), G[key + "_dequant"].view(np.uint32))
     y = np.empty((3, rows), np.float32)
     k.gemm(qt, x, y, 3, rows, cols)
-    assert rel_inf(y, G[key + "_gemm"]) <= 1e-4
+    assert rel_inf(y, G[key + "_gemm"]) <= tolf(t, 1e-4)
     kp = -(-cols // S.BLOCK_SIZE[t]) * S.BLOCK_SIZE[t]
     xp = np.zeros(kp, np.float32)
     xp[:cols] = x[0]
@@ -331,7 +337,7 @@ def test_config3_q8_0_prefill(K, disp):
     ("q", S.Q4_K, 4096, 4096), ("k", S.Q4_K, 1024, 4096), ("down", S.Q6_K, 4096, 14336)])
 @pytest.mark.parametrize("m", [1, 8, 32])
 def test_config4_layer_linears(K, disp, name, t, rows, cols, m):
-    _check_config(K, disp, t, rows, cols, m, 4, TOL_F32 if m == 1 else TOL, row_cap=256)
+    _check_config(K, disp, t, rows, cols, m, 4, tolf(t) if m == 1 else TOL, row_cap=256)
 
 
 def test_row_shard_writes_its_column_block(K, disp):
@@ -401,3 +407,63 @@ def test_moe_ffn_matches_oracle(t, tokens):
         sh.free()
     assert rel_inf((parts[0] + parts[1]).cpu().numpy(), ref) <= 2 * TOL
     ex.free()
+
+
+def test_moe_argument_checks():
+    import ctypes as C
+    import torch
+    from oxillama_b200 import moe
+    hidden, inter, n_exp = 256, 256, 2
+    gate, up, down, logits, x, *_ = _moe_case(S.Q4_K, hidden, inter, n_exp, 4, seed=62)
+    ex = moe.MoeExperts(S.Q4_K, gate, up, down, hidden, inter, n_exp)
+    lg, xd = torch.from_numpy(logits).cuda(), torch.from_numpy(x).cuda()
+    y = torch.zeros((4, hidden), device="cuda")
+    lib, h = ex.ctx.lib, ex.ctx.handle
+    args = (ex._g, ex._u, ex._d)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    assert lib.qk_moe_ffn_dev(h, *args, 2, 1, 2, ptr(lg), ptr(xd), ptr(y), 4, 2, None) == 102  # experts 1..3 of 2
+    assert lib.qk_moe_ffn_dev(h, *args, 2, 0, 2, ptr(lg), ptr(xd), ptr(y), 4, 0, None) == 102  # top_k = 0
+    assert lib.qk_moe_ffn_dev(h, *args, 2, 0, 2, None, ptr(xd), ptr(y), 4, 2, None) == 102
+    # gate of one expert with the wrong shape
+    from oxillama_b200.device import DeviceWeights
+    bad = DeviceWeights(S.Q4_K, S.gen_weight(S.Q4_K, 8, 512, seed=1), 8, 512)
+    g2 = (C.c_void_p * 2)(ex.gate[0].handle, bad.handle)
+    assert lib.qk_moe_ffn_dev(h, g2, ex._u, ex._d, 2, 0, 2, ptr(lg), ptr(xd), ptr(y), 4, 2, None) == 3
+    # no tokens: nothing to do
+    assert lib.qk_moe_ffn_dev(h, *args, 2, 0, 2, ptr(lg), ptr(xd), ptr(y), 0, 2, None) == 0
+    bad.free()
+    ex.free()
+
+
+@pytest.mark.parametrize("t,m", [(S.Q4_K, 1), (S.Q4_K, 4), (S.Q6_K, 1), (S.Q8_0, 12)])
+def test_peer_gather_single_rank(t, m):
+    # world size 1: the gathered buffer is just y; the fused (Q4_K, m <= 4) and the push route
+    import torch
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    from oxillama_b200.sharded import PeerGather
+    rows, cols = 72, 1024
+    w = S.gen_weight(t, rows, cols, seed=81)
+    x = S.gen_acts(m, cols, seed=81)
+    dw = DeviceWeights(t, w, rows, cols)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.empty((m, rows), device="cuda")
+    dw.gemm(xd, y, m)
+    pg = PeerGather(rows, m_cap=m)
+    for call in range(2):
+        pg.gemm(dw, xd, m, after=pg if call else None)
+        pg.wait()
+        torch.cuda.synchronize()
+        if m <= 4:
+            assert torch.equal(pg.buffer[:m], y)
+        else:  # split-K partial sums meet in atomic adds: the last bits may differ between runs
+            assert float((pg.buffer[:m] - y).abs().max() / y.abs().max()) <= 1e-5
+    check_device_status()
+    with pytest.raises(K_err()):
+        pg.gemm(dw, xd, m + 1)  # more activation rows than the buffer was made for
+    pg.free()
+    dw.free()
+
+
+def K_err():
+    from oxillama_b200.kernels import QuantError
+    return QuantError
