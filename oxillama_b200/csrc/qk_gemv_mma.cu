@@ -553,7 +553,12 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
                                        peers ? peers->wait_epoch : nullptr, peers ? peers->wait_n : 0u, status);
     if (e != cudaSuccess) return e;
   }
-  uint32_t grid = (uint32_t)sm_count;  // persistent, one CTA per SM
+  static int ctas = -1;  // developer knob: persistent CTAs per SM (they must fit: see QK_CW, QK_NSTAGE)
+  if (ctas < 0) {
+    const char *e = getenv("QK_CTAS");
+    ctas = (e && atoi(e) == 2) ? 2 : 1;
+  }
+  uint32_t grid = (uint32_t)sm_count * (uint32_t)ctas;  // persistent
   if (grid > L.chunks) grid = L.chunks;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1) * 32), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
@@ -583,11 +588,15 @@ cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, fl
   // Warp groups: a group owns every G-th chunk.  A stage must always be consumed by
   // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
   // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
-  static int cw = -1;
-  if (cw < 0) {
+  // 16 compute warps stream best at M = 1; from M = 2 their 96-register budget spills
+  // (18 / 36 / 56 us at M = 2 / 3 / 4 on the 14336 x 4096 shape), 8 warps with twice the
+  // registers do not (15 / 21 / 31 us).  QK_CW overrides.
+  static int cw_env = -1;
+  if (cw_env < 0) {
     const char *e = getenv("QK_CW");
-    cw = (e && atoi(e) == 8) ? 8 : 16;
+    cw_env = e ? (atoi(e) == 8 ? 8 : 16) : 0;
   }
+  const int cw = cw_env ? cw_env : (M >= 2 ? 8 : 16);
 #define QK_LAUNCH(CWV, GV)                                                                       \
   return split_in_cta(P, M)                                                                      \
              ? launch_mma<M, true, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
