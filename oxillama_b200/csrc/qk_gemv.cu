@@ -149,6 +149,10 @@ __global__ void __launch_bounds__(NT)
     bulk_g2s(sbase + S.stage + st * stage_bytes, W + qk_tile_offset(L, chunk, kt), bytes, bar);
   };
 
+  // Programmatic dependent launch: the next kernel in the stream may start its prologue
+  // as this one's CTAs retire, and this one prefetches its (immutable) weights before it
+  // waits for the previous kernel, whose output x may be.
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < nstage; s++) mbar_init(sbase + S.bars + s * 8, 1);
@@ -156,6 +160,7 @@ __global__ void __launch_bounds__(NT)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     for (uint32_t i = 0; i < (uint32_t)nstage && i < my_items; i++) issue(i);
   }
+  pdl_wait();  // x and y belong to the previous kernel until it has finished
   prep_x<TYPE, M, D>(L, x, smem, S, Kp);
   __syncthreads();
 
@@ -412,8 +417,13 @@ cudaError_t launch_one(const QkLayout &L, const uint8_t *W, const float *x, floa
   int ctas = occ_cached[1] < P.ctas_per_sm ? occ_cached[1] : P.ctas_per_sm;
   uint32_t grid = (uint32_t)sm_count * ctas;
   if (grid > L.chunks) grid = L.chunks;
-  kern<<<grid, NT, P.total, s>>>(L, W, x, y, ldy, status, P.nstage, P.stage_bytes, P.S, P.Kp);
-  return cudaGetLastError();
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NT), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
+  cfg.attrs = at, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, L, W, x, y, ldy, status, P.nstage, P.stage_bytes, P.S, P.Kp);
 }
 
 // Row splits: as many rows per thread as still leave every warp a unit to work on.
