@@ -234,8 +234,17 @@ def run_ours(args):
     peer = world > 1 and args.collective == "peer"
     pgs = []
     if peer:
+        # every rank must take the same route: agree on whether the IPC setup worked everywhere
         from oxillama_b200.sharded import PeerGather
-        pgs = [PeerGather(ROWS, m_cap=1, ctx=ctx) for _ in range(2)]
+        ok = torch.ones(1, device="cuda")
+        try:
+            pgs = [PeerGather(ROWS, m_cap=1, ctx=ctx) for _ in range(2)]
+        except Exception as e:  # noqa: BLE001 - any failure means "use the NCCL route"
+            print(f"rank {rank}: peer-store gather unavailable ({e!r}); falling back to NCCL", file=sys.stderr)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) == 0.0:
+            peer, pgs = False, []
 
     def step():
         for i in range(RING):

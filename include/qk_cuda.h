@@ -176,6 +176,9 @@ typedef struct qk_gather qk_gather;
 int qk_gather_create(qk_ctx *ctx, size_t rows_per_rank, size_t m_cap, int world, int rank, qk_gather **out);
 int qk_gather_export(qk_ctx *ctx, qk_gather *g, unsigned char *handle, size_t handle_len);
 int qk_gather_import(qk_ctx *ctx, qk_gather *g, int peer_rank, const unsigned char *handle, size_t handle_len);
+/* Once every rank's handle is imported: touches each peer mapping and waits.  Every rank
+ * calls it, then the ranks synchronise on the host, before the first sharded call. */
+int qk_gather_ready(qk_ctx *ctx, qk_gather *g);
 int qk_gather_destroy(qk_ctx *ctx, qk_gather *g);
 /* Device pointer of the local buffer: y_full[i * world * rows_per_rank + r * rows_per_rank + j]. */
 float *qk_gather_buffer(qk_gather *g);

@@ -38,9 +38,9 @@ __global__ void __launch_bounds__(256)
     for (uint32_t p = 0; p < peers.n; p++)
       if (p != peers.rank) peers.y[p][off] = v;
   }
+  __threadfence_system();  // every thread orders its own peer stores before the count below
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
     if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
       __threadfence();
       *peers.counter = 0;
@@ -71,6 +71,16 @@ __global__ void __launch_bounds__(32)
       atomicOr(status, QK_DEV_TIMEOUT);
       return;
     }
+  }
+}
+
+// First touch of every peer mapping from this GPU (one zero into this rank's block of
+// each peer's freshly cleared buffer), so that the first real call meets established
+// translations.
+__global__ void qk_gather_touch_kernel(QkPeers peers) {
+  if (threadIdx.x < peers.n) {
+    peers.y[threadIdx.x][0] = 0.f;
+    __threadfence_system();
   }
 }
 
@@ -145,6 +155,19 @@ extern "C" int qk_gather_import(qk_ctx *c, qk_gather *g, int peer_rank, const un
   }
   g->peer_y[peer_rank] = (float *)p0, g->peer_ctl[peer_rank] = (unsigned *)p1, g->opened[peer_rank] = true;
   return QK_OK;
+}
+
+// After every import: touches all peer mappings once and waits for it.  Call it on every
+// rank, then synchronise the ranks on the host, before the first qk_gemm_gather_dev.
+extern "C" int qk_gather_ready(qk_ctx *c, qk_gather *g) {
+  if (!c || !g) return QK_INVALID_ARGUMENT;
+  for (int r = 0; r < g->world; r++)
+    if (!g->peer_y[r]) return QK_INVALID_ARGUMENT;
+  cudaSetDevice(c->device);
+  qk_gather_touch_kernel<<<1, 32>>>(peers_of(g));
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gather_ready");
 }
 
 extern "C" int qk_gather_destroy(qk_ctx *c, qk_gather *g) {

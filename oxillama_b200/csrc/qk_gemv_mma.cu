@@ -307,9 +307,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
     }
     if (peers.n) {  // this CTA's rows are out; the last CTA of the launch publishes the epoch
+      __threadfence_system();  // every lane orders its own peer stores before the count below
       __syncwarp();
       if (lane == 0) {
-        __threadfence_system();
         if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
           __threadfence();
           *peers.counter = 0;

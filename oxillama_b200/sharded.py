@@ -128,20 +128,42 @@ class PeerGather:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.rows, self.m_cap = rows_per_rank, m_cap
-        h = C.c_void_p()
-        self.ctx.check(self.ctx.lib.qk_gather_create(self.ctx.handle, rows_per_rank, m_cap, self.world, self.rank,
-                                                     C.byref(h)))
-        self.handle = h
+        # Failures are agreed on by all ranks before anyone raises, so that no rank is left
+        # waiting in a collective for one that has already given up.
+        h, err, payload = C.c_void_p(), None, None
+        try:
+            self.ctx.check(self.ctx.lib.qk_gather_create(self.ctx.handle, rows_per_rank, m_cap, self.world,
+                                                         self.rank, C.byref(h)))
+            if self.world > 1:
+                buf = (C.c_ubyte * 128)()
+                self.ctx.check(self.ctx.lib.qk_gather_export(self.ctx.handle, h, buf, 128))
+                payload = bytes(buf)
+        except Exception as e:  # noqa: BLE001
+            err = e
+        self.handle = h if err is None else None
         if self.world > 1:
-            buf = (C.c_ubyte * 128)()
-            self.ctx.check(self.ctx.lib.qk_gather_export(self.ctx.handle, h, buf, 128))
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(buf), group=group)
-            for r, hb in enumerate(handles):
-                if r != self.rank:
-                    pb = (C.c_ubyte * 128).from_buffer_copy(hb)
-                    self.ctx.check(self.ctx.lib.qk_gather_import(self.ctx.handle, h, r, pb, 128))
-            dist.barrier(group=group)
+            dist.all_gather_object(handles, payload, group=group)
+            if err is None and all(hb is not None for hb in handles):
+                try:
+                    for r, hb in enumerate(handles):
+                        if r != self.rank:
+                            pb = (C.c_ubyte * 128).from_buffer_copy(hb)
+                            self.ctx.check(self.ctx.lib.qk_gather_import(self.ctx.handle, h, r, pb, 128))
+                    self.ctx.check(self.ctx.lib.qk_gather_ready(self.ctx.handle, h))
+                except Exception as e:  # noqa: BLE001
+                    err = e
+            elif err is None:
+                err = RuntimeError("a peer rank could not create or export its gather buffer")
+            oks = [None] * self.world
+            dist.all_gather_object(oks, err is None, group=group)
+            if err is None and not all(oks):
+                err = RuntimeError("a peer rank could not import the gather buffers")
+        if err is not None:
+            if h:
+                self.ctx.lib.qk_gather_destroy(self.ctx.handle, h)
+            self.handle = None
+            raise err
         ptr = self.ctx.lib.qk_gather_buffer(h)
         self.buffer = torch.as_tensor(_DevPtr(ptr, (m_cap, self.world * rows_per_rank)), device="cuda")
 
