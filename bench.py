@@ -38,6 +38,7 @@ from oxillama_b200 import synth as S  # noqa: E402
 
 ROWS, COLS, QTYPE = 14336, 4096, S.Q4_K
 RING = 16
+NOWAIT = bool(os.environ.get("QK_BENCH_NOWAIT"))  # developer knob: fan out but never wait for the peers
 METRIC = "q4_k_gemv_weight_bandwidth"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the
@@ -231,18 +232,19 @@ def run_ours(args):
     # N > 1: every matvec's shard output goes to all ranks.  "peer": the matvec kernel stores
     # it into every rank's buffer over NVLink and publishes a flag, a bounded wait follows
     # (two buffers alternate); "nccl": an NCCL all-gather after the matvec.
-    peer = world > 1 and args.collective == "peer"
+    peer = (world > 1 or bool(os.environ.get("QK_BENCH_PEER1"))) and args.collective == "peer"
     pgs = []
     if peer:
         # every rank must take the same route: agree on whether the IPC setup worked everywhere
         from oxillama_b200.sharded import PeerGather
         ok = torch.ones(1, device="cuda")
-        try:
+        try:  # (world == 1 with QK_BENCH_PEER1: the protocol's own cost without NVLink)
             pgs = [PeerGather(ROWS, m_cap=1, ctx=ctx) for _ in range(2)]
         except Exception as e:  # noqa: BLE001 - any failure means "use the NCCL route"
             print(f"rank {rank}: peer-store gather unavailable ({e!r}); falling back to NCCL", file=sys.stderr)
             ok.zero_()
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if float(ok) == 0.0:
             peer, pgs = False, []
 
@@ -251,7 +253,7 @@ def run_ours(args):
             if peer:
                 # as in a decode chain: the kernel waits, under its prologue, until the previous
                 # matvec's blocks from all ranks have arrived, then runs and fans its own out
-                pgs[i & 1].gemm(dws[i], x, 1, after=pgs[(i + 1) & 1])
+                pgs[i & 1].gemm(dws[i], x, 1, after=None if NOWAIT else pgs[(i + 1) & 1])
                 if i == RING - 1:
                     pgs[i & 1].wait()
                 continue

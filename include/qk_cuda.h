@@ -188,7 +188,10 @@ float *qk_gather_buffer(qk_gather *g);
  * Q4_K and m <= 4 the matvec kernel itself does the peer stores; otherwise a push kernel
  * follows the ordinary one.  Every rank must make the same sequence of calls on a given
  * qk_gather, and must not start call k + 1 on it before its own qk_gather_wait_dev of
- * call k has been enqueued (alternate two qk_gather objects to overlap calls). */
+ * call k has been enqueued.  A faster rank's call k + 1 overwrites the buffer of a slower
+ * rank that may still be reading call k: alternate two qk_gather objects, each call
+ * waiting for the previous one (then no rank is ever more than one call ahead), or
+ * synchronise the ranks on the host before reusing a buffer. */
 int qk_gemm_gather_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g, void *stream);
 /* The same, for activations that are themselves gathered: x_dev (usually inside
  * qk_gather_buffer(after)) is read only once every rank's block of the latest call on

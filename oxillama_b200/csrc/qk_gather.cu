@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256)
     for (uint32_t p = 0; p < peers.n; p++)
       if (p != peers.rank) peers.y[p][off] = v;
   }
-  __threadfence_system();  // every thread orders its own peer stores before the count below
+  __threadfence();  // every thread orders its own peer stores before the count below (read on this GPU)
   __syncthreads();
   if (threadIdx.x == 0) {
     if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {

@@ -307,7 +307,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
     }
     if (peers.n) {  // this CTA's rows are out; the last CTA of the launch publishes the epoch
-      __threadfence_system();  // every lane orders its own peer stores before the count below
+      // Every lane orders its own peer stores before the count below (GPU scope: the count
+      // is read on this GPU); the one system-scope fence of the launch is the last CTA's,
+      // which has then observed every other CTA's count.  A system fence per CTA costs
+      // about 8 us per launch on B200.
+      __threadfence();
       __syncwarp();
       if (lane == 0) {
         if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {

@@ -48,7 +48,10 @@ def main():
             tol = 2e-5 if m <= 4 else 1e-3
             if not err <= tol:
                 bad += 1
-                print(f"rank {rank}: {S.NAMES[t]} m={m} call {call}: gather err {err}", flush=True)
+                blocks = [float(np.abs(got[:, r * (e - b):(r + 1) * (e - b)]).max()) for r in range(world)]
+                print(f"rank {rank}: {S.NAMES[t]} m={m} call {call}: gather err {err}; max |y| per rank block {blocks}",
+                      flush=True)
+            dist.barrier()  # the next call overwrites every rank's buffer: all must have read this one
         check_device_status()
         # the NCCL route for comparison
         yl = torch.empty((m, e - b), device="cuda")
