@@ -562,7 +562,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  pdl_wait();  // X16 and y belong to the previous kernel until it has finished
+  // The weights are immutable, so the dequant warps start at once; the activation
+  // producer (X16) and the epilogue (y, the activation scales) wait for the previous
+  // kernel below, each before its first access.
   QK_GSTAMP(threadIdx.x == 0, 1);
 
   bool dead = false;
@@ -572,6 +574,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // barrier alternates between two per stage (by use parity), so that a consumer
     // waiting for use u can never mistake the completion of use u - 2 for it.
     if (lane == 0) {
+      pdl_wait();  // X16 belongs to the previous kernel until it has finished
       uint32_t st = 0, use = 0, gstep = 0;
       for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
         const uint32_t tb = (t % n_tiles) % tok_blocks;
@@ -669,6 +672,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     uint32_t epi_it = 0, epi_rb = 0, epi_tb = 0, epi_next = 0;
     auto epi_piece = [&]() -> bool {
       const uint32_t buf = epi_it % NBUF;
+      if (epi_it == 0 && epi_next == 0) pdl_wait();  // y and the activation scales: see above
       if (epi_next == 0) {
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(sbase + S.acc_full + buf * 8, (epi_it / NBUF) & 1u)))
           return false;
@@ -929,7 +933,11 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
     if (v >= 1 && v <= 8 && v <= nsb) ks = v;
   }
   // the row is staged in shared memory between the maximum pass and the conversion when it fits
-  const uint32_t row_bytes = L.cols * 4u, cached = row_bytes <= 96u * 1024u ? 1u : 0u;
+  // The row is staged in shared memory between the two passes (measured a little faster
+  // than a second read, although a CTA holding shared memory cannot share an SM with a
+  // matmul CTA starting under it); QK_X16_STAGE=0 turns the staging off.
+  static const bool stage_rows = !(getenv("QK_X16_STAGE") && atoi(getenv("QK_X16_STAGE")) == 0);
+  const uint32_t row_bytes = L.cols * 4u, cached = (stage_rows && row_bytes <= 96u * 1024u) ? 1u : 0u;
   static bool x16_attr = false;
   if (!x16_attr) {
     cudaError_t ea = cudaFuncSetAttribute(qk_x16_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
