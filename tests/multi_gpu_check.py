@@ -5,7 +5,8 @@
 
 Every rank uploads its row shard, runs the sharded matvec / small matmul with the
 peer-store gather (`qk_gemm_gather_dev`) and with an NCCL all-gather, and compares both
-with the oracle's result for the whole matrix.  Exits non-zero on a mismatch.
+with the oracle's result for the whole matrix; then two chained sharded layers, and an
+expert-sharded mixture of experts summed by NCCL.  Exits non-zero on a mismatch.
 """
 import os
 import sys
@@ -88,6 +89,36 @@ def main():
             dist.barrier()  # nobody starts the next round while a rank still reads this one
         check_device_status()
         g1.free(), g2.free(), d1.free(), d2.free()
+    # expert-sharded mixture of experts: each rank runs its experts, NCCL sums the outputs
+    from oxillama_b200 import moe
+    for t in (S.Q4_K, S.IQ4_XS):
+        hidden, inter, n_exp, top_k, tokens = 256, 512, 8, 2, 24
+        gate = [S.gen_weight(t, inter, hidden, seed=74, stream=3 * e) for e in range(n_exp)]
+        up = [S.gen_weight(t, inter, hidden, seed=74, stream=3 * e + 1) for e in range(n_exp)]
+        down = [S.gen_weight(t, hidden, inter, seed=74, stream=3 * e + 2) for e in range(n_exp)]
+        rng = np.random.default_rng(74)
+        logits = rng.standard_normal((tokens, n_exp)).astype(np.float32)
+        x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+        deq = lambda ws, r, c: np.stack([O.dequant_matrix(t, w, r, c) for w in ws])
+        ref = O.moe_ffn_f32(deq(gate, inter, hidden), deq(up, inter, hidden), deq(down, hidden, inter), logits, x, top_k)
+        b, e = moe.expert_range(n_exp, world, rank)
+        ex = moe.MoeExperts(t, gate[b:e], up[b:e], down[b:e], hidden, inter, n_exp, expert_begin=b)
+        lg, xd = torch.from_numpy(logits).cuda(), torch.from_numpy(x).cuda()
+
+        def local_forward(lg_, x_, k_):
+            y = torch.empty((tokens, hidden), device="cuda")
+            ex.forward(lg_, x_, y, k_)
+            return y
+
+        layer = moe.ExpertShardedMoe(n_exp, world, rank, local_forward)
+        y = layer.forward(lg, xd, top_k)
+        torch.cuda.synchronize()
+        err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
+        if not err <= 2e-3:
+            bad += 1
+            print(f"rank {rank}: expert-sharded MoE {S.NAMES[t]}: err {err}", flush=True)
+        check_device_status()
+        ex.free()
     tot = torch.tensor([bad], device="cuda")
     dist.all_reduce(tot)
     if rank == 0:
