@@ -57,6 +57,9 @@ constexpr int FIRST_DW = 5;        // warp 4: activation producer
 constexpr int NTHREADS = (FIRST_DW + NDW) * 32;
 constexpr int MAX_RING = 8;        // most stages of the activation ring
 constexpr uint32_t A_HALF = BM * 64;  // bytes of one A half-stage: 128 rows of 32 fp16
+#ifndef QK_GEMM_UPG
+#define QK_GEMM_UPG 2                 // A units per dequant group: one per half-stage of a super-block (3 measured no faster)
+#endif
 
 struct GemmSmem {
   uint32_t a_full, a_empty, b_full, b_empty, acc_full, acc_empty, tmem_slot, lut;
@@ -521,7 +524,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   // epilogue leaves the columns it has read zeroed.
   constexpr uint32_t NBUF = 2 * RH * BN <= 512 ? 2 : 1;
   constexpr uint32_t TMEM_COLS = NBUF * RH * BN < 32 ? 32 : NBUF * RH * BN;
-  constexpr int NAU = 8 * RH;  // A half-stage units: unit ((g RH + rh) 2 + hf)
+  // A half-stage units: each of the four groups writes its half-stages round-robin into
+  // UPG units of its own.
+  constexpr int UPG = RH == 1 ? QK_GEMM_UPG : 2 * RH;
+  constexpr int NAU = 4 * UPG;
 
   pdl_launch_dependents();
   QK_GSTAMP(threadIdx.x == 0, 0);
@@ -603,8 +609,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     if (lane == 0) {
       const uint32_t me = warp;
       uint32_t bst = me % NB, buse = me / NB, usea = 0, i = 0;
-      const uint32_t abar = sbase + S.a_full + me * RH * 2 * 8, aebar = sbase + S.a_empty + me * RH * 2 * 8;
-      const uint32_t a0 = sbase + S.a + me * RH * 2 * A_HALF;
+      uint32_t unit = 0, upar = 0;  // the group's next unit and the parity of its use count
+      const uint32_t abar = sbase + S.a_full + me * UPG * 8, aebar = sbase + S.a_empty + me * UPG * 8;
+      const uint32_t a0 = sbase + S.a + me * UPG * A_HALF;
       for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x, i++) {
         const uint32_t buf = i % NBUF, use = i / NBUF, nsb = sb_end(t) - sb_begin(t);
         // the epilogue of the tile that last used these accumulators must have drained and zeroed them
@@ -615,11 +622,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * RH * BN;
         for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, usea++) {
-          const uint32_t apar = usea & 1u;
           const uint32_t bbar = sbase + S.b_full + ((buse & 1u) * MAX_RING + bst) * 8, bpar = (buse >> 1) & 1u;
           // both polls in flight together; the slow path only when one is not ready yet
-          const bool a_ok = mbar_try_wait(abar, apar), b_ok = mbar_try_wait(bbar, bpar);
-          if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar, apar) || !mbar_wait_bounded(bbar, bpar))) {
+          const bool a_ok = mbar_try_wait(abar + unit * 8, upar), b_ok = mbar_try_wait(bbar, bpar);
+          if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar + unit * 8, upar) || !mbar_wait_bounded(bbar, bpar))) {
             dead = true;
             break;
           }
@@ -629,8 +635,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           for (int rh = 0; rh < RH; rh++) {
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
-              const int unit = rh * 2 + hf;
-              if (unit > 0 && !mbar_wait_bounded(abar + unit * 8, apar)) {
+              if ((rh | hf) && !mbar_wait_bounded(abar + unit * 8, upar)) {
                 dead = true;
                 break;
               }
@@ -638,6 +643,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               umma_f16(tmem_d + rh * BN, umma_desc_sw64(au), umma_desc(b0 + hf * 64), IDESC, 1u);
               umma_f16(tmem_d + rh * BN, umma_desc_sw64(au + 32), umma_desc(b0 + hf * 64 + 32), IDESC, 1u);
               umma_commit(aebar + unit * 8);  // the unit is free when these two retire
+              if (++unit == (uint32_t)UPG) unit = 0, upar ^= 1u;
             }
             if (dead) break;
           }
@@ -657,10 +663,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const uint32_t r = 32 * (warp & 3u) + lane;   // weight row inside a 128-row half = accumulator lane (a warp reads lanes 32 (warp % 4) ..)
     const uint32_t chunk_in_half = r >> 3, rr = r & 7u;
     // this row in the group's half-stage units: 64-byte rows, 16-byte chunk c at c ^ ((r >> 1) & 3)
-    const uint32_t arow = sbase + S.a + grp * RH * 2 * A_HALF + r * 64, asw = (r >> 1) & 3u;
+    const uint32_t arow = sbase + S.a + grp * UPG * A_HALF + r * 64, asw = (r >> 1) & 3u;
     const uint32_t aaddr[4] = {arow + ((0u ^ asw) << 4), arow + ((1u ^ asw) << 4), arow + ((2u ^ asw) << 4),
                                arow + ((3u ^ asw) << 4)};
-    const uint32_t a_full = sbase + S.a_full + grp * RH * 2 * 8, a_empty = sbase + S.a_empty + grp * RH * 2 * 8;
+    const uint32_t a_full = sbase + S.a_full + grp * UPG * 8, a_empty = sbase + S.a_empty + grp * UPG * 8;
+    uint32_t unit = 0, upar = 0, wrapped = 0;  // next unit, parity of its use count, whether it was used before
     // Epilogue of a finished tile, in pieces of 16 columns.  With two accumulator sets the
     // pieces go between the super-blocks of the next tile, so that the stores are spread
     // out and the MMAs stay fed; with one set the next tile's MMAs wait for them, so they
@@ -778,11 +785,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           F::scales(pk[rh], grp, sc);
 #pragma unroll
           for (int hf = 0; hf < 2; hf++) {
-            const int unit = rh * 2 + hf;
             uint32_t o[4][4];
             F::expand(pk[rh], sc, grp, hf, o, sbase + S.lut);
             // the MMAs that read this unit's previous contents must have retired
-            if (u > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(a_empty + unit * 8, (u - 1) & 1u))) {
+            if (wrapped && !__all_sync(0xffffffffu, mbar_wait_bounded(a_empty + unit * 8, upar ^ 1u))) {
               dead = true;  // warp-uniform: these warps execute .aligned tcgen05 instructions later
               break;
             }
@@ -794,6 +800,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> MMA reads
             __syncwarp();
             if (lane == 0) mbar_arrive(a_full + unit * 8);
+            if (++unit == (uint32_t)UPG) unit = 0, upar ^= 1u, wrapped = 1;
           }
           if (dead) break;
         }
@@ -861,7 +868,7 @@ bool plan_gemm(int bn, int rh, GemmSmem *S, uint32_t *total) {
   // only after the MMAs that read it have retired, so its depth is what hides the L2
   // latency of the tile loads.
   const uint32_t budget = 227u * 1024u;
-  const uint32_t a_bytes = 8u * rh * A_HALF;
+  const uint32_t a_bytes = 4u * (rh == 1 ? QK_GEMM_UPG : 2u * rh) * A_HALF;
   int b_stages = (int)((budget - off - a_bytes) / s.b_stage);
   if (b_stages > MAX_RING) b_stages = MAX_RING;
   if (const char *e = getenv("QK_GEMM_BSTAGES")) {
