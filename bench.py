@@ -248,13 +248,18 @@ def run_ours(args):
         if float(ok) == 0.0:
             peer, pgs = False, []
 
-    def step():
+    def step(distance=2):
         for i in range(RING):
             if peer:
-                # as in a decode chain: the kernel waits, under its prologue, until the previous
-                # matvec's blocks from all ranks have arrived, then runs and fans its own out
-                pgs[i & 1].gemm(dws[i], x, 1, after=None if NOWAIT else pgs[(i + 1) & 1])
-                if i == RING - 1:
+                # Every matvec fans its block out to all ranks and, before it starts, waits
+                # in-kernel (under its prologue) for an earlier matvec's blocks from all ranks:
+                # distance 2 = the matvec before the previous one, whose buffer it is about to
+                # overwrite (two interleaved dependency chains, the cross-GPU hand-off hidden
+                # behind one matvec); distance 1 = the previous one (one decode chain, the
+                # hand-off exposed).  Either way every gather is waited for.
+                after = pgs[i & 1] if distance == 2 else pgs[(i + 1) & 1]
+                pgs[i & 1].gemm(dws[i], x, 1, after=None if NOWAIT else after)
+                if i >= RING - 2:
                     pgs[i & 1].wait()
                 continue
             dws[i].gemv(x, ys[i])
@@ -295,6 +300,26 @@ def run_ours(args):
         barrier()
         ms = ev[0].elapsed_time(ev[1])
         check_device_status(ctx, stream)
+        chain_ms = None
+        if peer:  # the same work as one dependent chain
+            g1 = None
+            if graph is not None:
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=stream):
+                    step(1)
+            run1 = g1.replay if g1 is not None else (lambda: step(1))
+            for _ in range(3):
+                run1()
+            barrier()
+            n1 = max(1, args.steps // 4)
+            e1 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            e1[0].record(stream)
+            for _ in range(n1):
+                run1()
+            e1[1].record(stream)
+            barrier()
+            chain_ms = e1[0].elapsed_time(e1[1]) / n1
+            check_device_status(ctx, stream)
 
         # kernel-only launch time for the roofline (no collective in the region)
         if world == 1:
@@ -330,10 +355,10 @@ def run_ours(args):
     if rank == 0 and not args.no_prefill:
         prefill = [prefill_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream),
                    prefill_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream)]
-    t = torch.tensor([ms, e2e_s * 1e3, kernel_ms], device="cuda", dtype=torch.float64)
+    t = torch.tensor([ms, e2e_s * 1e3, kernel_ms, chain_ms or 0.0], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, kernel_ms = (float(v) for v in t.cpu())
+    ms, e2e_ms, kernel_ms, chain_ms = (float(v) for v in t.cpu())
     total_bytes = algo_bytes * RING * args.steps * world
     if rank == 0:
         peak, which = peaks()
@@ -346,8 +371,9 @@ def run_ours(args):
                        "l2": f"{RING} distinct weight copies ({RING * algo_bytes / 1e6:.0f} MB) rotate, larger than L2",
                        "sharding": "none" if world == 1 else
                        f"{world} row shards of ({world}x14336)x4096; y of every matvec " +
-                       ("stored into every rank by the matvec kernel over NVLink; each matvec waits in-kernel for the previous one's blocks from all ranks" if peer
-                        else "all-gathered by NCCL")},
+                       ("stored into every rank by the matvec kernel over NVLink; each matvec first waits "
+                        "in-kernel for the blocks, from all ranks, of the matvec before the previous one "
+                        "(see dependent_chain for distance 1)" if peer else "all-gathered by NCCL")},
             "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": RING * COLS * 4, "d2h_bytes_per_step": RING * ROWS * 4,
                     "note": "qk_gemv host-pointer call per matvec; weights cached on device after first use"},
@@ -358,6 +384,11 @@ def run_ours(args):
                          "us_per_launch": kernel_ms * 1e3},
             "clocks": clocks,
         }
+        if peer and chain_ms:
+            line["dependent_chain"] = {
+                "value": algo_bytes * RING * world / (chain_ms * 1e-3) / 1e9, "unit": UNIT,
+                "ms_per_step": chain_ms,
+                "note": "same work, every matvec waiting for the previous one's blocks from all ranks"}
         if world == 1:
             line["cpu_baseline"] = cpu_gemv_rate(args.cpu_seconds)
         line["prefill"] = prefill
