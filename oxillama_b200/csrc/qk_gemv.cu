@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(NT)
     uint32_t st = item % nstage;
     uint32_t bar = sbase + S.bars + st * 8;
     mbar_expect_tx(bar, bytes);
-    bulk_g2s(sbase + S.stage + st * stage_bytes, W + qk_tile_offset(L, chunk, kt), bytes, bar);
+    bulk_g2s_stream(sbase + S.stage + st * stage_bytes, W + qk_tile_offset(L, chunk, kt), bytes, bar);
   };
 
   // Programmatic dependent launch: the next kernel in the stream may start its prologue

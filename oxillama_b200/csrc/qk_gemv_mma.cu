@@ -165,21 +165,35 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
                               unsigned char *img, uint32_t PS, uint32_t xs_off) {
   constexpr int CT = CW * 32;  // compute threads
   const uint32_t quads = Kp / 4, total = (uint32_t)M * quads;
-  constexpr int U = 4;  // quads in flight per thread
+  // Every CTA of the grid reads the same few KB of x at the same moment: each starts at
+  // a different 32-column block (whole blocks, so the 8 threads of a block stay together)
+  // to spread the requests over the L2 slices, and loads 16 bytes at a time when it can.
+  const uint32_t rot = (blockIdx.x * 40u) % total;  // a multiple of 8 quads
+  const bool vec = (cols & 3u) == 0 && ((uintptr_t)x & 15u) == 0;
+  constexpr int U = (M * 4096 / 4 + CT - 1) / CT < 4 ? (M * 4096 / 4 + CT - 1) / CT : 4;  // quads in flight per thread
   for (uint32_t base = 0; base < total; base += CT * U) {
     float v[U][4];
+    uint32_t qidx[U];
 #pragma unroll
     for (int j = 0; j < U; j++) {
-      const uint32_t it = base + j * CT + threadIdx.x;
+      const uint32_t it0 = base + j * CT + threadIdx.x;
+      uint32_t it = it0 + rot;
+      if (it >= total) it -= total;
+      qidx[j] = it0 < total ? it : 0xFFFFFFFFu;
       const uint32_t m = it / quads, e0 = (it % quads) * 4;
+      if (it0 < total && vec && e0 + 4 <= cols) {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(x + (uint64_t)m * cols + e0));
+        v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; i++)
-        v[j][i] = (it < total && e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
+        for (int i = 0; i < 4; i++)
+          v[j][i] = (it0 < total && e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
+      }
     }
 #pragma unroll
     for (int j = 0; j < U; j++) {
-      const uint32_t it = base + j * CT + threadIdx.x;
-      if (it >= total) continue;  // warp-uniform: total and CT are multiples of 32
+      const uint32_t it = qidx[j];
+      if (it == 0xFFFFFFFFu) continue;  // warp-uniform: total and CT are multiples of 32
       const uint32_t m = it / quads, e0 = (it % quads) * 4;
       float amax = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fmaxf(fabsf(v[j][2]), fabsf(v[j][3])));
       float s4 = (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
@@ -189,6 +203,7 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
         s4 += __shfl_xor_sync(0xffffffffu, s4, o);
       }
       if (!(amax < 3.0e38f)) amax = 3.0e38f;
+      QK_STAMP(threadIdx.x == 0 && j == 0 && amax >= 0.f, 122);
       const float inv = amax > 0.f ? 127.f / amax : 0.f;
       uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
@@ -262,7 +277,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
       const uint32_t bar = sbase + S.full + pst * 8;
       mbar_expect_tx(bar, bytes);
-      bulk_g2s(sbase + S.stage + pst * stage_bytes, W + qk_tile_offset(L, chunk, pkt), bytes, bar);
+      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, W + qk_tile_offset(L, chunk, pkt), bytes, bar);
       if (++pkt == L.ktiles) pkt = 0, pc++;
       if (++pst == (uint32_t)nstage) pst = 0;
     };
@@ -354,6 +369,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   }
   if (INCTA) {
     xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off);
+    QK_STAMP(warp == 0, 123);
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
   } else if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
     dead = true;
