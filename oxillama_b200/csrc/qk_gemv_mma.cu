@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(256)
 // redoing it is cheaper than a second kernel and a copy).
 template <int M, int CW>
 __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32_t Kp,
-                              unsigned char *img, uint32_t PS, uint32_t xs_off) {
+                              unsigned char *img, uint32_t PS, uint32_t xs_off, bool tell_producer) {
   constexpr int CT = CW * 32;  // compute threads
   const uint32_t quads = Kp / 4, total = (uint32_t)M * quads;
   // Every CTA of the grid reads the same few KB of x at the same moment: each starts at
@@ -193,7 +193,10 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
 #pragma unroll
     for (int j = 0; j < U; j++) {
       const uint32_t it = qidx[j];
-      if (it == 0xFFFFFFFFu) continue;  // warp-uniform: total and CT are multiples of 32
+      if (it == 0xFFFFFFFFu) {  // warp-uniform: total and CT are multiples of 32
+        if (tell_producer && base == 0 && j == 0) asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
+        continue;
+      }
       const uint32_t m = it / quads, e0 = (it % quads) * 4;
       float amax = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fmaxf(fabsf(v[j][2]), fabsf(v[j][3])));
       float s4 = (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
@@ -204,6 +207,8 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
       }
       if (!(amax < 3.0e38f)) amax = 3.0e38f;
       QK_STAMP(threadIdx.x == 0 && j == 0 && amax >= 0.f, 122);
+      // this thread's activation loads have landed: the producer may send the rest of the ring
+      if (tell_producer && base == 0 && j == 0) asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
       const float inv = amax > 0.f ? 127.f / amax : 0.f;
       uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
@@ -243,7 +248,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
                            uint64_t ldy, unsigned *status, int nstage, int nslot,
-                           uint32_t stage_bytes, SmemMma S, uint32_t Kp, QkPeers peers) {
+                           uint32_t stage_bytes, SmemMma S, uint32_t Kp, QkPeers peers, int npre) {
   constexpr int WG = CW / G;  // warps per group; a group owns every G-th chunk
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -284,13 +289,21 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     uint32_t item = 0;
     if (lane == 0) {
       // weights are immutable: their prefetch need not wait for the previous kernel
-      for (; item < (uint32_t)nstage && item < my_items; item++) issue();
+      for (; item < (uint32_t)npre && item < my_items; item++) issue();
     }
     pdl_wait();  // the x image and y belong to the previous kernel until it has finished
     QK_STAMP(true, 120);
     if (!INCTA && lane == 0) {
       mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
       bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
+    }
+    if (npre < nstage) {
+      // The rest of the first ring fill goes out once the compute warps' activation loads
+      // have landed (named barrier 2), so that those loads do not queue behind a whole
+      // ring of weight tiles from every CTA: measured 11.1 -> 9.7 us per launch at 14336 x 4096.
+      if (INCTA) asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
+      if (lane == 0)
+        for (; item < (uint32_t)nstage && item < my_items; item++) issue();
     }
     uint32_t slot = 0, sph = 0;
     for (uint32_t c = 0; c < my_chunks; c++) {
@@ -368,7 +381,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
   }
   if (INCTA) {
-    xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off);
+    xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off, npre < nstage);
     QK_STAMP(warp == 0, 123);
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
   } else if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
@@ -585,8 +598,18 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
   QkPeers pv = {};
   if (peers) pv = *peers;
+  // Weight tiles issued before the wait on the previous kernel; the rest of the ring follows
+  // the activation loads. Measured at 14336 x 4096: one tile 9.7 us, the whole ring 11.1 us
+  // (M = 1); three tiles 15.5 us against 16.1 us (M = 2). QK_PRE overrides (developer knob).
+  static int npre_env = -1;
+  if (npre_env < 0) {
+    const char *e = getenv("QK_PRE");
+    npre_env = e ? atoi(e) : 0;
+  }
+  int npre = npre_env > 0 ? npre_env : (M == 1 ? 1 : 3);
+  if (npre > P.nstage) npre = P.nstage;
   return cudaLaunchKernelEx(&cfg, kern, L, W, x, (const unsigned char *)ximg, y, ldy, status,
-                            P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv);
+                            P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv, npre);
 }
 
 // Every CTA redoing the split costs ~M*K/512 quads per thread; past this size the
