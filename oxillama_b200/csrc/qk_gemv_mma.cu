@@ -50,6 +50,7 @@
 #include "qk_formats.cuh"
 #include "qk_kernels.h"
 #include "qk_pipe.cuh"
+#include <type_traits>
 
 using namespace qkpipe;
 
@@ -86,10 +87,36 @@ struct SmemMma {
   uint32_t ximg_bytes;
 };
 
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+// Loads at a compile-time byte offset from a register base: the offset rides in the
+// instruction, where an address built in C++ costs an integer add per load.
+template <int OFF>
+__device__ __forceinline__ uint2 lds64o(uint32_t addr) {
   uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
   return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128o(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ float4 lds128fo(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int I, int N, typename Fn>
+__device__ __forceinline__ void static_for(Fn &&f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -366,7 +393,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   // B column g of this lane: digit g / 2 of sub-block 2p (g even) or 2p + 1 (g odd);
   // columns 6 and 7 are never used, so they may hold anything (digit plane 2 again)
   const uint32_t b_off = (g < 6 ? (g >> 1) : 2u) * S.PS + (g & 1u) * 32u + tig * 8;
-  const uint32_t src_base = lane & ~3u;
   // header decode constants of this lane (it unpacks sub-blocks 2 tig and 2 tig + 1)
   const bool hi_half = tig >= 2;
   const uint32_t m1 = hi_half ? 0x0F0F0F0Fu : 0x3F3F3F3Fu, m2 = hi_half ? 0x30303030u : 0u;
@@ -392,20 +418,31 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 #pragma unroll
   for (int m = 0; m < M; m++) accA[m] = accB[m] = mt[m] = 0.f;
 
-  // every shared-memory load of one super-block column, issued together
-  auto load_sb = [&](SbData<M> &D, uint32_t tile, uint32_t nbt, uint32_t kt, uint32_t sb) {
-    const uint32_t sub = kt * (QK_TILE_ELEMS / 32) + 8 * sb;  // first activation sub-block
+  // Every shared-memory load of one super-block column, issued together.  Column J of this
+  // warp is super-block wl + J * WG of the tile; the four bases are per tile, the rest of
+  // each address is a compile-time offset.
+  struct TileBase {
+    uint32_t h, q, x, xs;
+  };
+  // lane constants: header of row g, the lane's 8 nibble bytes, its digit fragment and scales
+  const uint32_t hl = wl * 1152 + g * 16, ql = wl * 1152 + 128 + g * 32 + tig * 8;
+  const uint32_t xl = sbase + S.ximg + b_off + wl * 256;
+  const uint32_t xsl = sbase + S.ximg + S.xs_off + (wl * 8 + 2 * tig) * 8;
+  const uint32_t xm = 3 * S.PS, xsm = (Kp / 32) * 8;  // per activation row
+  auto load_sb = [&](SbData<M> &D, const TileBase &B, auto jt) {
+    constexpr int J = decltype(jt)::value;
     // block-major tile: super-block column sb = 1152 bytes, 8 headers then 4 x 8 x 32 nibbles
-    D.h = lds128(tile + sb * 1152 + g * 16);
-    const uint32_t qa = tile + sb * 1152 + 128 + g * 32 + tig * 8;
-#pragma unroll
-    for (int gq = 0; gq < 4; gq++) D.w[gq] = lds64(qa + gq * 256);
-    const uint32_t xb = sbase + S.ximg + sub * 32 + b_off;
+    D.h = lds128o<J * WG * 1152>(B.h);
+    static_for<0, 4>([&](auto gq) {
+      D.w[decltype(gq)::value] = lds64o<J * WG * 1152 + decltype(gq)::value * 256>(B.q);
+    });
 #pragma unroll
     for (int m = 0; m < M; m++) {
-      D.xs[m] = lds128f(sbase + S.ximg + S.xs_off + (m * (Kp / 32) + sub + 2 * tig) * 8);
-#pragma unroll
-      for (int gq = 0; gq < 4; gq++) D.b[m][gq] = lds64(xb + m * 3 * S.PS + gq * 64);
+      D.xs[m] = lds128fo<J * WG * 64>(B.xs + m * xsm);
+      const uint32_t xb = B.x + m * xm;
+      static_for<0, 4>([&](auto gq) {
+        D.b[m][decltype(gq)::value] = lds64o<J * WG * 256 + decltype(gq)::value * 64>(xb);
+      });
     }
   };
   auto compute_sb = [&](const SbData<M> &D) {
@@ -434,8 +471,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
                  D.b[m][gq].x, D.b[m][gq].y);
 #pragma unroll
       for (int gq = 0; gq < 4; gq++) {
-        const float sx = __shfl_sync(0xffffffffu, tx, src_base + gq);
-        const float sy = __shfl_sync(0xffffffffu, ty, src_base + gq);
+        // lane gq of this lane's group of four (width 4: the source lane is an immediate)
+        const float sx = __shfl_sync(0xffffffffu, tx, gq, 4);
+        const float sy = __shfl_sync(0xffffffffu, ty, gq, 4);
         accA[m] = fmaf(sx, __int2float_rn(c[gq][0]), accA[m]);
         accB[m] = fmaf(sy, __int2float_rn(c[gq][3] - c[gq][1]), accB[m]);
       }
@@ -463,20 +501,31 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       QK_STAMP(warp == 0 && tstamp < 30, 2 + 2 * tstamp);
       // software pipeline over this warp's columns (fully unrolled, two register
       // buffers): the next column's loads are in flight while the current one is
-      // decoded, multiplied and scaled
-      {
+      // decoded, multiplied and scaled.  A full tile (all but the last k-tile of a K that
+      // is not a multiple of the tile width) runs without the per-column bound checks.
+      const TileBase B = {tile + hl, tile + ql, xl + kt * (QK_TILE_ELEMS / 32) * 32,
+                          xsl + kt * (QK_TILE_ELEMS / 32) * 8};
+      auto tile_body = [&](auto full_tag) {
+        constexpr bool FULL = decltype(full_tag)::value;
         constexpr int NSB = NBT / WG;  // columns of a full tile per warp
         SbData<M> d0, d1;
-        if (wl < nbt) load_sb(d0, tile, nbt, kt, wl);
-#pragma unroll
-        for (int j = 0; j < NSB; j += 2) {
-          const uint32_t sb0 = wl + j * WG, sb1 = sb0 + WG, sb2 = sb1 + WG;
-          if (NSB > 1 && sb1 < nbt) load_sb(d1, tile, nbt, kt, sb1);
-          if (sb0 < nbt) compute_sb(d0);
-          if (j + 2 < NSB && sb2 < nbt) load_sb(d0, tile, nbt, kt, sb2);
-          if (NSB > 1 && sb1 < nbt) compute_sb(d1);
-        }
-      }
+        if (FULL || wl < nbt) load_sb(d0, B, std::integral_constant<int, 0>{});
+        static_for<0, (NSB + 1) / 2>([&](auto pt) {
+          constexpr int J = 2 * decltype(pt)::value;
+          const uint32_t sb0 = wl + J * WG, sb1 = sb0 + WG, sb2 = sb1 + WG;
+          if constexpr (J + 1 < NSB)
+            if (FULL || sb1 < nbt) load_sb(d1, B, std::integral_constant<int, J + 1>{});
+          if (FULL || sb0 < nbt) compute_sb(d0);
+          if constexpr (J + 2 < NSB)
+            if (FULL || sb2 < nbt) load_sb(d0, B, std::integral_constant<int, J + 2>{});
+          if constexpr (J + 1 < NSB)
+            if (FULL || sb1 < nbt) compute_sb(d1);
+        });
+      };
+      if (nbt == NBT)
+        tile_body(std::true_type{});
+      else
+        tile_body(std::false_type{});
       QK_STAMP(warp == 0 && tstamp < 30, 3 + 2 * tstamp);
       tstamp++;
       advance_stage(1);
