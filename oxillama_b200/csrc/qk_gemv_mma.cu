@@ -134,6 +134,29 @@ __device__ __forceinline__ float small_int_to_float(int v) {
   return __int_as_float(0x4B400000 + v) - 12582912.0f;
 }
 
+// Four activations of one 32-column block -> their three balanced base-254 digits, one
+// packed word per digit plane: x ~ (amax / 127) (d0 + d1 / 254 + d2 / 254^2).  Adding
+// 1.5 * 2^23 rounds to the nearest integer and leaves it, as two's complement, in the low
+// mantissa byte; with |v| <= amax every digit lies in [-127, 127] without a clamp.  (Values
+// that are not finite give arbitrary digits: the product is meaningless for them anyway.)
+__device__ __forceinline__ void split_quad(const float (&v)[4], float inv, uint32_t &w0, uint32_t &w1,
+                                           uint32_t &w2) {
+  constexpr float MAGIC = 12582912.f;
+  uint32_t b0[4], b1[4], b2[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const float t0 = fmaf(v[i], inv, MAGIC);
+    const float r1 = fmaf(v[i], inv, -(t0 - MAGIC));  // exact residual of the first digit
+    const float t1 = fmaf(r1, 254.f, MAGIC);
+    const float r2 = fmaf(r1, 254.f, -(t1 - MAGIC));
+    const float t2 = fmaf(r2, 254.f, MAGIC);
+    b0[i] = __float_as_uint(t0), b1[i] = __float_as_uint(t1), b2[i] = __float_as_uint(t2);
+  }
+  w0 = __byte_perm(__byte_perm(b0[0], b0[1], 0x0040), __byte_perm(b0[2], b0[3], 0x0040), 0x5410);
+  w1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
+  w2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
+}
+
 // ---------------------------------------------------------------- x image
 // [M][3 digit planes of PS bytes, natural column order][M][Kp/32] float2 (sx, Sx)
 __global__ void __launch_bounds__(256)
@@ -161,19 +184,10 @@ __global__ void __launch_bounds__(256)
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     s4 += __shfl_xor_sync(0xffffffffu, s4, o);
   }
-  if (!(amax < 3.0e38f)) amax = 3.0e38f;  // inf/nan in x: keep the arithmetic finite
-  const float inv = amax > 0.f ? 127.f / amax : 0.f;
-  uint32_t w0 = 0, w1 = 0, w2 = 0;
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    float d0 = fminf(fmaxf(rintf(v[i] * inv), -127.f), 127.f);
-    float t1 = fmaf(v[i], inv, -d0) * 254.f;
-    float d1 = fminf(fmaxf(rintf(t1), -127.f), 127.f);
-    float d2 = fminf(fmaxf(rintf((t1 - d1) * 254.f), -127.f), 127.f);
-    w0 |= ((uint32_t)(int)d0 & 0xFFu) << (8 * i);
-    w1 |= ((uint32_t)(int)d1 & 0xFFu) << (8 * i);
-    w2 |= ((uint32_t)(int)d2 & 0xFFu) << (8 * i);
-  }
+  if (!(amax < 8.0e37f)) amax = 8.0e37f;  // inf/nan/huge x: keep the scale finite (__fdividef: y < 2^126)
+  const float inv = amax > 0.f ? __fdividef(127.f, amax) : 0.f;
+  uint32_t w0, w1, w2;
+  split_quad(v, inv, w0, w1, w2);
   unsigned char *p = img + (size_t)m * 3 * PS + e0;
   *reinterpret_cast<uint32_t *>(p) = w0;
   *reinterpret_cast<uint32_t *>(p + PS) = w1;
@@ -207,7 +221,7 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
       uint32_t it = it0 + rot;
       if (it >= total) it -= total;
       qidx[j] = it0 < total ? it : 0xFFFFFFFFu;
-      const uint32_t m = it / quads, e0 = (it % quads) * 4;
+      const uint32_t m = M == 1 ? 0u : it / quads, e0 = (M == 1 ? it : it % quads) * 4;
       if (it0 < total && vec && e0 + 4 <= cols) {
         const float4 q = __ldg(reinterpret_cast<const float4 *>(x + (uint64_t)m * cols + e0));
         v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
@@ -217,14 +231,14 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
           v[j][i] = (it0 < total && e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
       }
     }
+    // This thread's first activation loads are on their way: the producer may send the rest
+    // of the ring behind them.
+    if (tell_producer && base == 0) asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
 #pragma unroll
     for (int j = 0; j < U; j++) {
       const uint32_t it = qidx[j];
-      if (it == 0xFFFFFFFFu) {  // warp-uniform: total and CT are multiples of 32
-        if (tell_producer && base == 0 && j == 0) asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
-        continue;
-      }
-      const uint32_t m = it / quads, e0 = (it % quads) * 4;
+      if (it == 0xFFFFFFFFu) continue;  // warp-uniform: total and CT are multiples of 32
+      const uint32_t m = M == 1 ? 0u : it / quads, e0 = (M == 1 ? it : it % quads) * 4;
       float amax = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fmaxf(fabsf(v[j][2]), fabsf(v[j][3])));
       float s4 = (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
 #pragma unroll
@@ -232,22 +246,11 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         s4 += __shfl_xor_sync(0xffffffffu, s4, o);
       }
-      if (!(amax < 3.0e38f)) amax = 3.0e38f;
+      if (!(amax < 8.0e37f)) amax = 8.0e37f;
       QK_STAMP(threadIdx.x == 0 && j == 0 && amax >= 0.f, 122);
-      // this thread's activation loads have landed: the producer may send the rest of the ring
-      if (tell_producer && base == 0 && j == 0) asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
-      const float inv = amax > 0.f ? 127.f / amax : 0.f;
-      uint32_t w0 = 0, w1 = 0, w2 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        float d0 = fminf(fmaxf(rintf(v[j][i] * inv), -127.f), 127.f);
-        float t1 = fmaf(v[j][i], inv, -d0) * 254.f;
-        float d1 = fminf(fmaxf(rintf(t1), -127.f), 127.f);
-        float d2 = fminf(fmaxf(rintf((t1 - d1) * 254.f), -127.f), 127.f);
-        w0 |= ((uint32_t)(int)d0 & 0xFFu) << (8 * i);
-        w1 |= ((uint32_t)(int)d1 & 0xFFu) << (8 * i);
-        w2 |= ((uint32_t)(int)d2 & 0xFFu) << (8 * i);
-      }
+      const float inv = amax > 0.f ? __fdividef(127.f, amax) : 0.f;
+      uint32_t w0, w1, w2;
+      split_quad(v[j], inv, w0, w1, w2);
       unsigned char *p = img + (size_t)m * 3 * PS + e0;
       *reinterpret_cast<uint32_t *>(p) = w0;
       *reinterpret_cast<uint32_t *>(p + PS) = w1;
@@ -554,8 +557,22 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 struct PlanMma {
   SmemMma S;
   uint32_t Kp, stage_bytes, total;
-  int nstage, nslot, groups;
+  int nstage, nslot, groups, cw;
 };
+
+// Compute warps per CTA.  16 stream best at M = 1; from M = 2 their 96-register budget spills
+// (18 / 36 / 56 us at M = 2 / 3 / 4 on the 14336 x 4096 shape), 8 warps with twice the
+// registers do not (15 / 21 / 31 us).  QK_CW overrides (developer knob).
+int compute_warps(uint32_t m) {
+  static int cw_env = -1;
+  if (cw_env < 0) {
+    const char *e = getenv("QK_CW");
+    const int v = e ? atoi(e) : 0;
+    cw_env = (v == 8 || v == 12 || v == 16) ? v : 0;
+  }
+  if (cw_env == 12) return m == 1 ? 12 : 8;
+  return cw_env ? cw_env : (m >= 2 ? 8 : 16);
+}
 
 bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   uint32_t Kp = L.nb * 256u;
@@ -591,7 +608,15 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   int groups = 1;
   const char *ge = getenv("QK_GROUPS");
   const int gmax = ge ? atoi(ge) : 4;
-  for (int gtry = 4; gtry >= 2; gtry >>= 1) {
+  int cw = compute_warps(m);
+  if (cw == 12) {  // three groups of four warps, if the ring can hold three chunks
+    const int unit = 3 * (int)L.ktiles;
+    if (nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1)
+      groups = 3, nstage = (nstage / unit) * unit;
+    else
+      cw = 16;
+  }
+  for (int gtry = 4; gtry >= 2 && cw != 12; gtry >>= 1) {
     const int unit = gtry * (int)L.ktiles;
     if (gtry <= gmax && nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1) {
       groups = gtry;
@@ -599,7 +624,7 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
       break;
     }
   }
-  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1, P->groups = groups;
+  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1, P->groups = groups, P->cw = cw;
   P->total = off + nstage * stage_bytes;
   return true;
 }
@@ -680,19 +705,13 @@ cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, fl
   // Warp groups: a group owns every G-th chunk.  A stage must always be consumed by
   // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
   // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
-  // 16 compute warps stream best at M = 1; from M = 2 their 96-register budget spills
-  // (18 / 36 / 56 us at M = 2 / 3 / 4 on the 14336 x 4096 shape), 8 warps with twice the
-  // registers do not (15 / 21 / 31 us).  QK_CW overrides.
-  static int cw_env = -1;
-  if (cw_env < 0) {
-    const char *e = getenv("QK_CW");
-    cw_env = e ? (atoi(e) == 8 ? 8 : 16) : 0;
-  }
-  const int cw = cw_env ? cw_env : (M >= 2 ? 8 : 16);
+  const int cw = P.cw;
 #define QK_LAUNCH(CWV, GV)                                                                       \
   return split_in_cta(P, M)                                                                      \
              ? launch_mma<M, true, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
              : launch_mma<M, false, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers)
+  if constexpr (M == 1)
+    if (cw == 12) QK_LAUNCH(12, 3);
   if (cw == 8) {
     switch (P.groups) {
       case 4:
