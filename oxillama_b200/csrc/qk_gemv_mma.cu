@@ -560,18 +560,22 @@ struct PlanMma {
   int nstage, nslot, groups, cw;
 };
 
-// Compute warps per CTA.  16 stream best at M = 1; from M = 2 their 96-register budget spills
-// (18 / 36 / 56 us at M = 2 / 3 / 4 on the 14336 x 4096 shape), 8 warps with twice the
-// registers do not (15 / 21 / 31 us).  QK_CW overrides (developer knob).
-int compute_warps(uint32_t m) {
+// Compute warps per CTA (+ one producer / reducer warp).  With 16 the register budget is 96
+// per thread and the column pipeline spills; 8 warps (up to 255 registers) stream as fast or
+// faster at every M (14336 x 4096, M = 1: 8.2 us against 8.8 us).  12 warps in three groups
+// (128 registers) start and finish sooner when a CTA has few chunks: 3.3 against 3.8 us at
+// 1024 rows, 4.6 against 4.7 us at 4096, level from 14336 rows on.  QK_CW overrides
+// (developer knob: 8, 12 or 16).
+int compute_warps(const QkLayout &L, uint32_t m) {
   static int cw_env = -1;
   if (cw_env < 0) {
     const char *e = getenv("QK_CW");
     const int v = e ? atoi(e) : 0;
     cw_env = (v == 8 || v == 12 || v == 16) ? v : 0;
   }
-  if (cw_env == 12) return m == 1 ? 12 : 8;
-  return cw_env ? cw_env : (m >= 2 ? 8 : 16);
+  if (m >= 2) return cw_env == 16 ? 16 : 8;  // the 12-warp kernel is built for M = 1 only
+  if (cw_env) return cw_env;
+  return (L.ktiles == 1 && L.chunks <= 1024) ? 12 : 8;
 }
 
 bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
@@ -608,13 +612,13 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   int groups = 1;
   const char *ge = getenv("QK_GROUPS");
   const int gmax = ge ? atoi(ge) : 4;
-  int cw = compute_warps(m);
+  int cw = compute_warps(L, m);
   if (cw == 12) {  // three groups of four warps, if the ring can hold three chunks
     const int unit = 3 * (int)L.ktiles;
     if (nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1)
       groups = 3, nstage = (nstage / unit) * unit;
     else
-      cw = 16;
+      cw = 8;
   }
   for (int gtry = 4; gtry >= 2 && cw != 12; gtry >>= 1) {
     const int unit = gtry * (int)L.ktiles;
@@ -673,14 +677,15 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   QkPeers pv = {};
   if (peers) pv = *peers;
   // Weight tiles issued before the wait on the previous kernel; the rest of the ring follows
-  // the activation loads. Measured at 14336 x 4096: one tile 9.7 us, the whole ring 11.1 us
-  // (M = 1); three tiles 15.5 us against 16.1 us (M = 2). QK_PRE overrides (developer knob).
+  // the activation loads.  Measured at 14336 x 4096, M = 1, 8 warps: 1 tile 8.2 us, 2 8.3,
+  // 3 8.6, 4 8.8, 6 9.2; M = 2: 2 tiles 13.1 us, 3 12.9, 4 12.7.  QK_PRE overrides
+  // (developer knob).
   static int npre_env = -1;
   if (npre_env < 0) {
     const char *e = getenv("QK_PRE");
     npre_env = e ? atoi(e) : 0;
   }
-  int npre = npre_env > 0 ? npre_env : (M == 1 ? 1 : 3);
+  int npre = npre_env > 0 ? npre_env : (M == 1 ? (CW == 12 ? 2 : 1) : (M == 2 ? 4 : 3));
   if (npre > P.nstage) npre = P.nstage;
   return cudaLaunchKernelEx(&cfg, kern, L, W, x, (const unsigned char *)ximg, y, ldy, status,
                             P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv, npre);
@@ -773,11 +778,11 @@ cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, co
 #define QK_SPLIT(MV)                                                                             \
   switch (P.groups) {                                                                            \
     case 4:                                                                                      \
-      return launch_mma<MV, false, 16, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+      return launch_mma<MV, false, 8, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
     case 2:                                                                                      \
-      return launch_mma<MV, false, 16, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+      return launch_mma<MV, false, 8, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
     default:                                                                                     \
-      return launch_mma<MV, false, 16, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+      return launch_mma<MV, false, 8, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
   }
   switch (m) {
     case 1:
