@@ -68,16 +68,18 @@ struct Smem {
 };
 
 // Fills the CTA's digit planes and block statistics from x (global, f32).
-template <int TYPE, int M, int D>
+// `after_first_loads` runs once per thread, right after its first activation loads are issued.
+template <int TYPE, int M, int D, typename F>
 __device__ void prep_x(const QkLayout &L, const float *__restrict__ x, unsigned char *smem,
-                       const Smem &S, uint32_t Kp) {
+                       const Smem &S, uint32_t Kp, F &&after_first_loads) {
   const uint32_t quads = Kp / 4;
   for (uint32_t it = threadIdx.x; it < (uint32_t)M * quads; it += NT) {
-    uint32_t m = it / quads, q = it % quads, e0 = q * 4;
+    uint32_t m = M == 1 ? 0u : it / quads, q = M == 1 ? it : it % quads, e0 = q * 4;
     float v[4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
       v[i] = (e0 + i < L.cols) ? x[(uint64_t)m * L.cols + e0 + i] : 0.f;
+    if (it == threadIdx.x) after_first_loads();
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
     float s4 = (v[0] + v[1]) + (v[2] + v[3]);
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -86,21 +88,24 @@ __device__ void prep_x(const QkLayout &L, const float *__restrict__ x, unsigned 
     s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
     s4 += __shfl_xor_sync(0xffffffffu, s4, 2);  // sum of this thread's 16-column half
     float other = __shfl_xor_sync(0xffffffffu, s4, 4);
-    if (!(amax < 3.0e38f)) amax = 3.0e38f;  // inf/nan in x: keep the arithmetic finite
-    float inv = amax > 0.f ? 127.f / amax : 0.f;
+    if (!(amax < 8.0e37f)) amax = 8.0e37f;  // inf/nan/huge x: keep the scale finite (__fdividef: y < 2^126)
+    float inv = amax > 0.f ? __fdividef(127.f, amax) : 0.f;
+    // Balanced base-254 digits by magic-number rounding: adding 1.5 * 2^23 rounds to the
+    // nearest integer and leaves it, as two's complement, in the low mantissa byte; with
+    // |v| <= amax every digit lies in [-127, 127] without a clamp.
+    constexpr float MAGIC = 12582912.f;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      float t0 = v[i] * inv;
-      float d0 = rintf(t0);
-      d0 = fminf(fmaxf(d0, -127.f), 127.f);
-      float t1 = fmaf(v[i], inv, -d0) * 254.f;
-      float d1 = fminf(fmaxf(rintf(t1), -127.f), 127.f);
-      float d2 = fminf(fmaxf(rintf((t1 - d1) * 254.f), -127.f), 127.f);
+      const float t0 = fmaf(v[i], inv, MAGIC);
+      const float r1 = fmaf(v[i], inv, -(t0 - MAGIC));  // exact residual of the first digit
+      const float t1 = fmaf(r1, 254.f, MAGIC);
+      const float r2 = fmaf(r1, 254.f, -(t1 - MAGIC));
+      const float t2 = fmaf(r2, 254.f, MAGIC);
       uint32_t pos = x_pos<TYPE>(e0 + i);
       unsigned char *base = smem + S.xd + (size_t)m * D * Kp + pos;
-      base[0] = (unsigned char)(int)d0;
-      base[Kp] = (unsigned char)(int)d1;
-      if (D == 3) base[2 * Kp] = (unsigned char)(int)d2;
+      base[0] = (unsigned char)__float_as_uint(t0);
+      base[Kp] = (unsigned char)__float_as_uint(t1);
+      if (D == 3) base[2 * Kp] = (unsigned char)__float_as_uint(t2);
     }
     if ((threadIdx.x & 7) == 0) {
       float4 st = make_float4(amax * (1.f / 127.f), s4 + other, s4, other);
@@ -123,7 +128,7 @@ template <int TYPE, int M, int D, int RS>
 __global__ void __launch_bounds__(NT)
     qk_gemv_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
                    float *__restrict__ y, uint64_t ldy, unsigned *status, int nstage,
-                   uint32_t stage_bytes, Smem S, uint32_t Kp) {
+                   uint32_t stage_bytes, Smem S, uint32_t Kp, int npre) {
   extern __shared__ __align__(128) unsigned char smem[];
   // Eight neighbouring lanes take the eight rows of a chunk and the same 64-weight unit:
   // their 16-byte weight reads are one 128-byte span of the block-major tile (no bank
@@ -158,10 +163,16 @@ __global__ void __launch_bounds__(NT)
     for (int s = 0; s < nstage; s++) mbar_init(sbase + S.bars + s * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (uint32_t i = 0; i < (uint32_t)nstage && i < my_items; i++) issue(i);
+    for (uint32_t i = 0; i < (uint32_t)npre && i < my_items; i++) issue(i);
   }
   pdl_wait();  // x and y belong to the previous kernel until it has finished
-  prep_x<TYPE, M, D>(L, x, smem, S, Kp);
+  // The rest of the first ring fill goes out behind the activation loads, not ahead of
+  // them: queued behind a whole ring of weight tiles from every CTA those loads take
+  // about a microsecond longer.
+  prep_x<TYPE, M, D>(L, x, smem, S, Kp, [&]() {
+    if (threadIdx.x == 0)
+      for (uint32_t i = (uint32_t)npre; i < (uint32_t)nstage && i < my_items; i++) issue(i);
+  });
   __syncthreads();
 
   float acc[M][RPT];
@@ -429,7 +440,17 @@ cudaError_t launch_one(const QkLayout &L, const uint8_t *W, const float *x, floa
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NT), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, x, y, ldy, status, P.nstage, P.stage_bytes, P.S, P.Kp);
+  static int npre_env = -1;  // developer knob: weight tiles issued before the wait on the previous kernel
+  if (npre_env < 0) {
+    const char *e = getenv("QK_PRE");
+    npre_env = e ? atoi(e) : 0;
+  }
+  // Default: the whole ring.  Holding tiles back until the activation loads are out (what
+  // the Q4_K kernel does) measured within 3 % either way here: Q8_0 4096^2 7.9 us with two
+  // tiles first against 8.1 us, Q6_K 4096 x 14336 28.9 us against 28.2 us.
+  int npre = npre_env > 0 ? npre_env : P.nstage;
+  if (npre > P.nstage) npre = P.nstage;
+  return cudaLaunchKernelEx(&cfg, kern, L, W, x, y, ldy, status, P.nstage, P.stage_bytes, P.S, P.Kp, npre);
 }
 
 // Row splits: as many rows per thread as still leave every warp a unit to work on.

@@ -29,20 +29,21 @@
 // with d, dmin, sc, mn decoded as reference/q4_k.rs:27-49,141-157 and Sx the
 // f32 sum of x over the sub-block (the `- m1` term of reference/q4_k.rs:163).
 //
-// Two kernels per call:
-//  1. qk_xsplit_kernel splits x once into the digit planes and (sx, Sx) pairs
-//     and leaves them in a small scratch image in global memory;
-//  2. qk_gemv_q4k_mma_kernel, persistent, one CTA per SM: a producer warp
-//     streams 8-row tiles into a ring of shared-memory stages with
-//     cp.async.bulk (mbarrier completion) and brings the x image in with one
-//     more bulk copy; 8 compute warps take two super-block columns of the tile
-//     each (header decode in-lane, four MMAs per column) and leave their row
-//     partials in a small ring; the producer warp sums a chunk's partials, writes
-//     the outputs and then refills the chunk's stages.  No CTA-wide barrier and
-//     no compute warp ever waits for another in steady state.
-// Both kernels use programmatic dependent launch: the weight prefetch of call
-// i+1 (weights are immutable) overlaps the tail of call i; griddepcontrol.wait
-// orders everything that touches x, y or the scratch image.  Every wait on an
+// qk_gemv_q4k_mma_kernel, persistent, one CTA per SM: a producer warp streams 8-row
+// tiles into a ring of shared-memory stages with cp.async.bulk (mbarrier completion);
+// the compute warps (8 in four groups; 12 in three for short matrices) first split x
+// into the digit planes and (sx, Sx) pairs in shared memory, then a group takes every
+// G-th chunk, each warp its share of the tile's super-block columns (header decode
+// in-lane, four MMAs per column), and leaves its row partials in a small ring; the
+// producer warp sums a chunk's partials, writes the outputs and then refills the chunk's
+// stages.  No CTA-wide barrier and no compute warp ever waits for another in steady
+// state.  When M * K is too large for every CTA to redo the split, qk_xsplit_kernel
+// does it once into a scratch image in global memory, which each CTA brings in with one
+// more bulk copy.
+// Both kernels use programmatic dependent launch: call i+1 is resident and has its first
+// weight tiles (weights are immutable) under way before call i has finished;
+// griddepcontrol.wait orders everything that touches x, y or the scratch image, and the
+// rest of the ring is issued behind the activation loads, not ahead of them.  Every wait on an
 // mbarrier is bounded: when one runs out the warp stops, QK_DEV_TIMEOUT is
 // raised in the status word, and the other warps run into their own bounds.
 #include <cstdlib>
