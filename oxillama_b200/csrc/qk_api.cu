@@ -496,8 +496,22 @@ static int host_gemm(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t
   if ((st = grow(c, &c->sa, &c->sa_cap, xb ? xb : 4))) return st;
   if ((st = grow(c, &c->sb, &c->sb_cap, yb ? yb : 4))) return st;
   if (xb) CK(c, cudaMemcpyAsync(c->sa, x, xb, cudaMemcpyHostToDevice, c->stream));
-  if ((st = gemm_dispatch(c, h, (const float *)c->sa, (float *)c->sb, m, n, c->stream))) return st;
-  if (yb) CK(c, cudaMemcpyAsync(y, c->sb, yb, cudaMemcpyDeviceToHost, c->stream));
+  // Decode-sized calls into pinned host memory: the kernels that serve M <= 4 only store y
+  // (a few KB, 32 contiguous bytes per 8-row chunk), so they write it straight through the
+  // mapping and the device-to-host copy with its launch drops out.  (Not IQ4_XS: its
+  // tensor-core path accumulates into y.)
+  float *ydev = (float *)c->sb;
+  bool mapped = false;
+  if (yb && m <= QK_GEMV_MAX_M && type != QK_T_IQ4_XS) {
+    cudaPointerAttributes pa;
+    if (cudaPointerGetAttributes(&pa, y) == cudaSuccess && pa.type == cudaMemoryTypeHost &&
+        pa.devicePointer)
+      ydev = (float *)pa.devicePointer, mapped = true;
+    else
+      (void)cudaGetLastError();
+  }
+  if ((st = gemm_dispatch(c, h, (const float *)c->sa, ydev, m, n, c->stream))) return st;
+  if (yb && !mapped) CK(c, cudaMemcpyAsync(y, c->sb, yb, cudaMemcpyDeviceToHost, c->stream));
   CK(c, cudaStreamSynchronize(c->stream));
   return QK_OK;
 }

@@ -88,6 +88,31 @@ def test_gemv_matches_oracle(K, disp, t, rows, cols):
     assert rel_inf(y, ref) <= tolf(t), rel_inf(y, ref)
 
 
+@pytest.mark.parametrize("t", [t for t in S.ALL_TYPES if t != S.IQ4_XS])
+@pytest.mark.parametrize("m", [1, 3])
+def test_pinned_output_written_through_the_mapping(K, disp, t, m):
+    """Decode-sized calls whose output is pinned host memory store y straight through its
+    device mapping (no device-to-host copy): same bits as the copy route.  (IQ4_XS always
+    takes the copy route: its tensor-core path accumulates into y.)"""
+    import torch
+    rows, cols = 520, 1024
+    w = S.gen_weight(t, rows, cols, seed=31)
+    x = S.gen_acts(m, cols, seed=31)
+    qt = K.QuantTensor(w, (rows, cols), t)
+    y_copy = np.full((m, rows), np.nan, np.float32)
+    y_pin_t = torch.full((m, rows), float("nan")).pin_memory()
+    y_pin = y_pin_t.numpy()
+    k = disp.get_kernel(t)
+    if m == 1:
+        k.gemv(qt, x[0], y_copy[0])
+        k.gemv(qt, x[0], y_pin[0])
+    else:
+        k.gemm(qt, x, y_copy, m, rows, cols)
+        k.gemm(qt, x, y_pin, m, rows, cols)
+    assert np.all(np.isfinite(y_pin))
+    assert np.array_equal(y_pin, y_copy)
+
+
 @pytest.mark.parametrize("t", S.ALL_TYPES)
 @pytest.mark.parametrize("m", [2, 3, 4, 8, 13])
 def test_gemm_matches_oracle(K, disp, t, m):
