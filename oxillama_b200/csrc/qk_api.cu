@@ -90,15 +90,19 @@ extern "C" int qk_init(int device, qk_ctx **out) {
     return QK_CUDA_ERROR;
   }
   c->sm_count = prop.multiProcessorCount;
+  unsigned *sh = nullptr;
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaMalloc(&c->status_dev, sizeof(unsigned)) != cudaSuccess ||
-      cudaMemset(c->status_dev, 0, sizeof(unsigned)) != cudaSuccess ||
+      cudaHostAlloc((void **)&sh, sizeof(unsigned), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess ||
+      cudaHostGetDevicePointer((void **)&c->status_dev, sh, 0) != cudaSuccess ||
       cudaMalloc(&c->scratch, (size_t)1 << 20) != cudaSuccess) {
+    if (sh) cudaFreeHost(sh);
     delete c;
     return QK_CUDA_ERROR;
   }
+  *sh = 0;
+  c->status_host = sh;
   c->scratch_cap = (size_t)1 << 20;
-  const char *fs = getenv("QK_FORCE_SIMPLE");
+  const char *fs = qk_knob("QK_FORCE_SIMPLE");
   c->force_simple = fs && fs[0] == '1';
   *out = c;
   return QK_OK;
@@ -117,7 +121,7 @@ extern "C" int qk_shutdown(qk_ctx *c) {
   for (auto &kv : c->cache) free_weights(kv.second);
   if (c->sa) cudaFree(c->sa);
   if (c->sb) cudaFree(c->sb);
-  cudaFree(c->status_dev);
+  cudaFreeHost((void *)c->status_host);
   if (c->scratch) cudaFree(c->scratch);
   if (c->moe) cudaFree(c->moe);
   cudaStreamDestroy(c->stream);
@@ -432,17 +436,19 @@ extern "C" int qk_quantize_q8_0_dev(qk_ctx *c, const float *x_dev, size_t n, uin
   return QK_OK;
 }
 
+// Reads and clears the status word; the stream that ran the kernels must have been synchronised.
+static int take_device_status(qk_ctx *c) {
+  const unsigned v = *c->status_host;
+  if (!v) return QK_OK;
+  *c->status_host = 0;
+  c->err = (v & QK_DEV_TIMEOUT) ? "device-side wait ran out" : "device-side range check tripped";
+  return (v & QK_DEV_TIMEOUT) ? QK_TIMEOUT : QK_KERNEL_ERROR;
+}
+
 extern "C" int qk_check_device_status(qk_ctx *c, void *stream) {
   if (!c) return QK_INVALID_ARGUMENT;
-  unsigned v = 0;
-  CK(c, cudaMemcpyAsync(&v, c->status_dev, sizeof(v), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   CK(c, cudaStreamSynchronize((cudaStream_t)stream));
-  if (v) {
-    CK(c, cudaMemsetAsync(c->status_dev, 0, sizeof(v), (cudaStream_t)stream));
-    c->err = (v & QK_DEV_TIMEOUT) ? "device-side wait ran out" : "device-side range check tripped";
-    return (v & QK_DEV_TIMEOUT) ? QK_TIMEOUT : QK_KERNEL_ERROR;
-  }
-  return QK_OK;
+  return take_device_status(c);
 }
 
 // ------------------------------------------------------------ host-pointer entry points
@@ -513,7 +519,7 @@ static int host_gemm(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t
   if ((st = gemm_dispatch(c, h, (const float *)c->sa, ydev, m, n, c->stream))) return st;
   if (yb && !mapped) CK(c, cudaMemcpyAsync(y, c->sb, yb, cudaMemcpyDeviceToHost, c->stream));
   CK(c, cudaStreamSynchronize(c->stream));
-  return QK_OK;
+  return take_device_status(c);  // a bounded wait that ran out leaves y invalid: say so
 }
 
 extern "C" int qk_gemv(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows,

@@ -871,7 +871,7 @@ bool plan_gemm(int bn, int rh, GemmSmem *S, uint32_t *total) {
   const uint32_t a_bytes = 4u * (rh == 1 ? QK_GEMM_UPG : 2u * rh) * A_HALF;
   int b_stages = (int)((budget - off - a_bytes) / s.b_stage);
   if (b_stages > MAX_RING) b_stages = MAX_RING;
-  if (const char *e = getenv("QK_GEMM_BSTAGES")) {
+  if (const char *e = qk_knob("QK_GEMM_BSTAGES")) {
     const int v = atoi(e);
     if (v >= 2 && v <= b_stages) b_stages = v;
   }
@@ -895,11 +895,10 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   uint32_t total;
   if (!plan_gemm(BN, RH, &S, &total)) return cudaErrorInvalidConfiguration;
   auto kern = qk_gemm_tc_kernel<T, BN, RH>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static QkPerDevice attr_set;
+  if (attr_set.first()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+    if (e != cudaSuccess) return attr_set.reset(), e;
   }
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
@@ -935,7 +934,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   if (n_tiles * 4 < (uint32_t)sm_count * 3) ks = (uint32_t)sm_count / n_tiles;
   if (ks > 8) ks = 8;
   if (ks > nsb) ks = nsb;
-  if (const char *ev = getenv("QK_GEMM_KS")) {
+  if (const char *ev = qk_knob("QK_GEMM_KS")) {
     const uint32_t v = (uint32_t)atoi(ev);
     if (v >= 1 && v <= 8 && v <= nsb) ks = v;
   }
@@ -943,13 +942,12 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   // The row is staged in shared memory between the two passes (measured a little faster
   // than a second read, although a CTA holding shared memory cannot share an SM with a
   // matmul CTA starting under it); QK_X16_STAGE=0 turns the staging off.
-  static const bool stage_rows = !(getenv("QK_X16_STAGE") && atoi(getenv("QK_X16_STAGE")) == 0);
+  static const bool stage_rows = !(qk_knob("QK_X16_STAGE") && atoi(qk_knob("QK_X16_STAGE")) == 0);
   const uint32_t row_bytes = L.cols * 4u, cached = (stage_rows && row_bytes <= 96u * 1024u) ? 1u : 0u;
-  static bool x16_attr = false;
-  if (!x16_attr) {
+  static QkPerDevice x16_attr;
+  if (x16_attr.first()) {
     cudaError_t ea = cudaFuncSetAttribute(qk_x16_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    if (ea != cudaSuccess) return ea;
-    x16_attr = true;
+    if (ea != cudaSuccess) return x16_attr.reset(), ea;
   }
   c0.dynamicSmemBytes = cached ? ((row_bytes + 15u) & ~15u) : 0u;
   cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16, xscale, y, ldy,

@@ -367,6 +367,7 @@ struct Plan {
 
 bool make_plan(const QkLayout &L, uint32_t m, int RS, Plan *P) {
   (void)RS;
+  if (L.nb == 0 || L.chunks == 0) return false;  // nothing to stream: the callers handle empty shapes
   uint32_t Kp = L.nb * L.bs;
   Kp = (Kp + 255u) & ~255u;
   // Activation digits (base 254): three give f32-grade results (~2e-6 of the output's
@@ -375,7 +376,7 @@ bool make_plan(const QkLayout &L, uint32_t m, int RS, Plan *P) {
   // developer knob for M <= 2.
   int D = m <= 2 ? 3 : 2;
   if (m <= 2)
-    if (const char *e = getenv("QK_DIGITS")) D = atoi(e) == 2 ? 2 : atoi(e) == 3 ? 3 : D;
+    if (const char *e = qk_knob("QK_DIGITS")) D = atoi(e) == 2 ? 2 : atoi(e) == 3 ? 3 : D;
   uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
   uint32_t stage_bytes = QK_TILE_ROWS * nbt_max * L.bb;
   stage_bytes = (stage_bytes + 127u) & ~127u;
@@ -415,12 +416,11 @@ template <int TYPE, int M, int D, int RS>
 cudaError_t launch_one(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
                        unsigned *status, int sm_count, const Plan &P, cudaStream_t s) {
   auto kern = qk_gemv_kernel<TYPE, M, D, RS>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static QkPerDevice attr_set;
+  if (attr_set.first()) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+    if (e != cudaSuccess) return attr_set.reset(), e;
   }
   // A persistent grid must be fully resident: size it from the real occupancy.
   static int occ_cached[2] = {0, 0};  // [0] smem it was computed for, [1] CTAs per SM
@@ -442,7 +442,7 @@ cudaError_t launch_one(const QkLayout &L, const uint8_t *W, const float *x, floa
   cfg.attrs = at, cfg.numAttrs = 1;
   static int npre_env = -1;  // developer knob: weight tiles issued before the wait on the previous kernel
   if (npre_env < 0) {
-    const char *e = getenv("QK_PRE");
+    const char *e = qk_knob("QK_PRE");
     npre_env = e ? atoi(e) : 0;
   }
   // Default: the whole ring.  Holding tiles back until the activation loads are out (what

@@ -570,7 +570,7 @@ struct PlanMma {
 int compute_warps(const QkLayout &L, uint32_t m) {
   static int cw_env = -1;
   if (cw_env < 0) {
-    const char *e = getenv("QK_CW");
+    const char *e = qk_knob("QK_CW");
     const int v = e ? atoi(e) : 0;
     cw_env = (v == 8 || v == 12 || v == 16) ? v : 0;
   }
@@ -579,7 +579,10 @@ int compute_warps(const QkLayout &L, uint32_t m) {
   return (L.ktiles == 1 && L.chunks <= 1024) ? 12 : 8;
 }
 
-bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
+// force_cw8: always the 8-warp kernel (the route that takes its split activations from a
+// caller-provided image is built for 8 warps only).
+bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P, bool force_cw8 = false) {
+  if (L.nb == 0 || L.chunks == 0) return false;  // nothing to stream: the callers handle empty shapes
   uint32_t Kp = L.nb * 256u;
   uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
   uint32_t stage_bytes = QK_TILE_ROWS * nbt_max * L.bb;
@@ -602,7 +605,7 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   if (off + 2 * stage_bytes > budget) return false;
   int nstage = (int)((budget - off) / stage_bytes);
   if (nstage > MAX_STAGE) nstage = MAX_STAGE;
-  if (const char *e = getenv("QK_NSTAGE")) {  // developer knob: shallower ring
+  if (const char *e = qk_knob("QK_NSTAGE")) {  // developer knob: shallower ring
     int v = atoi(e);
     if (v >= 2 && v < nstage) nstage = v;
   }
@@ -611,9 +614,9 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P) {
   if ((uint32_t)nstage < L.ktiles + 1) return false;
   // largest group count whose G * ktiles divides a ring depth we can afford
   int groups = 1;
-  const char *ge = getenv("QK_GROUPS");
+  const char *ge = qk_knob("QK_GROUPS");
   const int gmax = ge ? atoi(ge) : 4;
-  int cw = compute_warps(L, m);
+  int cw = force_cw8 ? 8 : compute_warps(L, m);
   if (cw == 12) {  // three groups of four warps, if the ring can hold three chunks
     const int unit = 3 * (int)L.ktiles;
     if (nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1)
@@ -639,16 +642,15 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
                        unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
                        cudaStream_t s, const QkPeers *peers = nullptr) {
   auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW, G>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static QkPerDevice attr_set;
+  if (attr_set.first()) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+    if (e != cudaSuccess) return attr_set.reset(), e;
   }
   static int use_pdl = -1;
   if (use_pdl < 0) {
-    const char *e = getenv("QK_PDL");
+    const char *e = qk_knob("QK_PDL");
     use_pdl = (e && e[0] == '0') ? 0 : 1;
   }
   cudaLaunchAttribute at[1];
@@ -667,7 +669,7 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   }
   static int ctas = -1;  // developer knob: persistent CTAs per SM (they must fit: see QK_CW, QK_NSTAGE)
   if (ctas < 0) {
-    const char *e = getenv("QK_CTAS");
+    const char *e = qk_knob("QK_CTAS");
     ctas = (e && atoi(e) == 2) ? 2 : 1;
   }
   uint32_t grid = (uint32_t)sm_count * (uint32_t)ctas;  // persistent
@@ -683,7 +685,7 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   // (developer knob).
   static int npre_env = -1;
   if (npre_env < 0) {
-    const char *e = getenv("QK_PRE");
+    const char *e = qk_knob("QK_PRE");
     npre_env = e ? atoi(e) : 0;
   }
   int npre = npre_env > 0 ? npre_env : (M == 1 ? (CW == 12 ? 2 : 1) : (M == 2 ? 4 : 3));
@@ -697,7 +699,7 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
 bool split_in_cta(const PlanMma &P, uint32_t m) {
   static int force = -2;
   if (force == -2) {
-    const char *e = getenv("QK_XSPLIT");
+    const char *e = qk_knob("QK_XSPLIT");
     force = e ? atoi(e) : -1;  // 0: always the split kernel, 1: always in-CTA
   }
   if (force >= 0) return force == 1;
@@ -775,7 +777,7 @@ cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, co
                                      float *y, uint32_t m, uint64_t ldy, unsigned *status,
                                      unsigned char *scratch, int sm_count, cudaStream_t s) {
   PlanMma P;
-  if (!make_plan_mma(L, m, &P)) return cudaErrorInvalidConfiguration;
+  if (!make_plan_mma(L, m, &P, true)) return cudaErrorInvalidConfiguration;
 #define QK_SPLIT(MV)                                                                             \
   switch (P.groups) {                                                                            \
     case 4:                                                                                      \

@@ -19,7 +19,11 @@ struct qk_ctx {
   int device;
   int sm_count;
   cudaStream_t stream;
-  unsigned *status_dev;
+  // Status word raised by device code (bounded waits that ran out, range checks): one word of
+  // pinned host memory that the kernels reach through its device mapping, so the host reads
+  // it after a stream synchronise without another copy.
+  unsigned *status_dev;                  // device-side address, passed to kernels
+  volatile unsigned *status_host = nullptr;  // the same word as the host sees it
   // device scratch of the *_dev entry points (split activations); grown on demand,
   // which synchronises: size it once before capturing into a CUDA graph
   unsigned char *scratch = nullptr;

@@ -1,6 +1,38 @@
 // Internal launch interface between the C-ABI layer and the kernel translation units.
 #pragma once
+#include <cstdlib>
+
 #include "qk_layout.cuh"
+
+// Developer knobs (environment variables that change ring depths, warp counts and the like)
+// exist only in builds made with -DQK_DEV_KNOBS; the default build never reads the
+// environment, so nothing outside the caller's arguments changes what a call computes.
+static inline const char *qk_knob(const char *name) {
+#ifdef QK_DEV_KNOBS
+  return getenv(name);
+#else
+  (void)name;
+  return nullptr;
+#endif
+}
+
+// A flag per CUDA device: function attributes (e.g. the dynamic shared-memory limit) and
+// occupancy figures belong to a device, and one process may drive several.
+struct QkPerDevice {
+  bool done[64] = {};
+  // true the first time it is asked on the current device
+  bool first() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return true;
+    if (done[d]) return false;
+    done[d] = true;
+    return true;
+  }
+  void reset() {  // the first-time work failed: try again on the next call
+    int d = 0;
+    if (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 64) done[d] = false;
+  }
+};
 
 // Device status word bits (read back by qk_check_device_status).
 #define QK_DEV_TIMEOUT 1u

@@ -45,7 +45,17 @@ extern "C" int qk_gemm_dev_noalloc(qk_ctx *c, const qk_weights *h, const float *
     return QK_UNSUPPORTED_TYPE;
   }
   if (ldy < h->L.rows) return QK_DIMENSION_MISMATCH;
-  if (m < 1 || m > 4 || !qk_gemv_mma_supported(h->L, (uint32_t)m)) {
+  if (m == 0 || h->L.rows == 0) return QK_OK;  // nothing to write
+  if (h->L.cols == 0) {  // empty dot products: y = 0, as qk_gemm_dev gives (a memset allocates nothing)
+    cudaError_t e = cudaMemset2DAsync(y_dev, ldy * sizeof(float), 0, h->L.rows * sizeof(float), m,
+                                      (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+      c->err = std::string("qk_gemm_dev_noalloc: memset: ") + cudaGetErrorString(e);
+      return QK_CUDA_ERROR;
+    }
+    return QK_OK;
+  }
+  if (m > 4 || !qk_gemv_mma_supported(h->L, (uint32_t)m)) {
     c->err = "qk_gemm_dev_noalloc: needs 1 <= m <= 4 and a shape the Q4_K decode kernel takes";
     return QK_INVALID_ARGUMENT;
   }
@@ -59,9 +69,13 @@ extern "C" int qk_gemm_dev_noalloc(qk_ctx *c, const qk_weights *h, const float *
   {
     std::lock_guard<std::mutex> g(g_mu);
     ptr = g_scratch_ptr[c->device];
-    if (!ptr) {  // set-up, once per device, with that device current
-      cudaError_t e = cudaSetDevice(c->device);
+    if (!ptr) {  // set-up, once per device, with that device current (the caller's own
+                 // current device is put back afterwards)
+      int prev = -1;
+      cudaError_t e = cudaGetDevice(&prev);
+      if (e == cudaSuccess) e = cudaSetDevice(c->device);
       if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&ptr, qk_noalloc_scratch);
+      if (prev >= 0 && prev != c->device) cudaSetDevice(prev);
       if (e != cudaSuccess || !ptr) {
         c->err = std::string("qk_gemm_dev_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e);
         return QK_CUDA_ERROR;
@@ -69,7 +83,6 @@ extern "C" int qk_gemm_dev_noalloc(qk_ctx *c, const qk_weights *h, const float *
       g_scratch_ptr[c->device] = ptr;
     }
   }
-  if (h->L.rows == 0) return QK_OK;
   cudaError_t e = qk_launch_gemv_mma_split(h->L, h->dev, x_dev, y_dev, (uint32_t)m, ldy, c->status_dev,
                                            ptr, c->sm_count, (cudaStream_t)stream);
   if (e != cudaSuccess) {
