@@ -170,38 +170,49 @@ int qk_moe_ffn_dev(qk_ctx *ctx, const qk_weights *const *gate, const qk_weights 
  * crates/oxillama-arch/src/common/linear.rs:77-132) */
 typedef struct qk_gather qk_gather;
 
-/* This rank's [m_cap x world * rows_per_rank] f32 buffer plus its control words.
- * world <= 8.  The ranks then exchange qk_gather_export handles (128 bytes each) over
- * any host channel and qk_gather_import each other's. */
+/* This rank's gathered [m_cap x world * rows_per_rank] f32 result and, behind it, an array
+ * of 8-byte (value, tag) slots of the same shape that every rank stores into.  world <= 8.
+ * The ranks then exchange qk_gather_export handles (128 bytes each) over any host channel
+ * and qk_gather_import each other's (ranks that live in one process: qk_gather_import_local). */
 int qk_gather_create(qk_ctx *ctx, size_t rows_per_rank, size_t m_cap, int world, int rank, qk_gather **out);
 int qk_gather_export(qk_ctx *ctx, qk_gather *g, unsigned char *handle, size_t handle_len);
 int qk_gather_import(qk_ctx *ctx, qk_gather *g, int peer_rank, const unsigned char *handle, size_t handle_len);
+int qk_gather_import_local(qk_ctx *ctx, qk_gather *g, int peer_rank, qk_gather *peer);
 /* Once every rank's handle is imported: touches each peer mapping and waits.  Every rank
  * calls it, then the ranks synchronise on the host, before the first sharded call. */
 int qk_gather_ready(qk_ctx *ctx, qk_gather *g);
+/* Teardown, in two steps: every rank calls qk_gather_close_peers (waits for this GPU's
+ * work, closes what it imported), the ranks synchronise on the host, then every rank
+ * calls qk_gather_destroy.  Freeing memory that a peer still has open is undefined. */
+int qk_gather_close_peers(qk_ctx *ctx, qk_gather *g);
 int qk_gather_destroy(qk_ctx *ctx, qk_gather *g);
-/* Device pointer of the local buffer: y_full[i * world * rows_per_rank + r * rows_per_rank + j]. */
+/* Device pointer of the plain result: y_full[i * world * rows_per_rank + r * rows_per_rank + j],
+ * valid once a qk_gather_wait_dev enqueued after the call has run. */
 float *qk_gather_buffer(qk_gather *g);
 
 /* qk_gemm_dev of this rank's shard (rows == rows_per_rank), with the [m x rows] result
- * stored into every rank's buffer and the call's epoch published to every rank.  For
- * Q4_K and m <= 4 the matvec kernel itself does the peer stores; otherwise a push kernel
- * follows the ordinary one.  Every rank must make the same sequence of calls on a given
- * qk_gather, and must not start call k + 1 on it before its own qk_gather_wait_dev of
- * call k has been enqueued.  A faster rank's call k + 1 overwrites the buffer of a slower
- * rank that may still be reading call k: alternate two qk_gather objects, each call
- * waiting for the previous one (then no rank is ever more than one call ahead), or
- * synchronise the ranks on the host before reusing a buffer. */
+ * stored into the slots of every rank, tagged with the call's ordinal on this qk_gather.
+ * Where the decode kernel supports it (Q4_K, m <= 4) the kernel itself does the peer
+ * stores; otherwise a push kernel follows the ordinary one.  Every rank must make the same
+ * sequence of calls on a given qk_gather.  A call overwrites the slots of the previous
+ * call on the same object in every rank, so a rank may start call k + 1 on an object only
+ * when every rank has finished reading call k from it.  Two objects used alternately, each
+ * call waiting (qk_gather_wait_dev, or `after` below) for the previous call before it
+ * starts, satisfy this: a rank that has seen every block of call k knows that all ranks
+ * have finished reading call k - 1.  Ranks that let a call run ahead of the wait for the
+ * previous one (waiting one call later) need four objects in rotation. */
 int qk_gemm_gather_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g, void *stream);
-/* The same, for activations that are themselves gathered: x_dev (usually inside
- * qk_gather_buffer(after)) is read only once every rank's block of the latest call on
- * `after` has arrived.  Where the matvec kernel does the peer stores it also does this
- * wait, under its own prologue; otherwise qk_gather_wait_dev(after) is enqueued first.
- * after == NULL: no wait. */
+/* The same, for activations that are themselves gathered: x_dev points into
+ * qk_gather_buffer(after) (activation rows one buffer row apart) and stands for the result
+ * of the latest call on `after`.  Where the matvec kernel does the peer stores it also reads
+ * x straight from `after`'s slots, each read waiting until the slot carries that call's tag
+ * (no unpacking pass, no kernel boundary between the arrival of the data and its use);
+ * otherwise qk_gather_wait_dev(after) is enqueued first.  after == NULL: plain x_dev. */
 int qk_gemm_gather_after_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
                              qk_gather *after, void *stream);
-/* Enqueues a wait until every rank's block of the latest call has arrived (at most
- * 0.25 s, then QK_TIMEOUT through qk_check_device_status). */
+/* Enqueues the unpacking of the latest call into the plain buffer: every slot is waited
+ * for (at most 0.25 s per thread, then QK_TIMEOUT through qk_check_device_status and
+ * zeros in the places that did not arrive). */
 int qk_gather_wait_dev(qk_ctx *ctx, qk_gather *g, void *stream);
 
 /* No counterpart in the reference.  qk_gemm_dev for Q4_K shards and m <= 4 that
@@ -210,7 +221,8 @@ int qk_gather_wait_dev(qk_ctx *ctx, qk_gather *g, void *stream);
  * memory budget, a loop that must not take the allocator lock).  Its scratch is
  * a 96 KiB array built into the library (held on every GPU that loads it), so
  * the split activations of a call (about 3.1 bytes per activation) must fit
- * 96 KiB, else QK_INVALID_ARGUMENT.
+ * 96 KiB, else QK_INVALID_ARGUMENT.  Like every *_dev entry point it launches on the
+ * calling thread's current device, which must be the context's.
  * The first call on a device resolves the array's address: make it before any
  * stream capture.  Calls on one device share the array; overlapping calls race. */
 int qk_gemm_dev_noalloc(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_dev,

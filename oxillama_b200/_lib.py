@@ -43,7 +43,9 @@ SIGNATURES = {
     "qk_gather_create": (C.c_int, [vp, sz, sz, C.c_int, C.c_int, vp]),
     "qk_gather_export": (C.c_int, [vp, vp, vp, sz]),
     "qk_gather_import": (C.c_int, [vp, vp, C.c_int, vp, sz]),
+    "qk_gather_import_local": (C.c_int, [vp, vp, C.c_int, vp]),
     "qk_gather_ready": (C.c_int, [vp, vp]),
+    "qk_gather_close_peers": (C.c_int, [vp, vp]),
     "qk_gather_destroy": (C.c_int, [vp, vp]),
     "qk_gather_buffer": (vp, [vp]),
     "qk_gemm_gather_dev": (C.c_int, [vp, vp, vp, sz, vp, vp]),

@@ -1,85 +1,87 @@
-// Row-sharded outputs gathered over NVLink without a collective library: every rank of a
-// node owns a [m_cap x world * rows] f32 buffer; a sharded matvec stores its column
-// block into the buffer of every rank (peer stores, from inside the matvec kernel where
-// that kernel supports it, else from a small push kernel) and publishes an epoch flag
-// in every rank; a consumer waits (bounded) until all ranks' flags have reached its own
-// epoch.  Buffers and flags are plain cudaMalloc memory shared through CUDA IPC handles,
+// Row-sharded outputs gathered over NVLink without a collective library.
+//
+// Every rank of a node owns, per gather object, an array of 8-byte slots, one per element
+// of the gathered [m_cap x world * rows] result: (f32 value, tag), the tag being the
+// ordinal of the sharded call that produced the value.  A sharded matvec stores each of
+// its results, as one 64-bit word, into the slot of every rank (peer stores issued from
+// inside the matvec kernel where that kernel supports it, else from a small push kernel
+// behind the ordinary one).  A consumer polls a slot until it carries the tag of the call
+// it wants (bounded: a quarter of a second, then QK_TIMEOUT): either the next matvec
+// kernel itself, which reads its activations straight out of the slots, or
+// qk_gather_wait_dev, which unpacks them into a plain f32 buffer.  Because value and tag
+// travel in one single-copy-atomic store there is no flag behind the data, hence no fence
+// that waits for a peer's acknowledgement and no last-CTA publish on the producer's
+// critical path.  Slot arrays are plain cudaMalloc memory shared through CUDA IPC handles,
 // which the ranks exchange by whatever host channel they have.
 //
-// Replaces, for a sharded layer, the NCCL all-gather that follows the matvec in the
-// reference-shaped design (one all-gather of y per linear).  No multicast loads, no
-// waits without a time limit.
+// Replaces, for a sharded layer, the all-gather that follows the matvec in the
+// reference-shaped design (one all-gather of y per linear,
+// crates/oxillama-arch/src/common/linear.rs:77-98).  No multicast loads, no waits without
+// a time limit.
 #include <cstring>
 
 #include "qk_internal.h"
+#include "qk_peer.cuh"
 #include "qk_pipe.cuh"
 
 struct qk_gather {
   int world, rank, device;
   size_t rows, m_cap;          // rows per rank, most activation rows a call may carry
-  float *local;                // [m_cap][world * rows]
-  unsigned *ctl;               // flags[world], counter, epoch
-  float *peer_y[QK_MAX_PEERS];
-  unsigned *peer_ctl[QK_MAX_PEERS];
-  bool opened[QK_MAX_PEERS];
+  size_t last_m;               // activation rows of the latest call
+  float *local;                // [m_cap][world * rows] plain result, filled by qk_gather_wait_dev
+  unsigned long long *slots;   // [m_cap][world * rows] tagged slots, written by every rank
+  unsigned *ctl;               // [0] CTAs finished in the running launch, [1] calls completed (last tag)
+  unsigned long long *peer_slots[QK_MAX_PEERS];
+  bool opened[QK_MAX_PEERS];   // peer_slots[r] came from cudaIpcOpenMemHandle
 };
 
 namespace {
 
-// Copies this rank's column block of the local buffer into every other rank's buffer,
-// then the last CTA publishes the epoch (same protocol as the fused matvec).
+using namespace qkpeer;
+
+// Stores this rank's column block (already computed into the plain buffer) into the slots
+// of every rank, tagged with this call's ordinal; the last CTA records the call.
 __global__ void __launch_bounds__(256)
     qk_gather_push_kernel(QkPeers peers, const float *__restrict__ src, uint32_t m, uint32_t rows,
                           uint64_t ldy) {
+  const unsigned tag = *reinterpret_cast<const volatile unsigned *>(peers.epoch) + 1u;
   const uint64_t n = (uint64_t)m * rows;
   for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += (uint64_t)gridDim.x * 256) {
     const uint64_t off = (i / rows) * ldy + (i % rows);
     const float v = src[off];
-    for (uint32_t p = 0; p < peers.n; p++)
-      if (p != peers.rank) peers.y[p][off] = v;
+    for (uint32_t p = 0; p < peers.n; p++) slot_store(peers.slots[p] + off, v, tag);
   }
-  __threadfence();  // every thread orders its own peer stores before the count below (read on this GPU)
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
-      __threadfence();
-      *peers.counter = 0;
-      const unsigned e = *peers.epoch + 1;
-      *peers.epoch = e;
-      __threadfence_system();
-      for (uint32_t p = 0; p < peers.n; p++)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(e) : "memory");
-    }
+  __syncthreads();  // every thread has read the call count
+  if (threadIdx.x == 0 && atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
+    *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
+    *reinterpret_cast<volatile unsigned *>(peers.epoch) = tag;
   }
 }
 
-// One thread per rank: waits until that rank's flag has reached the local epoch, for at
-// most a quarter of a second.
-__global__ void __launch_bounds__(32)
-    qk_gather_wait_kernel(const unsigned *flags, const unsigned *epoch, uint32_t n, unsigned *status) {
-  if (threadIdx.x >= n) return;
+// Unpacks the latest call: every slot of the [m x ld] result is polled until it carries
+// the call's tag (each thread gives up after a quarter of a second) and its value goes
+// into the plain buffer.
+__global__ void __launch_bounds__(256)
+    qk_gather_unpack_kernel(const unsigned long long *slots, const unsigned *epoch, float *__restrict__ out,
+                            uint64_t n, unsigned *status) {
   const unsigned want = *epoch;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
-    if ((int)(v - want) >= 0) return;
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (t - t0 > 250000000ull) {
+  bool arrived = true;
+  for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += (uint64_t)gridDim.x * 256) {
+    float v = 0.f;
+    if (arrived && !slot_wait(slots + i, want, v)) {
+      arrived = false;
       atomicOr(status, QK_DEV_TIMEOUT);
-      return;
     }
+    out[i] = v;
   }
 }
 
-// First touch of every peer mapping from this GPU (one zero into this rank's block of
-// each peer's freshly cleared buffer), so that the first real call meets established
-// translations.
+// First touch of every peer mapping from this GPU (slot 0 of this rank's block in each
+// peer's freshly cleared array is written with its initial contents, value 0 and tag 0), so
+// that the first real call meets established translations.
 __global__ void qk_gather_touch_kernel(QkPeers peers) {
   if (threadIdx.x < peers.n) {
-    peers.y[threadIdx.x][0] = 0.f;
+    slot_store(peers.slots[threadIdx.x], 0.f, 0u);
     __threadfence_system();
   }
 }
@@ -92,13 +94,12 @@ int fail(qk_ctx *c, cudaError_t e, const char *what) {
 QkPeers peers_of(const qk_gather *g) {
   QkPeers p = {};
   p.n = (uint32_t)g->world, p.rank = (uint32_t)g->rank;
-  for (int r = 0; r < g->world; r++) {
-    p.y[r] = g->peer_y[r] + (size_t)g->rank * g->rows;
-    p.flags[r] = g->peer_ctl[r];
-  }
-  p.counter = g->ctl + QK_MAX_PEERS, p.epoch = g->ctl + QK_MAX_PEERS + 1;
+  for (int r = 0; r < g->world; r++) p.slots[r] = g->peer_slots[r] + (size_t)g->rank * g->rows;
+  p.counter = g->ctl, p.epoch = g->ctl + 1;
   return p;
 }
+
+size_t elems(const qk_gather *g) { return g->m_cap * (size_t)g->world * g->rows; }
 
 }  // namespace
 
@@ -111,49 +112,69 @@ extern "C" int qk_gather_create(qk_ctx *c, size_t rows_per_rank, size_t m_cap, i
   cudaSetDevice(c->device);
   qk_gather *g = new qk_gather();
   g->world = world, g->rank = rank, g->device = c->device, g->rows = rows_per_rank, g->m_cap = m_cap;
-  cudaError_t e = cudaMalloc(&g->local, m_cap * world * rows_per_rank * sizeof(float));
-  if (e == cudaSuccess) e = cudaMalloc(&g->ctl, (QK_MAX_PEERS + 2) * sizeof(unsigned));
-  if (e == cudaSuccess) e = cudaMemset(g->ctl, 0, (QK_MAX_PEERS + 2) * sizeof(unsigned));
-  if (e == cudaSuccess) e = cudaMemset(g->local, 0, m_cap * world * rows_per_rank * sizeof(float));
+  g->last_m = m_cap;
+  const size_t n = elems(g);
+  cudaError_t e = cudaMalloc(&g->local, n * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(&g->slots, n * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMalloc(&g->ctl, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(g->ctl, 0, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(g->local, 0, n * sizeof(float));
+  if (e == cudaSuccess) e = cudaMemset(g->slots, 0, n * sizeof(unsigned long long));  // tag 0: nothing arrived
   if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the clears must have run before a peer can store here
   if (e != cudaSuccess) {
     if (g->local) cudaFree(g->local);
+    if (g->slots) cudaFree(g->slots);
     if (g->ctl) cudaFree(g->ctl);
     delete g;
     return fail(c, e, "qk_gather_create");
   }
-  g->peer_y[rank] = g->local, g->peer_ctl[rank] = g->ctl, g->opened[rank] = false;
+  g->peer_slots[rank] = g->slots;
   *out = g;
   return QK_OK;
 }
 
-// handle: 128 bytes = the IPC handles of the buffer and of the control words.
+// handle: 128 bytes; the first 64 are the IPC handle of the slot array, the rest is reserved.
 extern "C" int qk_gather_export(qk_ctx *c, qk_gather *g, unsigned char *handle, size_t len) {
   if (!c || !g || !handle || len < 128) return QK_INVALID_ARGUMENT;
   cudaSetDevice(c->device);
-  cudaIpcMemHandle_t h0, h1;
-  cudaError_t e = cudaIpcGetMemHandle(&h0, g->local);
-  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h1, g->ctl);
+  cudaIpcMemHandle_t h0;
+  cudaError_t e = cudaIpcGetMemHandle(&h0, g->slots);
   if (e != cudaSuccess) return fail(c, e, "qk_gather_export");
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
-  memcpy(handle, &h0, 64), memcpy(handle + 64, &h1, 64);
+  memset(handle, 0, 128);
+  memcpy(handle, &h0, 64);
   return QK_OK;
 }
 
 extern "C" int qk_gather_import(qk_ctx *c, qk_gather *g, int peer_rank, const unsigned char *handle, size_t len) {
-  if (!c || !g || !handle || len < 128 || peer_rank < 0 || peer_rank >= g->world || peer_rank == g->rank)
+  if (!c || !g || !handle || len < 128 || peer_rank < 0 || peer_rank >= g->world || peer_rank == g->rank ||
+      g->peer_slots[peer_rank])
     return QK_INVALID_ARGUMENT;
   cudaSetDevice(c->device);
-  cudaIpcMemHandle_t h0, h1;
-  memcpy(&h0, handle, 64), memcpy(&h1, handle + 64, 64);
-  void *p0 = nullptr, *p1 = nullptr;
+  cudaIpcMemHandle_t h0;
+  memcpy(&h0, handle, 64);
+  void *p0 = nullptr;
   cudaError_t e = cudaIpcOpenMemHandle(&p0, h0, cudaIpcMemLazyEnablePeerAccess);
-  if (e == cudaSuccess) e = cudaIpcOpenMemHandle(&p1, h1, cudaIpcMemLazyEnablePeerAccess);
-  if (e != cudaSuccess) {
-    if (p0) cudaIpcCloseMemHandle(p0);
-    return fail(c, e, "qk_gather_import");
+  if (e != cudaSuccess) return fail(c, e, "qk_gather_import");
+  g->peer_slots[peer_rank] = (unsigned long long *)p0, g->opened[peer_rank] = true;
+  return QK_OK;
+}
+
+// The same wiring for a peer that lives in this process (several contexts driven by one
+// host thread, or several "ranks" on one GPU in a test): no IPC handle, the peer's slot
+// array is used directly.  With the peer on another GPU, access to it is enabled first.
+extern "C" int qk_gather_import_local(qk_ctx *c, qk_gather *g, int peer_rank, qk_gather *peer) {
+  if (!c || !g || !peer || peer_rank < 0 || peer_rank >= g->world || peer_rank == g->rank ||
+      g->peer_slots[peer_rank] || peer->world != g->world || peer->rank != peer_rank || peer->rows != g->rows ||
+      peer->m_cap != g->m_cap)
+    return QK_INVALID_ARGUMENT;
+  if (peer->device != g->device) {
+    cudaSetDevice(c->device);
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer->device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError(), e = cudaSuccess;
+    if (e != cudaSuccess) return fail(c, e, "qk_gather_import_local");
   }
-  g->peer_y[peer_rank] = (float *)p0, g->peer_ctl[peer_rank] = (unsigned *)p1, g->opened[peer_rank] = true;
+  g->peer_slots[peer_rank] = peer->slots, g->opened[peer_rank] = false;
   return QK_OK;
 }
 
@@ -162,7 +183,7 @@ extern "C" int qk_gather_import(qk_ctx *c, qk_gather *g, int peer_rank, const un
 extern "C" int qk_gather_ready(qk_ctx *c, qk_gather *g) {
   if (!c || !g) return QK_INVALID_ARGUMENT;
   for (int r = 0; r < g->world; r++)
-    if (!g->peer_y[r]) return QK_INVALID_ARGUMENT;
+    if (!g->peer_slots[r]) return QK_INVALID_ARGUMENT;
   cudaSetDevice(c->device);
   qk_gather_touch_kernel<<<1, 32>>>(peers_of(g));
   cudaError_t e = cudaGetLastError();
@@ -170,20 +191,43 @@ extern "C" int qk_gather_ready(qk_ctx *c, qk_gather *g) {
   return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gather_ready");
 }
 
-extern "C" int qk_gather_destroy(qk_ctx *c, qk_gather *g) {
+// Teardown is two steps with a host synchronisation of the ranks between them: freeing
+// memory that another process still has open through an IPC handle is undefined, so
+// every rank first closes what it imported, and only when all have done so does anyone
+// free its own arrays.
+extern "C" int qk_gather_close_peers(qk_ctx *c, qk_gather *g) {
   if (!c || !g) return QK_INVALID_ARGUMENT;
   cudaSetDevice(c->device);
-  cudaDeviceSynchronize();
-  for (int r = 0; r < g->world; r++)
-    if (g->opened[r]) cudaIpcCloseMemHandle(g->peer_y[r]), cudaIpcCloseMemHandle(g->peer_ctl[r]);
-  cudaFree(g->local), cudaFree(g->ctl);
+  cudaDeviceSynchronize();  // none of this rank's kernels may still be storing into a peer
+  for (int r = 0; r < g->world; r++) {
+    if (r == g->rank) continue;
+    if (g->opened[r]) cudaIpcCloseMemHandle(g->peer_slots[r]);
+    g->peer_slots[r] = nullptr, g->opened[r] = false;
+  }
+  return QK_OK;
+}
+
+extern "C" int qk_gather_destroy(qk_ctx *c, qk_gather *g) {
+  if (!c || !g) return QK_INVALID_ARGUMENT;
+  qk_gather_close_peers(c, g);
+  cudaFree(g->local), cudaFree(g->slots), cudaFree(g->ctl);
   delete g;
   return QK_OK;
 }
 
 extern "C" float *qk_gather_buffer(qk_gather *g) { return g ? g->local : nullptr; }
 
-extern "C" int qk_gather_wait_dev(qk_ctx *c, qk_gather *g, void *stream);
+extern "C" int qk_gather_wait_dev(qk_ctx *c, qk_gather *g, void *stream) {
+  if (!c || !g) return QK_INVALID_ARGUMENT;
+  // rows of the result are ld apart and the call filled m of them: one contiguous run
+  const uint64_t n = (uint64_t)g->last_m * g->world * g->rows;
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  const unsigned cap = (unsigned)c->sm_count * 2u;
+  if (blocks > cap) blocks = cap;
+  qk_gather_unpack_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g->slots, g->ctl + 1, g->local, n, c->status_dev);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gather_wait_dev");
+}
 
 extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
                                         qk_gather *after, void *stream) {
@@ -192,7 +236,7 @@ extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const fl
   if (h->device != c->device || g->device != c->device) return QK_INVALID_ARGUMENT;
   if (h->L.rows != g->rows || m == 0 || m > g->m_cap) return QK_DIMENSION_MISMATCH;
   for (int r = 0; r < g->world; r++)
-    if (!g->peer_y[r]) {
+    if (!g->peer_slots[r]) {
       c->err = "qk_gemm_gather_dev: a rank's buffer has not been imported";
       return QK_INVALID_ARGUMENT;
     }
@@ -200,20 +244,31 @@ extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const fl
   const uint64_t ldy = (uint64_t)g->world * g->rows;
   QkPeers peers = peers_of(g);
   float *mine = g->local + (size_t)g->rank * g->rows;
-  const bool fused = !c->force_simple && m <= QK_GEMV_MAX_M && h->L.type == QK_T_Q4_K &&
-                     qk_gemv_mma_supported(h->L, (uint32_t)m);
+  const bool fused = !c->force_simple && m <= QK_GEMV_MAX_M && h->L.cols > 0 &&
+                     qk_gemv_peer_supported(h->L, (uint32_t)m);
   if (after) {
-    if (fused) {  // the matvec kernels wait themselves, under their own prologue
-      peers.wait_flags = after->ctl, peers.wait_epoch = after->ctl + QK_MAX_PEERS + 1;
-      peers.wait_n = (uint32_t)after->world;
+    // Activations that are the gathered output of the latest call on `after`.  Where the
+    // matvec kernel can, it reads them straight from `after`'s slots (x_dev must then lie
+    // inside after's buffer, rows one buffer row apart); otherwise `after` is unpacked
+    // first and the kernels read the plain buffer.
+    const uint64_t ld_a = (uint64_t)after->world * after->rows, n_a = after->m_cap * ld_a;
+    const ptrdiff_t off = x_dev - after->local;
+    const bool inside = x_dev >= after->local && (uint64_t)off + (m - 1) * ld_a + h->L.cols <= n_a;
+    const bool rows_ok = m == 1 || h->L.cols == ld_a;  // the plain kernels take rows `cols` apart
+    if (inside && !rows_ok) {
+      c->err = "qk_gemm_gather_after_dev: several activation rows inside a gathered buffer need cols == world * rows";
+      return QK_DIMENSION_MISMATCH;
+    }
+    if (fused && inside && (off & 1) == 0 && (ld_a & 1) == 0) {
+      peers.wait_slots = after->slots + off, peers.wait_epoch = after->ctl + 1, peers.wait_ld = ld_a;
     } else {
       int st = qk_gather_wait_dev(c, after, stream);
       if (st) return st;
     }
   }
-  if (!c->force_simple && m <= QK_GEMV_MAX_M && h->L.type == QK_T_Q4_K && qk_gemv_mma_supported(h->L, (uint32_t)m)) {
-    // fused: the matvec kernel itself stores into every rank and signals
-    const size_t need = qk_gemv_mma_scratch_bytes(h->L, (uint32_t)m);
+  g->last_m = m;
+  if (fused) {  // the matvec kernel itself stores into every rank
+    const size_t need = qk_gemv_peer_scratch_bytes(h->L, (uint32_t)m);
     if (need > c->scratch_cap) {
       cudaError_t e = cudaDeviceSynchronize();
       if (e != cudaSuccess) return fail(c, e, "qk_gemm_gather_dev");
@@ -223,17 +278,18 @@ extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const fl
       if (e != cudaSuccess) return fail(c, e, "qk_gemm_gather_dev");
       c->scratch_cap = need * 2;
     }
-    cudaError_t e = qk_launch_gemv_mma(h->L, h->dev, x_dev, mine, (uint32_t)m, ldy, c->status_dev, c->scratch,
-                                       c->sm_count, s, &peers);
+    cudaError_t e = qk_launch_gemv_peer(h->L, h->dev, x_dev, (uint32_t)m, ldy, c->status_dev, c->scratch,
+                                        c->sm_count, s, &peers);
     return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gemm_gather_dev");
   }
-  // any other shape or format: the ordinary kernels write this rank's block of the local
-  // buffer, then a push kernel copies it to the other ranks and signals
+  // any other shape or format (an empty K included: zeros): the ordinary kernels write this
+  // rank's block of the local plain buffer, then a push kernel stores it into every rank's slots
   int st = qk_gemm_dev(c, h, x_dev, mine, m, ldy, stream);
   if (st) return st;
   const uint64_t n = (uint64_t)m * g->rows;
   unsigned blocks = (unsigned)((n + 255) / 256);
-  if (blocks > 296) blocks = 296;
+  const unsigned cap = (unsigned)c->sm_count * 2u;
+  if (blocks > cap) blocks = cap;
   qk_gather_push_kernel<<<blocks, 256, 0, s>>>(peers, mine, (uint32_t)m, (uint32_t)g->rows, ldy);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gemm_gather_dev");
@@ -242,12 +298,4 @@ extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const fl
 extern "C" int qk_gemm_gather_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
                                   void *stream) {
   return qk_gemm_gather_after_dev(c, h, x_dev, m, g, nullptr, stream);
-}
-
-extern "C" int qk_gather_wait_dev(qk_ctx *c, qk_gather *g, void *stream) {
-  if (!c || !g) return QK_INVALID_ARGUMENT;
-  qk_gather_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(g->ctl, g->ctl + QK_MAX_PEERS + 1, (uint32_t)g->world,
-                                                           c->status_dev);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gather_wait_dev");
 }

@@ -521,3 +521,17 @@ cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const f
       return cudaErrorInvalidValue;
   }
 }
+
+// ---- decode kernels with the output fan-out built in
+bool qk_gemv_peer_supported(const QkLayout &L, uint32_t m) {
+  return L.type == QK_T_Q4_K && qk_gemv_mma_supported(L, m);
+}
+
+size_t qk_gemv_peer_scratch_bytes(const QkLayout &L, uint32_t m) { return qk_gemv_mma_scratch_bytes(L, m); }
+
+cudaError_t qk_launch_gemv_peer(const QkLayout &L, const uint8_t *tiled, const float *x, uint32_t m,
+                                uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
+                                cudaStream_t s, const QkPeers *peers) {
+  if (L.type != QK_T_Q4_K) return cudaErrorNotSupported;
+  return qk_launch_gemv_mma(L, tiled, x, nullptr, m, ldy, status, scratch, sm_count, s, peers);
+}

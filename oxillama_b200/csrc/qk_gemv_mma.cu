@@ -50,6 +50,7 @@
 
 #include "qk_formats.cuh"
 #include "qk_kernels.h"
+#include "qk_peer.cuh"
 #include "qk_pipe.cuh"
 #include <type_traits>
 
@@ -158,26 +159,40 @@ __device__ __forceinline__ void split_quad(const float (&v)[4], float inv, uint3
   w2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
 }
 
+// Activations e0 .. e0 + 3 of one row out of the tagged slots of a gathered buffer (columns
+// past `cols` read as zero); false if a slot's tag did not arrive within the wait's bound.
+__device__ __forceinline__ bool load_quad_slots(const unsigned long long *row, unsigned want, uint32_t e0,
+                                                uint32_t cols, float (&v)[4]) {
+  if (e0 + 4 <= cols) return qkpeer::slot_wait4(row + e0, want, v);
+  bool ok = true;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    v[i] = 0.f;
+    if (e0 + i < cols) ok &= qkpeer::slot_wait(row + e0 + i, want, v[i]);
+  }
+  return ok;
+}
+
 // ---------------------------------------------------------------- x image
 // [M][3 digit planes of PS bytes, natural column order][M][Kp/32] float2 (sx, Sx)
 __global__ void __launch_bounds__(256)
     qk_xsplit_kernel(const float *__restrict__ x, uint32_t m_rows, uint32_t cols, uint32_t Kp,
                      uint32_t PS, uint32_t xs_off, unsigned char *__restrict__ img,
-                     const unsigned *wait_flags, const unsigned *wait_epoch, uint32_t wait_n,
+                     const unsigned long long *wait_slots, const unsigned *wait_epoch, uint64_t wait_ld,
                      unsigned *status) {
   pdl_launch_dependents();
   pdl_wait();  // x may be the previous kernel's output; the image may still be in use by it
-  if (wait_n) {  // x is gathered from other GPUs: their blocks must have arrived
-    if (!flags_wait_bounded(wait_flags, wait_epoch, wait_n, threadIdx.x)) atomicOr(status, QK_DEV_TIMEOUT);
-    __syncthreads();
-  }
   const uint32_t quads = Kp / 4, total = m_rows * quads;
   const uint32_t it = blockIdx.x * 256 + threadIdx.x;
   if (it >= total) return;  // warp-uniform: total is a multiple of 64
   const uint32_t m = it / quads, e0 = (it % quads) * 4;
   float v[4];
+  if (wait_slots) {  // x is gathered from other GPUs: read it from the tagged slots as it arrives
+    if (!load_quad_slots(wait_slots + (uint64_t)m * wait_ld, *wait_epoch, e0, cols, v)) atomicOr(status, QK_DEV_TIMEOUT);
+  } else {
 #pragma unroll
-  for (int i = 0; i < 4; i++) v[i] = (e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
+    for (int i = 0; i < 4; i++) v[i] = (e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
+  }
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
   float s4 = (v[0] + v[1]) + (v[2] + v[3]);
 #pragma unroll
@@ -202,9 +217,10 @@ __global__ void __launch_bounds__(256)
 // The same split as qk_xsplit_kernel, done by the compute warps straight into the
 // CTA's shared-memory x image (used when x is small enough that every CTA
 // redoing it is cheaper than a second kernel and a copy).
-template <int M, int CW>
+template <int M, int CW, bool PEER>
 __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32_t Kp,
-                              unsigned char *img, uint32_t PS, uint32_t xs_off, bool tell_producer) {
+                              unsigned char *img, uint32_t PS, uint32_t xs_off, bool tell_producer,
+                              const QkPeers &peers, unsigned *status) {
   constexpr int CT = CW * 32;  // compute threads
   const uint32_t quads = Kp / 4, total = (uint32_t)M * quads;
   // Every CTA of the grid reads the same few KB of x at the same moment: each starts at
@@ -212,6 +228,9 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
   // to spread the requests over the L2 slices, and loads 16 bytes at a time when it can.
   const uint32_t rot = (blockIdx.x * 40u) % total;  // a multiple of 8 quads
   const bool vec = (cols & 3u) == 0 && ((uintptr_t)x & 15u) == 0;
+  const bool from_slots = PEER && peers.wait_slots != nullptr;
+  const unsigned want = from_slots ? *peers.wait_epoch : 0u;
+  bool arrived = true;  // false once a slot has failed to arrive in time: this thread waits no more
   constexpr int U = (M * 4096 / 4 + CT - 1) / CT < 4 ? (M * 4096 / 4 + CT - 1) / CT : 4;  // quads in flight per thread
   for (uint32_t base = 0; base < total; base += CT * U) {
     float v[U][4];
@@ -223,7 +242,14 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
       if (it >= total) it -= total;
       qidx[j] = it0 < total ? it : 0xFFFFFFFFu;
       const uint32_t m = M == 1 ? 0u : it / quads, e0 = (M == 1 ? it : it % quads) * 4;
-      if (it0 < total && vec && e0 + 4 <= cols) {
+      if (from_slots) {  // gathered activations: straight from the tagged slots, as they arrive
+        v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
+        if (it0 < total && arrived &&
+            !load_quad_slots(peers.wait_slots + (uint64_t)m * peers.wait_ld, want, e0, cols, v[j])) {
+          arrived = false;
+          atomicOr(status, QK_DEV_TIMEOUT);
+        }
+      } else if (it0 < total && vec && e0 + 4 <= cols) {
         const float4 q = __ldg(reinterpret_cast<const float4 *>(x + (uint64_t)m * cols + e0));
         v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
       } else {
@@ -274,7 +300,10 @@ struct SbData {
   uint2 b[M][4];
 };
 
-template <int M, bool INCTA, int CW, int G>
+// PEER: the variant that can store its results into every rank's tagged slots and read
+// gathered activations out of slots (kept out of the single-GPU variant, whose speed is
+// sensitive to its code size).
+template <int M, bool INCTA, int CW, int G, bool PEER>
 __global__ void __launch_bounds__((CW + 1) * 32, 1)
     qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
@@ -324,6 +353,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     }
     pdl_wait();  // the x image and y belong to the previous kernel until it has finished
     QK_STAMP(true, 120);
+    // sharded output: this call's tag (the buffer's call count was left by the previous kernel on it)
+    const unsigned tag = (PEER && peers.n) ? *reinterpret_cast<const volatile unsigned *>(peers.epoch) + 1u : 0u;
     if (!INCTA && lane == 0) {
       mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
       bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
@@ -343,18 +374,24 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         break;
       }
       const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (WG * M * 8);
+      float v = 0.f;
       if (lane < 8 * M) {
         const uint32_t m = lane >> 3, r = lane & 7u;
-        float v = 0.f;
 #pragma unroll
         for (int wv = 0; wv < WG; wv++) v += red[(wv * M + m) * 8 + r];
         const uint32_t row = (blockIdx.x + c * gridDim.x) * 8 + r;
-        if (row < L.rows) {
-          if (peers.n == 0) {
-            y[(uint64_t)m * ldy + row] = v;
-          } else {  // the same value into every rank's gathered buffer
-            for (uint32_t p = 0; p < peers.n; p++) peers.y[p][(uint64_t)m * ldy + row] = v;
-          }
+        if (!(PEER && peers.n) && row < L.rows) y[(uint64_t)m * ldy + row] = v;
+      }
+      if (PEER && peers.n) {
+        // The same (value, tag) word into the slot of every rank: lane (q, r) stores row r
+        // to ranks q, q + 4 (eight consecutive slots = 64 bytes per rank and activation row).
+        const uint32_t r = lane & 7u, row = (blockIdx.x + c * gridDim.x) * 8 + r;
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+          const float vm = __shfl_sync(0xffffffffu, v, m * 8 + (int)r);
+          if (row < L.rows)
+            for (uint32_t p = lane >> 3; p < peers.n; p += 4)
+              qkpeer::slot_store(peers.slots[p] + (uint64_t)m * ldy + row, vm, tag);
         }
       }
       __syncwarp();
@@ -365,23 +402,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       if (lane == 0)
         for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
     }
-    if (peers.n) {  // this CTA's rows are out; the last CTA of the launch publishes the epoch
-      // Every lane orders its own peer stores before the count below (GPU scope: the count
-      // is read on this GPU); the one system-scope fence of the launch is the last CTA's,
-      // which has then observed every other CTA's count.  A system fence per CTA costs
-      // about 8 us per launch on B200.
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) {
-        if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
-          __threadfence();
-          *peers.counter = 0;
-          const unsigned e = *peers.epoch + 1;
-          *peers.epoch = e;
-          __threadfence_system();
-          for (uint32_t p = 0; p < peers.n; p++)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + peers.rank), "r"(e) : "memory");
-        }
+    if (PEER && peers.n && lane == 0) {
+      // The last CTA to finish records that the buffer has seen one more call.  The count
+      // only orders this bookkeeping: the data needs no fence (see QkPeers).
+      if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
+        *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
+        *reinterpret_cast<volatile unsigned *>(peers.epoch) = tag;
       }
     }
     return;
@@ -405,13 +431,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   pdl_wait();  // x may be the previous kernel's output; y may be read or written by it
   QK_STAMP(warp == 0, 121);
   bool dead = false;
-  if (INCTA && peers.wait_n) {  // x is gathered from other GPUs: their blocks must have arrived
-    if (!flags_wait_bounded(peers.wait_flags, peers.wait_epoch, peers.wait_n, threadIdx.x))
-      atomicOr(status, QK_DEV_TIMEOUT);
-    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
-  }
   if (INCTA) {
-    xsplit_in_cta<M, CW>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off, npre < nstage);
+    xsplit_in_cta<M, CW, PEER>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off, npre < nstage, peers, status);
     QK_STAMP(warp == 0, 123);
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
   } else if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
@@ -637,11 +658,11 @@ bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P, bool force_cw8 = f
   return true;
 }
 
-template <int M, bool INCTA, int CW, int G>
+template <int M, bool INCTA, int CW, int G, bool PEER = false>
 cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
                        unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
                        cudaStream_t s, const QkPeers *peers = nullptr) {
-  auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW, G>;
+  auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW, G, PEER>;
   static QkPerDevice attr_set;
   if (attr_set.first()) {
     cudaError_t e =
@@ -663,8 +684,8 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
     c0.gridDim = dim3((quads + 255) / 256), c0.blockDim = dim3(256), c0.stream = s;
     c0.attrs = at, c0.numAttrs = use_pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&c0, qk_xsplit_kernel, x, (uint32_t)M, L.cols, P.Kp,
-                                       P.S.PS, P.S.xs_off, ximg, peers ? peers->wait_flags : nullptr,
-                                       peers ? peers->wait_epoch : nullptr, peers ? peers->wait_n : 0u, status);
+                                       P.S.PS, P.S.xs_off, ximg, peers ? peers->wait_slots : nullptr,
+                                       peers ? peers->wait_epoch : nullptr, peers ? peers->wait_ld : (uint64_t)0, status);
     if (e != cudaSuccess) return e;
   }
   static int ctas = -1;  // developer knob: persistent CTAs per SM (they must fit: see QK_CW, QK_NSTAGE)
@@ -714,30 +735,42 @@ cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, fl
   // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
   // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
   const int cw = P.cw;
-#define QK_LAUNCH(CWV, GV)                                                                       \
-  return split_in_cta(P, M)                                                                      \
-             ? launch_mma<M, true, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
-             : launch_mma<M, false, CWV, GV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers)
+  const bool peer = peers != nullptr;
+#define QK_LAUNCH1(CWV, GV, PV)                                                                       \
+  return split_in_cta(P, M)                                                                           \
+             ? launch_mma<M, true, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
+             : launch_mma<M, false, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers)
+#define QK_LAUNCH(CWV, GV)          \
+  do {                              \
+    if (peer) {                     \
+      QK_LAUNCH1(CWV, GV, true);    \
+    } else {                        \
+      QK_LAUNCH1(CWV, GV, false);   \
+    }                               \
+  } while (0)
   if constexpr (M == 1)
     if (cw == 12) QK_LAUNCH(12, 3);
-  if (cw == 8) {
+#ifdef QK_DEV_KNOBS  // the 16-warp variants exist for experiments only (QK_CW=16)
+  if (cw == 16) {
     switch (P.groups) {
       case 4:
-        QK_LAUNCH(8, 4);
+        QK_LAUNCH(16, 4);
       case 2:
-        QK_LAUNCH(8, 2);
+        QK_LAUNCH(16, 2);
       default:
-        QK_LAUNCH(8, 1);
+        QK_LAUNCH(16, 1);
     }
   }
+#endif
   switch (P.groups) {
     case 4:
-      QK_LAUNCH(16, 4);
+      QK_LAUNCH(8, 4);
     case 2:
-      QK_LAUNCH(16, 2);
+      QK_LAUNCH(8, 2);
     default:
-      QK_LAUNCH(16, 1);
+      QK_LAUNCH(8, 1);
   }
+#undef QK_LAUNCH1
 #undef QK_LAUNCH
 }
 

@@ -49,22 +49,25 @@ cudaError_t qk_launch_fused_simple(const QkLayout &L, const uint8_t *tiled, cons
                                    float *out, cudaStream_t s);
 cudaError_t qk_launch_quantize_q8_0(const float *x, uint64_t n, uint8_t *out, cudaStream_t s);
 
-// Output fan-out of a row-sharded matvec: the kernel stores every result into the
-// gathered buffer of each rank of the node (plain peer stores over NVLink; entry `rank`
-// is the local buffer), then the last CTA to finish publishes the call's epoch in every
-// rank's flag array.  n == 0: ordinary local output.
+// Output fan-out of a row-sharded matvec.  Every rank of the node owns a buffer of 8-byte
+// slots, one per output element of the gathered [m x world * rows] result: the f32 value in
+// the low half, the call's tag (its ordinal on that buffer, from 1) in the high half.  The
+// kernel that computes a result stores the pair, as one 64-bit word, into the slot of every
+// rank (plain peer stores over NVLink; entry `rank` is the local buffer).  A naturally
+// aligned 64-bit store is single-copy atomic, so a reader that sees the tag it expects has
+// the value that belongs to it: no fence, flag or counter stands between the data and its
+// consumer, and nothing waits for a peer's acknowledgement.  n == 0: ordinary local output.
 #define QK_MAX_PEERS 8
 struct QkPeers {
-  float *y[QK_MAX_PEERS];         // each rank's buffer, already offset to this rank's columns
-  unsigned *flags[QK_MAX_PEERS];  // each rank's flag array [n]
-  unsigned *counter;              // local: CTAs finished in this launch (returns to 0)
-  unsigned *epoch;                // local: calls completed so far
+  unsigned long long *slots[QK_MAX_PEERS];  // each rank's slot array, already offset to this rank's columns
+  unsigned *counter;                        // local: CTAs finished in this launch (returns to 0)
+  unsigned *epoch;                          // local: calls completed so far on this buffer (the last tag used)
   uint32_t n, rank;
-  // optional: before the kernel reads its activations, wait (bounded) until all wait_n
-  // ranks' flags in wait_flags have reached *wait_epoch (the activations are the gathered
-  // output of an earlier sharded call)
-  const unsigned *wait_flags, *wait_epoch;
-  uint32_t wait_n;
+  // optional: the activations are the gathered output of an earlier sharded call and are
+  // read straight from its slots, each read waiting (bounded) for the tag *wait_epoch
+  const unsigned long long *wait_slots;     // slot of x[0][0]; row stride = wait_ld slots
+  const unsigned *wait_epoch;
+  uint64_t wait_ld;
 };
 
 // Bandwidth-bound decode path (m <= QK_GEMV_MAX_M): bulk-copied tiles, integer dot.
@@ -82,6 +85,13 @@ cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const fl
 cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, const float *x,
                                      float *y, uint32_t m, uint64_t ldy, unsigned *status,
                                      unsigned char *scratch, int sm_count, cudaStream_t s);
+// Decode kernels that can store their results into every rank's tagged slots themselves
+// (and read gathered activations out of slots): `peers` as described at QkPeers.
+bool qk_gemv_peer_supported(const QkLayout &L, uint32_t m);
+size_t qk_gemv_peer_scratch_bytes(const QkLayout &L, uint32_t m);
+cudaError_t qk_launch_gemv_peer(const QkLayout &L, const uint8_t *tiled, const float *x, uint32_t m,
+                                uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
+                                cudaStream_t s, const QkPeers *peers);
 size_t qk_gemv_fast_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                 uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,

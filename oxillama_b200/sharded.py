@@ -111,23 +111,36 @@ class _DevPtr:
 
 class PeerGather:
     """Gathered outputs of a row-sharded layer over the GPUs of one node, without a
-    collective: every rank's matvec stores its block into every rank's buffer over NVLink
-    and publishes an epoch flag (`qk_gemm_gather_dev`); `wait()` enqueues the bounded
-    wait for all blocks.  The ranks exchange the CUDA IPC handles of their buffers through
-    `torch.distributed` (any host channel would do).
+    collective: every rank's matvec stores its block, as (value, tag) words, into a slot
+    array of every rank over NVLink (`qk_gemm_gather_dev`); the consumer is either the next
+    sharded matvec, which reads its activations straight from the slots as they arrive
+    (`after=`), or `wait()`, which unpacks them into `buffer`.  Every wait is bounded.  The
+    ranks exchange the CUDA IPC handles of their slot arrays through `torch.distributed`
+    (any host channel would do).
 
-    Every rank must issue the same sequence of calls on a `PeerGather`; alternate two
-    of them if call k + 1 should overlap the consumers of call k.
+    Every rank must issue the same sequence of calls on a `PeerGather`.  A call overwrites
+    the previous call's slots in every rank: alternate two objects when each call waits for
+    the one before it, four when the wait trails by one call.
     """
 
-    def __init__(self, rows_per_rank: int, m_cap: int = 1, group: Optional[dist.ProcessGroup] = None, ctx=None):
+    def __init__(self, rows_per_rank: int, m_cap: int = 1, group: Optional[dist.ProcessGroup] = None, ctx=None,
+                 _local=None):
         import ctypes as C
         from .kernels import default_context
         self.ctx = ctx or default_context()
         self.group = group
+        self.rows, self.m_cap = rows_per_rank, m_cap
+        self._siblings = None
+        if _local is not None:  # one of several ranks emulated inside this process (see local_world)
+            self.world, self.rank = _local
+            h = C.c_void_p()
+            self.ctx.check(self.ctx.lib.qk_gather_create(self.ctx.handle, rows_per_rank, m_cap, self.world,
+                                                         self.rank, C.byref(h)))
+            self.handle = h
+            self._view()
+            return
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.rows, self.m_cap = rows_per_rank, m_cap
         # Failures are agreed on by all ranks before anyone raises, so that no rank is left
         # waiting in a collective for one that has already given up.
         h, err, payload = C.c_void_p(), None, None
@@ -159,19 +172,42 @@ class PeerGather:
             dist.all_gather_object(oks, err is None, group=group)
             if err is None and not all(oks):
                 err = RuntimeError("a peer rank could not import the gather buffers")
-        if err is not None:
+        if err is not None:  # every rank is here (the failure was agreed on above)
+            if h:
+                self.ctx.lib.qk_gather_close_peers(self.ctx.handle, h)
+            if self.world > 1:
+                dist.barrier(group=group)
             if h:
                 self.ctx.lib.qk_gather_destroy(self.ctx.handle, h)
             self.handle = None
             raise err
-        ptr = self.ctx.lib.qk_gather_buffer(h)
-        self.buffer = torch.as_tensor(_DevPtr(ptr, (m_cap, self.world * rows_per_rank)), device="cuda")
+        self._view()
+
+    @classmethod
+    def local_world(cls, rows_per_rank: int, world: int, m_cap: int = 1, ctx=None) -> "list[PeerGather]":
+        """`world` ranks inside this process and on this GPU, wired to one another without IPC:
+        what a single-GPU test drives to exercise the cross-rank protocol (the ranks' calls
+        are enqueued one after another on one stream, producers before their consumers)."""
+        ranks = [cls(rows_per_rank, m_cap, ctx=ctx, _local=(world, r)) for r in range(world)]
+        for a in ranks:
+            for b in ranks:
+                if a is not b:
+                    a.ctx.check(a.ctx.lib.qk_gather_import_local(a.ctx.handle, a.handle, b.rank, b.handle))
+        for a in ranks:
+            a.ctx.check(a.ctx.lib.qk_gather_ready(a.ctx.handle, a.handle))
+            a._siblings = ranks
+        return ranks
+
+    def _view(self):
+        ptr = self.ctx.lib.qk_gather_buffer(self.handle)
+        self.buffer = torch.as_tensor(_DevPtr(ptr, (self.m_cap, self.world * self.rows)), device="cuda")
 
     def gemm(self, dw, x: torch.Tensor, m: int = 1, after: "PeerGather | None" = None, stream=None) -> None:
         """Enqueues this rank's shard matvec with its result fanned out to every rank.
 
-        `after`: x is the gathered output of the latest call on that PeerGather; the kernels
-        wait for all of its blocks before they read x."""
+        `after`: x lies inside `after.buffer` and stands for the gathered output of the latest
+        call on that PeerGather; the kernels read it from the arriving slots (or unpack it
+        first where they cannot)."""
         import ctypes as C
         from .device import _stream_ptr
         self.ctx.check(self.ctx.lib.qk_gemm_gather_after_dev(
@@ -179,14 +215,27 @@ class PeerGather:
             after.handle if after is not None else None, _stream_ptr(stream)))
 
     def wait(self, stream=None) -> None:
+        """Enqueues the (bounded) wait for every block of the latest call; `buffer` then holds it."""
         from .device import _stream_ptr
         self.ctx.check(self.ctx.lib.qk_gather_wait_dev(self.ctx.handle, self.handle, _stream_ptr(stream)))
+
+    def _teardown(self, h):
+        # two steps with a rendezvous between them: nobody frees arrays a peer still has open
+        self.ctx.lib.qk_gather_close_peers(self.ctx.handle, h)
+        if self.world > 1 and self._siblings is None and dist.is_initialized():
+            dist.barrier(group=self.group)
+        self.ctx.lib.qk_gather_destroy(self.ctx.handle, h)
 
     def free(self):
         if self.handle:
             self.buffer = None
-            if self.world > 1:
+            if self._siblings is not None:  # in-process ranks: close every rank's view first
                 torch.cuda.synchronize()
-                dist.barrier(group=self.group)  # nobody may still be storing into this rank's buffer
-            self.ctx.lib.qk_gather_destroy(self.ctx.handle, self.handle)
+                for sib in self._siblings:
+                    if sib.handle:
+                        sib.ctx.lib.qk_gather_close_peers(sib.ctx.handle, sib.handle)
+            elif self.world > 1:
+                torch.cuda.synchronize()
+                dist.barrier(group=self.group)  # nobody may still be storing into this rank's slots
+            self._teardown(self.handle)
             self.handle = None

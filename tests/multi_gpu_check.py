@@ -40,7 +40,7 @@ def main():
         dw = DeviceWeights(t, w, rows, cols, b, e)
         xd = torch.from_numpy(x).cuda()
         pg = PeerGather(e - b, m_cap=m)
-        for call in range(3):  # the epoch protocol across repeated calls
+        for call in range(3):  # the call counting across repeated calls
             pg.gemm(dw, xd * (call + 1), m)
             pg.wait()
             torch.cuda.synchronize()
@@ -89,6 +89,45 @@ def main():
             dist.barrier()  # nobody starts the next round while a rank still reads this one
         check_device_status()
         g1.free(), g2.free(), d1.free(), d2.free()
+    # A decode chain as a model runs it: eight sharded layers, each reading the gathered output
+    # of the one before it straight from the arriving slots, two gather objects alternating,
+    # no host synchronisation between the layers or between repeats.  Every layer's gathered
+    # result must equal, bit for bit, what one GPU computes for the whole matrix.
+    n, layers, repeats = 64 * world, 8, 60
+    ws = [S.gen_weight(S.Q4_K, n, n if l else 512, seed=75, stream=l, d_range=(1e-3, 2e-3)) for l in range(layers)]
+    x0 = torch.from_numpy(S.gen_acts(1, 512, seed=75)).cuda()
+    whole = [DeviceWeights(S.Q4_K, ws[l], n, n if l else 512) for l in range(layers)]
+    want, cur = [], x0
+    for l in range(layers):
+        y = torch.empty((1, n), device="cuda")
+        whole[l].gemm(cur, y, 1)
+        want.append(y)
+        cur = y
+    b, e = shard_rows(n, world, rank)
+    shards = [DeviceWeights(S.Q4_K, ws[l], n, n if l else 512, b, e) for l in range(layers)]
+    gs = [PeerGather(e - b) for _ in range(2)]
+    keep = torch.empty((repeats, layers, n), device="cuda")
+    for rep in range(repeats):
+        for l in range(layers):
+            g, prev = gs[l & 1], gs[(l + 1) & 1]
+            if l == 0:
+                # the first layer of a repeat overwrites gs[0]: the last layer of the previous
+                # repeat, which read it, has been waited for below by every rank
+                g.gemm(shards[0], x0, 1)
+            else:
+                g.gemm(shards[l], prev.buffer, 1, after=prev)
+            g.wait()
+            keep[rep, l].copy_(g.buffer[0])
+    torch.cuda.synchronize()
+    check_device_status()
+    for l in range(layers):
+        if not bool((keep[:, l] == want[l][0]).all()):
+            bad += 1
+            print(f"rank {rank}: decode chain layer {l}: gathered values differ from the single-GPU result", flush=True)
+    for g in gs:
+        g.free()
+    for d in whole + shards:
+        d.free()
     # expert-sharded mixture of experts: each rank runs its experts, NCCL sums the outputs
     from oxillama_b200 import moe
     for t in (S.Q4_K, S.IQ4_XS):
