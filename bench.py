@@ -9,9 +9,18 @@ streams its weights from HBM).  `value` is weight-GB/s with everything resident
 in HBM (CUDA events on the launching stream); `e2e` is the same metric through
 the host-pointer C-ABI call a binding of the reference's `QuantKernel::gemv`
 makes (pinned host activations in, host outputs back, copies inside the timed
-region).  With N > 1 ranks every rank owns a 14336-row shard of an
-(N*14336) x 4096 matrix and the shard outputs are all-gathered over NCCL after
-every matvec (weak scaling).
+region).
+
+With N > 1 ranks every rank owns a 14336-row shard of an (N*14336) x 4096 matrix
+(weak scaling) and every matvec's output reaches all ranks: the matvec kernel
+stores each result, tagged, into a slot array of every rank over NVLink, and a
+bounded unpacking wait on every rank polls all N*14336 slots of the call; the
+gathered vector is compared with an NCCL all-gather of the single-GPU results
+before anything is timed (`gather_checked`).
+
+Beside the headline the line carries the other configurations' figures
+(`decode_shapes`, `small_batch`, `layer`, `prefill`, `moe`) and, for N > 1,
+strong-scaling figures of the large shapes (`strong_scaling`).
 
 `--impl reference` times the CPU restatement of the reference's own fastest
 tier (oracle/qk_cpu_simd.c: AVX-512 / AVX2 rows under a row-parallel driver) on
@@ -38,7 +47,6 @@ from oxillama_b200 import synth as S  # noqa: E402
 
 ROWS, COLS, QTYPE = 14336, 4096, S.Q4_K
 RING = 16
-NOWAIT = bool(os.environ.get("QK_BENCH_NOWAIT"))  # developer knob: fan out but never wait for the peers
 METRIC = "q4_k_gemv_weight_bandwidth"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the
@@ -62,44 +70,159 @@ def tensor_peak():
     return 1590.0, "fallback"
 
 
-def prefill_rate(torch, ctx, qtype, rows, cols, m, stream, launches=96):
-    """Batched matmul (prefill) of one weight shape: TFLOP/s over graph-replayed launches that
-    rotate through enough weight copies to exceed L2; everything resident in HBM."""
-    from oxillama_b200.device import DeviceWeights, check_device_status
-    nbytes = S.weight_nbytes(qtype, rows, cols)
-    ring = max(2, min(16, int(300e6 / nbytes) + 1))
-    base = S.gen_weight(qtype, rows, cols, seed=0, stream=97)
-    dws = [DeviceWeights(qtype, base, rows, cols, ctx=ctx) for _ in range(ring)]
-    x = torch.from_numpy(S.gen_acts(m, cols, seed=1)).cuda()
-    y = torch.empty(m, rows, device="cuda")
+def big_weight(qtype, rows, cols, seed, stream):
+    """A seeded weight matrix; matrices above 64 MB repeat a seeded 1/8-row draw eight times
+    (same distribution, an eighth of the host time)."""
+    if S.weight_nbytes(qtype, rows, cols) <= 64e6 or rows % 8:
+        return S.gen_weight(qtype, rows, cols, seed=seed, stream=stream)
+    return np.tile(S.gen_weight(qtype, rows // 8, cols, seed=seed, stream=stream), 8)
+
+
+def graph_us(torch, stream, fn, calls_per_fn, launches=200, warm=3):
+    """fn() enqueues `calls_per_fn` kernels' worth of work on the current stream; it is captured
+    once into a CUDA graph and replayed.  Returns microseconds per call (CUDA events)."""
     with torch.cuda.stream(stream):
-        for d in dws:
-            d.gemm(x, y, m)
+        fn()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
-            for d in dws:
-                d.gemm(x, y, m)
-        for _ in range(3):
+            fn()
+        for _ in range(warm):
             g.replay()
         torch.cuda.synchronize()
-        iters = max(1, launches // ring)
+        iters = max(1, launches // calls_per_fn)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(iters):
             g.replay()
         e1.record(stream)
         torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * calls_per_fn)
+
+
+def ring_of(qtype, rows, cols, ctx, seed=0, stream0=97, min_bytes=300e6, row_begin=0, row_end=None, host=None):
+    """Enough device copies of one weight (or row shard) that a pass over them exceeds L2."""
+    from oxillama_b200.device import DeviceWeights
+    row_end = rows if row_end is None else row_end
+    nbytes = S.weight_nbytes(qtype, row_end - row_begin, cols)
+    ring = max(2, min(16, int(min_bytes / max(nbytes, 1)) + 1))
+    base = host if host is not None else big_weight(qtype, rows, cols, seed, stream0)
+    return [DeviceWeights(qtype, base, rows, cols, row_begin, row_end, ctx=ctx) for _ in range(ring)]
+
+
+def matvec_rates(torch, ctx, qtype, rows, cols, ms, stream, bound="hbm", launches=128):
+    """One weight shape at each batch size of `ms`: microseconds per call over graph-replayed
+    launches that rotate through enough weight copies to exceed L2, and the fraction of the
+    roofline that bounds it."""
+    from oxillama_b200.device import check_device_status
+    dws = ring_of(qtype, rows, cols, ctx)
+    nbytes = dws[0].algo_bytes
+    outs = []
+    for m in ms:
+        x = torch.from_numpy(S.gen_acts(m, cols, seed=1)).cuda()
+        y = torch.empty(m, rows, device="cuda")
+
+        def fn():
+            for d in dws:
+                d.gemm(x, y, m)
+        us = graph_us(torch, stream, fn, len(dws), launches)
         check_device_status(ctx, stream)
-    us = e0.elapsed_time(e1) * 1e3 / (iters * ring)
+        out = {"workload": f"{S.NAMES[qtype]} {rows}x{cols}, M={m}", "us_per_launch": us, "ring_copies": len(dws)}
+        if bound == "hbm":
+            peak, which = peaks()
+            gbs = nbytes / us / 1e3
+            out.update({"weight_gbs": gbs, "frac": gbs / peak, "bound": "hbm", "peak_source": which,
+                        "floor_us": nbytes / peak / 1e3})
+        else:
+            peak, which = tensor_peak()
+            tf = 2.0 * m * rows * cols / us / 1e6
+            out.update({"tflops": tf, "frac": tf / peak, "bound": "tensor", "peak_tflops": peak, "peak_source": which,
+                        "operands": "fp16 (weights dequantised in the kernel), f32 accumulation in TMEM"})
+        outs.append(out)
     for d in dws:
         d.free()
+    return outs
+
+
+def matvec_rate(torch, ctx, qtype, rows, cols, m, stream, bound="hbm", launches=128):
+    return matvec_rates(torch, ctx, qtype, rows, cols, [m], stream, bound, launches)[0]
+
+
+LAYER = [("q", S.Q4_K, 4096, 4096), ("k", S.Q4_K, 1024, 4096), ("v", S.Q4_K, 1024, 4096),
+         ("o", S.Q4_K, 4096, 4096), ("gate", S.Q4_K, 14336, 4096), ("up", S.Q4_K, 14336, 4096),
+         ("down", S.Q6_K, 4096, 14336)]
+
+
+def layer_rates(torch, ctx, ms, stream, copies=3):
+    """The seven linears of one Llama-3-8B-shaped decoder layer (Q4_K_M mix), one call each with
+    an independent input, `copies` distinct layers in rotation (3 x 138 MB > L2), at each batch
+    size of `ms`."""
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    hosts = [(t, r, c, S.gen_weight(t, r, c, seed=4, stream=i)) for i, (_, t, r, c) in enumerate(LAYER)]
+    layers = [[DeviceWeights(t, w, r, c, ctx=ctx) for (t, r, c, w) in hosts] for _ in range(copies)]
+    nbytes = sum(d.algo_bytes for d in layers[0])
+    outs = []
+    for m in ms:
+        xs = {c: torch.from_numpy(S.gen_acts(m, c, seed=4)).cuda() for c in (4096, 14336)}
+        ys = {r: torch.empty(m, r, device="cuda") for r in (4096, 1024, 14336)}
+
+        def fn():
+            for lw in layers:
+                for d in lw:
+                    d.gemm(xs[d.cols], ys[d.rows], m)
+        us = graph_us(torch, stream, fn, copies, launches=60)
+        check_device_status(ctx, stream)
+        flops = sum(2.0 * m * d.rows * d.cols for d in layers[0])
+        out = {"workload": f"config[3]: q,k,v,o,gate,up Q4_K + down Q6_K of one layer, M={m}", "us_per_layer": us,
+               "weight_bytes": nbytes}
+        if m <= 64:
+            peak, which = peaks()
+            out.update({"weight_gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "bound": "hbm",
+                        "floor_us": nbytes / peak / 1e3, "peak_source": which})
+        else:
+            peak, which = tensor_peak()
+            out.update({"tflops": flops / us / 1e6, "frac": flops / us / 1e6 / peak, "bound": "tensor",
+                        "peak_source": which})
+        outs.append(out)
+    for lw in layers:
+        for d in lw:
+            d.free()
+    return outs
+
+
+def moe_rate(torch, ctx, qtype, stream, n_local=8, expert_begin=0):
+    """config[4]: Mixtral-8x7B-shaped MoE FFN, 256 tokens routed top-2 over 8 experts.  The experts
+    are device copies of three seeded matrices (gate, up, down): same sizes and traffic as eight
+    independent draws, a fraction of the host time."""
+    from oxillama_b200 import moe
+    hidden, inter, n_exp, tokens, top_k = 4096, 14336, 8, 256, 2
+    g = S.gen_weight(qtype, inter, hidden, seed=5, stream=0)
+    u = S.gen_weight(qtype, inter, hidden, seed=5, stream=1)
+    d = S.gen_weight(qtype, hidden, inter, seed=5, stream=2)
+    ex = moe.MoeExperts(qtype, [g] * n_local, [u] * n_local, [d] * n_local, hidden, inter, n_exp,
+                        expert_begin=expert_begin, ctx=ctx)
+    rng = np.random.default_rng(5)
+    logits = torch.from_numpy(rng.standard_normal((tokens, n_exp)).astype(np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((tokens, hidden)).astype(np.float32)).cuda()
+    y = torch.empty((tokens, hidden), device="cuda")
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            ex.forward(logits, x, y, top_k)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 5
+        e0.record(stream)
+        for _ in range(iters):
+            ex.forward(logits, x, y, top_k)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    ex.free()
+    flops = 2.0 * tokens * top_k * 3 * inter * hidden * (n_local / n_exp)  # expected share of the routed slots
     peak, which = tensor_peak()
-    tf = 2.0 * m * rows * cols / us / 1e6
-    return {"workload": f"{S.NAMES[qtype]} {rows}x{cols} weight x {m} tokens (f32 in, f32 out)", "tflops": tf,
-            "us_per_launch": us, "peak_tflops": peak, "peak_source": which, "frac": tf / peak,
-            "operands": "fp16 (weights dequantised in the kernel), f32 accumulation in TMEM",
-            "launches": iters * ring, "ring_copies": ring}
+    return {"workload": f"config[4]: 8 x {S.NAMES[qtype]} experts (gate, up 14336x4096; down 4096x14336), "
+                        f"256 tokens, top-2; {n_local} experts on this GPU",
+            "ms": ms, "tflops": flops / ms / 1e9, "frac": flops / ms / 1e9 / peak, "peak_source": which}
 
 
 class ClockSampler:
@@ -151,21 +274,29 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU arm
-def cpu_gemv_rate(seconds: float, threads: int | None = None):
-    """Times the reference's CPU tier restated in oracle/qk_cpu_simd.c on this host."""
+TIERS = {0: "scalar", 1: "AVX2+FMA", 2: "AVX-512F"}
+
+
+def _cpu_lib():
     so = os.path.join(ROOT, "oracle", "_build", "libqk_cpu_simd.so")
     if not os.path.exists(so):
         subprocess.check_call(["make", "-s", "-C", os.path.join(ROOT, "oracle")])
-    lib = C.CDLL(so)
-    tier = lib.qk_cpu_best_tier()
+    return C.CDLL(so)
+
+
+def cpu_gemv_rate(seconds: float, threads: int | None = None, tier: int | None = None, qtype=QTYPE, rows=ROWS,
+                  cols=COLS, w=None):
+    """Times the reference's CPU tiers restated in oracle/qk_cpu_simd.c on this host."""
+    lib = _cpu_lib()
+    tier = lib.qk_cpu_best_tier() if tier is None else tier
     cores = threads or lib.qk_cpu_max_threads()
-    w = S.gen_weight(QTYPE, ROWS, COLS, seed=0, stream=0)
-    x = S.gen_acts(1, COLS, seed=0)[0]
-    y = np.zeros(ROWS, np.float32)
+    w = S.gen_weight(qtype, rows, cols, seed=0, stream=0) if w is None else w
+    x = S.gen_acts(1, cols, seed=0)[0]
+    y = np.zeros(rows, np.float32)
     used = C.c_int()
 
     def once():
-        lib.qk_cpu_gemv(QTYPE, tier, cores, C.c_void_p(w.ctypes.data), C.c_size_t(ROWS), C.c_size_t(COLS),
+        lib.qk_cpu_gemv(qtype, tier, cores, C.c_void_p(w.ctypes.data), C.c_size_t(rows), C.c_size_t(cols),
                         C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data), C.byref(used))
 
     for _ in range(3):
@@ -175,10 +306,22 @@ def cpu_gemv_rate(seconds: float, threads: int | None = None):
         once()
         n += 1
     dt = time.perf_counter() - t0
-    tiers = {0: "scalar", 1: "AVX2+FMA", 2: "AVX-512F"}
     return {"value": w.size * n / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{n} matvecs of the full 14336x4096 Q4_K weight in {dt:.1f} s, {tiers[used.value]} rows, "
-                      f"row-parallel over {cores} threads", "ms_per_matvec": dt / n * 1e3}
+            "sample": f"{n} matvecs of the full {rows}x{cols} {S.NAMES[qtype]} weight in {dt:.1f} s, "
+                      f"{TIERS[used.value]} rows, row-parallel over {cores} threads", "ms_per_matvec": dt / n * 1e3}
+
+
+def cpu_tiers_one_core(seconds_each: float):
+    """What the reference actually runs (its call chain is single-threaded): the scalar, AVX2 and
+    AVX-512 row kernels on one core, same weight and activations as the headline."""
+    lib = _cpu_lib()
+    best = lib.qk_cpu_best_tier()
+    w = S.gen_weight(QTYPE, ROWS, COLS, seed=0, stream=0)
+    out = {}
+    for tier in range(best + 1):
+        r = cpu_gemv_rate(seconds_each, threads=1, tier=tier, w=w)
+        out[TIERS[tier]] = {"value": r["value"], "unit": UNIT, "ms_per_matvec": r["ms_per_matvec"]}
+    return out
 
 
 def run_reference(args):
@@ -203,6 +346,42 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------ GPU arm
+def sharded_rate(torch, dist, ctx, qtype, rows, cols, stream, world, rank, launches=64):
+    """Strong scaling of one large matrix: rows split over the ranks, every matvec's output
+    gathered on all ranks (the unpacking wait trails the next matvec by one call; four gather
+    objects rotate).  Microseconds per matvec, maximum over the ranks."""
+    from oxillama_b200.device import check_device_status
+    from oxillama_b200.sharded import PeerGather, shard_rows
+    b, e = shard_rows(rows, world, rank)
+    host = big_weight(qtype, rows, cols, 0, 55)
+    dws = ring_of(qtype, rows, cols, ctx, row_begin=b, row_end=e, host=host)
+    n = len(dws)
+    n += (-n) % 4
+    pgs = [PeerGather(e - b, ctx=ctx) for _ in range(4)]
+    x = torch.from_numpy(S.gen_acts(1, cols, seed=1)).cuda()
+
+    def fn():
+        for i in range(n):
+            pgs[i % 4].gemm(dws[i % len(dws)], x, 1, unpack=pgs[(i - 1) % 4] if i else None)
+        pgs[(n - 1) % 4].wait()
+    torch.cuda.synchronize()
+    dist.barrier()
+    us = graph_us(torch, stream, fn, n, launches)
+    check_device_status(ctx, stream)
+    t = torch.tensor([us], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    nbytes = S.weight_nbytes(qtype, rows, cols)
+    for pg in pgs:
+        pg.free()
+    for d in dws:
+        d.free()
+    us = float(t)
+    peak, which = peaks()
+    return {"workload": f"{S.NAMES[qtype]} {rows}x{cols}, M=1, rows split over {world} GPUs, output gathered on all",
+            "us_per_matvec": us, "aggregate_weight_gbs": nbytes / us / 1e3, "frac_of_n_gpus_hbm": nbytes / us / 1e3 / (peak * world),
+            "peak_source": which}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -224,47 +403,64 @@ def run_ours(args):
     dws = [DeviceWeights(QTYPE, w, ROWS, COLS, ctx=ctx) for w in host_w]
     algo_bytes = dws[0].algo_bytes
     x_host = torch.from_numpy(S.gen_acts(1, COLS, seed=0)[0]).pin_memory()
-    y_host = torch.empty(ROWS, dtype=torch.float32).pin_memory()
+    y_host = torch.empty(world * ROWS, dtype=torch.float32).pin_memory()
     x = x_host.cuda()
     ys = [torch.empty(ROWS, device="cuda") for _ in range(RING)]
     gathered = torch.empty(world * ROWS, device="cuda") if world > 1 else None
     stream = torch.cuda.Stream()
     # N > 1: every matvec's shard output goes to all ranks.  "peer": the matvec kernel stores
-    # it into every rank's buffer over NVLink and publishes a flag, a bounded wait follows
-    # (two buffers alternate); "nccl": an NCCL all-gather after the matvec.
-    peer = (world > 1 or bool(os.environ.get("QK_BENCH_PEER1"))) and args.collective == "peer"
+    # it, tagged, into every rank's slots over NVLink and a bounded unpacking wait follows;
+    # "nccl": an NCCL all-gather after the matvec.
+    peer = world > 1 and args.collective == "peer"
     pgs = []
+    gather_checked = None
     if peer:
         # every rank must take the same route: agree on whether the IPC setup worked everywhere
         from oxillama_b200.sharded import PeerGather
         ok = torch.ones(1, device="cuda")
-        try:  # (world == 1 with QK_BENCH_PEER1: the protocol's own cost without NVLink)
-            pgs = [PeerGather(ROWS, m_cap=1, ctx=ctx) for _ in range(2)]
+        try:
+            pgs = [PeerGather(ROWS, m_cap=1, ctx=ctx) for _ in range(4)]
         except Exception as e:  # noqa: BLE001 - any failure means "use the NCCL route"
             print(f"rank {rank}: peer-store gather unavailable ({e!r}); falling back to NCCL", file=sys.stderr)
             ok.zero_()
-        if world > 1:
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if float(ok) == 0.0:
             peer, pgs = False, []
+    if peer:
+        # correctness before speed: the gathered vector of four matvecs against an NCCL
+        # all-gather of the plain single-GPU results, bit for bit, on every rank
+        good = torch.ones(1, device="cuda")
+        with torch.cuda.stream(stream):
+            for i in range(4):
+                pgs[i].gemm(dws[i], x, 1)
+                pgs[i].wait()
+                dws[i].gemv(x, ys[i])
+                stream.synchronize()
+                dist.all_gather_into_tensor(gathered, ys[i])
+                if not torch.equal(pgs[i].buffer[0], gathered):
+                    good.zero_()
+            torch.cuda.synchronize()
+        dist.all_reduce(good, op=dist.ReduceOp.MIN)
+        gather_checked = bool(float(good) == 1.0)
 
-    def step(distance=2):
+    def step(trail=True):
         for i in range(RING):
             if peer:
-                # Every matvec fans its block out to all ranks and, before it starts, waits
-                # in-kernel (under its prologue) for an earlier matvec's blocks from all ranks:
-                # distance 2 = the matvec before the previous one, whose buffer it is about to
-                # overwrite (two interleaved dependency chains, the cross-GPU hand-off hidden
-                # behind one matvec); distance 1 = the previous one (one decode chain, the
-                # hand-off exposed).  Either way every gather is waited for.
-                after = pgs[i & 1] if distance == 2 else pgs[(i + 1) & 1]
-                pgs[i & 1].gemm(dws[i], x, 1, after=None if NOWAIT else after)
-                if i >= RING - 2:
-                    pgs[i & 1].wait()
+                # trail: matvec i also unpacks (waits for, with a bound) all ranks' blocks of matvec
+                # i - 1, which crossed NVLink meanwhile (four gather objects rotate); else every
+                # matvec is followed at once by its own unpacking kernel (one dependent chain, two
+                # objects).
+                if trail:
+                    pgs[i % 4].gemm(dws[i], x, 1, unpack=pgs[(i - 1) % 4] if i else None)
+                else:
+                    pgs[i % 2].gemm(dws[i], x, 1)
+                    pgs[i % 2].wait()
                 continue
             dws[i].gemv(x, ys[i])
             if world > 1:
                 dist.all_gather_into_tensor(gathered, ys[i])
+        if peer and trail:
+            pgs[(RING - 1) % 4].wait()
 
     def barrier():
         torch.cuda.synchronize()
@@ -306,8 +502,8 @@ def run_ours(args):
             if graph is not None:
                 g1 = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g1, stream=stream):
-                    step(1)
-            run1 = g1.replay if g1 is not None else (lambda: step(1))
+                    step(False)
+            run1 = g1.replay if g1 is not None else (lambda: step(False))
             for _ in range(3):
                 run1()
             barrier()
@@ -321,41 +517,93 @@ def run_ours(args):
             chain_ms = e1[0].elapsed_time(e1[1]) / n1
             check_device_status(ctx, stream)
 
-        # kernel-only launch time for the roofline (no collective in the region)
+        # kernel-only launch time for the roofline (no gather in the region), graph-replayed at every N
         if world == 1:
             kernel_ms = ms / (args.steps * RING)
         else:
-            barrier()
-            e2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            e2[0].record(stream)
-            for _ in range(args.steps):
+            def plain():
                 for i in range(RING):
                     dws[i].gemv(x, ys[i])
-            e2[1].record(stream)
-            torch.cuda.synchronize()
-            kernel_ms = e2[0].elapsed_time(e2[1]) / (args.steps * RING)
+            barrier()
+            kernel_ms = graph_us(torch, stream, plain, RING, launches=RING * max(10, args.steps // 4)) * 1e-3
 
-    # ---- end to end through the reference-facing host-pointer call
-    kern = CudaQuantKernel(QTYPE, ctx)
-    qts = [QuantTensor(w, (ROWS, COLS), QTYPE) for w in host_w]
-    xn, yn = x_host.numpy(), y_host.numpy()
-    for qt in qts:  # first call uploads and caches the weights, as a model load does
-        kern.gemv(qt, xn, yn)
+    # ---- end to end: host activations in, host outputs back, every call synchronised
+    e2e_note = "qk_gemv host-pointer call per matvec; weights cached on device after first use"
     barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        for qt in qts:
-            kern.gemv(qt, xn, yn)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    if world == 1:
+        kern = CudaQuantKernel(QTYPE, ctx)
+        qts = [QuantTensor(w, (ROWS, COLS), QTYPE) for w in host_w]
+        xn, yn = x_host.numpy(), y_host.numpy()
+        for _ in range(3):  # the first call uploads and caches the weights, as a model load does
+            for qt in qts:
+                kern.gemv(qt, xn, yn)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            for qt in qts:
+                kern.gemv(qt, xn, yn)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        e2e_d2h = RING * ROWS * 4
+    elif peer:
+        # the sharded layer as its user calls it: pinned host x in, the gathered y of all
+        # ranks back in pinned host memory, per matvec (two gather objects alternate)
+        e2e_note = ("sharded call per matvec: H2D of x, shard matvec with in-kernel fan-out, unpacking wait for all "
+                    "ranks' blocks, D2H of the gathered y, stream synchronise")
+        xd = torch.empty(COLS, device="cuda")
+        with torch.cuda.stream(stream):
+            def host_call(i):
+                xd.copy_(x_host, non_blocking=True)
+                pgs[i % 2].gemm(dws[i], xd, 1)
+                pgs[i % 2].wait()
+                y_host.copy_(pgs[i % 2].buffer[0], non_blocking=True)
+                stream.synchronize()
+            for i in range(RING):
+                host_call(i)
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                for i in range(RING):
+                    host_call(i)
+            e2e_s = time.perf_counter() - t0
+            check_device_status(ctx, stream)
+        e2e_d2h = RING * world * ROWS * 4
+    else:
+        e2e_s, e2e_d2h = None, 0
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- prefill (batched matmul) on the tensor cores: reported beside the headline metric
-    prefill = None
-    if rank == 0 and not args.no_prefill:
-        prefill = [prefill_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream),
-                   prefill_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream)]
-    t = torch.tensor([ms, e2e_s * 1e3, kernel_ms, chain_ms or 0.0], device="cuda", dtype=torch.float64)
+    # ---- the other configurations, beside the headline metric
+    extras = {}
+    if world == 1 and not args.quick:
+        extras["decode_shapes"] = [
+            matvec_rate(torch, ctx, S.Q4_0, 4096, 4096, 1, stream),       # config[0]
+            matvec_rate(torch, ctx, S.Q6_K, 128256, 4096, 1, stream, launches=24),  # config[2] LM head
+            matvec_rate(torch, ctx, S.Q6_K, 4096, 14336, 1, stream),      # config[3] down
+            matvec_rate(torch, ctx, S.Q8_0, 4096, 4096, 1, stream),
+            matvec_rate(torch, ctx, S.IQ4_XS, 14336, 4096, 1, stream),    # config[4] expert gate / up
+        ]
+        extras["small_batch"] = matvec_rates(torch, ctx, S.Q4_K, 14336, 4096, (2, 4, 8, 32, 64, 128), stream)
+        extras["layer"] = layer_rates(torch, ctx, (1, 8, 32, 512), stream)
+        extras["prefill"] = [matvec_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream, bound="tensor", launches=96),
+                             matvec_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream, bound="tensor", launches=96),
+                             matvec_rate(torch, ctx, S.Q6_K, 4096, 14336, 512, stream, bound="tensor", launches=48),
+                             matvec_rate(torch, ctx, S.IQ4_XS, 14336, 4096, 512, stream, bound="tensor", launches=96)]
+        extras["moe"] = [moe_rate(torch, ctx, S.IQ4_XS, stream), moe_rate(torch, ctx, S.Q4_K, stream)]
+    elif world > 1 and peer and not args.quick:
+        extras["strong_scaling"] = [sharded_rate(torch, dist, ctx, S.Q6_K, 128256, 4096, stream, world, rank),
+                                    sharded_rate(torch, dist, ctx, S.Q4_K, 14336, 4096, stream, world, rank),
+                                    sharded_rate(torch, dist, ctx, S.Q6_K, 4096, 14336, stream, world, rank)]
+        if 8 % world == 0:  # expert-sharded MoE: this rank's experts for all tokens (outputs summed over the ranks)
+            from oxillama_b200 import moe as _moe
+            b, e = _moe.expert_range(8, world, rank)
+            r = moe_rate(torch, ctx, S.IQ4_XS, stream, n_local=e - b, expert_begin=b)
+            t = torch.tensor([r["ms"]], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            r["ms"] = float(t)
+            r["tflops_aggregate"] = 180.39e9 / r["ms"] / 1e9
+            r["note"] = "local experts' share only; the all-reduce of the outputs is not in the figure"
+            extras["moe"] = [r]
+
+    t = torch.tensor([ms, (e2e_s or 0.0) * 1e3, kernel_ms, chain_ms or 0.0], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms, kernel_ms, chain_ms = (float(v) for v in t.cpu())
@@ -363,6 +611,7 @@ def run_ours(args):
     if rank == 0:
         peak, which = peaks()
         achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        launches_per_matvec = 1
         line = {
             "metric": METRIC, "value": total_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
@@ -371,27 +620,32 @@ def run_ours(args):
                        "l2": f"{RING} distinct weight copies ({RING * algo_bytes / 1e6:.0f} MB) rotate, larger than L2",
                        "sharding": "none" if world == 1 else
                        f"{world} row shards of ({world}x14336)x4096; y of every matvec " +
-                       ("stored into every rank by the matvec kernel over NVLink; each matvec first waits "
-                        "in-kernel for the blocks, from all ranks, of the matvec before the previous one "
-                        "(see dependent_chain for distance 1)" if peer else "all-gathered by NCCL")},
-            "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": RING * COLS * 4, "d2h_bytes_per_step": RING * ROWS * 4,
-                    "note": "qk_gemv host-pointer call per matvec; weights cached on device after first use"},
-            "gpu_launches": RING * args.steps,
+                       ("stored, tagged, into every rank's slots by the matvec kernel over NVLink; matvec i + 1 "
+                        "waits for and unpacks all ranks' blocks of matvec i while its first weight tiles are in "
+                        "flight (see dependent_chain for a separate wait directly behind each matvec)" if peer
+                        else "all-gathered by NCCL")},
+            "e2e": ({"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                     "h2d_bytes_per_step": RING * COLS * 4, "d2h_bytes_per_step": e2e_d2h, "note": e2e_note}
+                    if e2e_s is not None else None),
+            "gpu_launches": RING * args.steps * launches_per_matvec,
             "cuda_graph": graph is not None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "traffic": DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": algo_bytes,
                          "us_per_launch": kernel_ms * 1e3},
             "clocks": clocks,
         }
+        if gather_checked is not None:
+            line["gather_checked"] = gather_checked
         if peer and chain_ms:
             line["dependent_chain"] = {
                 "value": algo_bytes * RING * world / (chain_ms * 1e-3) / 1e9, "unit": UNIT,
                 "ms_per_step": chain_ms,
-                "note": "same work, every matvec waiting for the previous one's blocks from all ranks"}
+                "note": "same work, every matvec followed at once by the wait for all ranks' blocks"}
         if world == 1:
             line["cpu_baseline"] = cpu_gemv_rate(args.cpu_seconds)
-        line["prefill"] = prefill
+            if not args.quick:
+                line["cpu_baseline"]["one_core"] = cpu_tiers_one_core(2.0)
+        line.update(extras)
         print(json.dumps(line))
     for pg in pgs:
         pg.free()
@@ -407,7 +661,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-graph", action="store_true", help="launch every matvec from the host")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the batched-matmul measurements")
+    ap.add_argument("--quick", action="store_true", help="the headline metric only (no other configurations)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="N = 1: only the batched-matmul measurements (a short run, e.g. for a profiler)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
@@ -420,8 +674,9 @@ def main():
         from oxillama_b200.kernels import Context
         torch.cuda.set_device(0)
         ctx, stream = Context(0), torch.cuda.Stream()
-        print(json.dumps({"prefill": [prefill_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream, launches=30),
-                                      prefill_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream, launches=32)]}))
+        print(json.dumps({"prefill": [
+            matvec_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream, bound="tensor", launches=30),
+            matvec_rate(torch, ctx, S.Q8_0, 4096, 4096, 512, stream, bound="tensor", launches=32)]}))
     else:
         run_ours(args)
 

@@ -210,6 +210,14 @@ int qk_gemm_gather_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, siz
  * otherwise qk_gather_wait_dev(after) is enqueued first.  after == NULL: plain x_dev. */
 int qk_gemm_gather_after_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
                              qk_gather *after, void *stream);
+/* The same, and in passing the latest call on `unpack` (another object, not g) is unpacked
+ * into its plain buffer as qk_gather_wait_dev would do, by the matvec kernel itself while
+ * its first weight tiles are on their way (where the matvec kernel does the peer stores;
+ * otherwise qk_gather_wait_dev(unpack) is enqueued first).  A decode loop that wants every
+ * gathered result in plain memory passes the previous call's object here and pays neither
+ * a kernel nor a gap between two matvecs for it.  after and unpack may be NULL. */
+int qk_gemm_gather_unpack_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
+                              qk_gather *after, qk_gather *unpack, void *stream);
 /* Enqueues the unpacking of the latest call into the plain buffer: every slot is waited
  * for (at most 0.25 s per thread, then QK_TIMEOUT through qk_check_device_status and
  * zeros in the places that did not arrive). */

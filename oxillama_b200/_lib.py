@@ -50,6 +50,7 @@ SIGNATURES = {
     "qk_gather_buffer": (vp, [vp]),
     "qk_gemm_gather_dev": (C.c_int, [vp, vp, vp, sz, vp, vp]),
     "qk_gemm_gather_after_dev": (C.c_int, [vp, vp, vp, sz, vp, vp, vp]),
+    "qk_gemm_gather_unpack_dev": (C.c_int, [vp, vp, vp, sz, vp, vp, vp, vp]),
     "qk_gather_wait_dev": (C.c_int, [vp, vp, vp]),
     "qk_moe_route_dev": (C.c_int, [vp, vp, sz, sz, sz, vp, vp, vp]),
     "qk_moe_ffn_dev": (C.c_int, [vp, vp, vp, vp, sz, sz, sz, vp, vp, vp, sz, sz, vp]),

@@ -30,7 +30,7 @@ struct qk_gather {
   size_t last_m;               // activation rows of the latest call
   float *local;                // [m_cap][world * rows] plain result, filled by qk_gather_wait_dev
   unsigned long long *slots;   // [m_cap][world * rows] tagged slots, written by every rank
-  unsigned *ctl;               // [0] CTAs finished in the running launch, [1] calls completed (last tag)
+  unsigned *ctl;               // [0] CTAs of the running launch counted in, [1] calls issued (the latest tag)
   unsigned long long *peer_slots[QK_MAX_PEERS];
   bool opened[QK_MAX_PEERS];   // peer_slots[r] came from cudaIpcOpenMemHandle
 };
@@ -44,17 +44,27 @@ using namespace qkpeer;
 __global__ void __launch_bounds__(256)
     qk_gather_push_kernel(QkPeers peers, const float *__restrict__ src, uint32_t m, uint32_t rows,
                           uint64_t ldy) {
-  const unsigned tag = *reinterpret_cast<const volatile unsigned *>(peers.epoch) + 1u;
+  qkpipe::pdl_launch_dependents();  // the next kernel may start its prologue
+  qkpipe::pdl_wait();               // src and the call count belong to the kernels before this one
+  // this call's tag = the object's call count + 1; the CTA that is counted in last knows that
+  // every CTA has read the count and moves it on
+  __shared__ unsigned tag_s;
+  if (threadIdx.x == 0) {
+    unsigned e;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(e) : "l"(peers.epoch) : "memory");
+    if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
+      *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
+      *reinterpret_cast<volatile unsigned *>(peers.epoch) = e + 1u;
+    }
+    tag_s = e + 1u;
+  }
+  __syncthreads();
+  const unsigned tag = tag_s;
   const uint64_t n = (uint64_t)m * rows;
   for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += (uint64_t)gridDim.x * 256) {
     const uint64_t off = (i / rows) * ldy + (i % rows);
     const float v = src[off];
     for (uint32_t p = 0; p < peers.n; p++) slot_store(peers.slots[p] + off, v, tag);
-  }
-  __syncthreads();  // every thread has read the call count
-  if (threadIdx.x == 0 && atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
-    *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
-    *reinterpret_cast<volatile unsigned *>(peers.epoch) = tag;
   }
 }
 
@@ -64,7 +74,12 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(256)
     qk_gather_unpack_kernel(const unsigned long long *slots, const unsigned *epoch, float *__restrict__ out,
                             uint64_t n, unsigned *status) {
-  const unsigned want = *epoch;
+  // Programmatic dependent launch on both sides: the kernel after this one (usually the next
+  // matvec) becomes resident and prefetches its weights while the slots are polled, and this
+  // kernel was itself resident before the matvec in front of it had drained.
+  qkpipe::pdl_launch_dependents();
+  qkpipe::pdl_wait();  // the call count is written by the last CTA of the producing kernel
+  const unsigned want = *reinterpret_cast<const volatile unsigned *>(epoch);
   bool arrived = true;
   for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += (uint64_t)gridDim.x * 256) {
     float v = 0.f;
@@ -84,6 +99,19 @@ __global__ void qk_gather_touch_kernel(QkPeers peers) {
     slot_store(peers.slots[threadIdx.x], 0.f, 0u);
     __threadfence_system();
   }
+}
+
+// Launch with programmatic stream serialization allowed (the kernels above order themselves
+// with griddepcontrol.wait).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned blocks, unsigned threads, cudaStream_t s, Args... args) {
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(threads), cfg.stream = s;
+  cfg.attrs = at, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
 int fail(qk_ctx *c, cudaError_t e, const char *what) {
@@ -224,15 +252,22 @@ extern "C" int qk_gather_wait_dev(qk_ctx *c, qk_gather *g, void *stream) {
   unsigned blocks = (unsigned)((n + 255) / 256);
   const unsigned cap = (unsigned)c->sm_count * 2u;
   if (blocks > cap) blocks = cap;
-  qk_gather_unpack_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g->slots, g->ctl + 1, g->local, n, c->status_dev);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(qk_gather_unpack_kernel, blocks, 256, (cudaStream_t)stream,
+                             (const unsigned long long *)g->slots, (const unsigned *)(g->ctl + 1), g->local, n,
+                             c->status_dev);
   return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gather_wait_dev");
 }
 
 extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
                                         qk_gather *after, void *stream) {
+  return qk_gemm_gather_unpack_dev(c, h, x_dev, m, g, after, nullptr, stream);
+}
+
+extern "C" int qk_gemm_gather_unpack_dev(qk_ctx *c, const qk_weights *h, const float *x_dev, size_t m, qk_gather *g,
+                                         qk_gather *after, qk_gather *unpack, void *stream) {
   if (!c || !h || !x_dev || !g) return QK_INVALID_ARGUMENT;
   if (after && after->device != c->device) return QK_INVALID_ARGUMENT;
+  if (unpack && (unpack->device != c->device || unpack == g)) return QK_INVALID_ARGUMENT;
   if (h->device != c->device || g->device != c->device) return QK_INVALID_ARGUMENT;
   if (h->L.rows != g->rows || m == 0 || m > g->m_cap) return QK_DIMENSION_MISMATCH;
   for (int r = 0; r < g->world; r++)
@@ -266,6 +301,15 @@ extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const fl
       if (st) return st;
     }
   }
+  if (unpack) {
+    if (fused) {  // the matvec kernel unpacks it while its first weight tiles are in flight
+      peers.unpack_slots = unpack->slots, peers.unpack_epoch = unpack->ctl + 1, peers.unpack_out = unpack->local;
+      peers.unpack_n = (uint64_t)unpack->last_m * unpack->world * unpack->rows;
+    } else {
+      int st = qk_gather_wait_dev(c, unpack, stream);
+      if (st) return st;
+    }
+  }
   g->last_m = m;
   if (fused) {  // the matvec kernel itself stores into every rank
     const size_t need = qk_gemv_peer_scratch_bytes(h->L, (uint32_t)m);
@@ -290,8 +334,8 @@ extern "C" int qk_gemm_gather_after_dev(qk_ctx *c, const qk_weights *h, const fl
   unsigned blocks = (unsigned)((n + 255) / 256);
   const unsigned cap = (unsigned)c->sm_count * 2u;
   if (blocks > cap) blocks = cap;
-  qk_gather_push_kernel<<<blocks, 256, 0, s>>>(peers, mine, (uint32_t)m, (uint32_t)g->rows, ldy);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(qk_gather_push_kernel, blocks, 256, s, peers, (const float *)mine, (uint32_t)m,
+                             (uint32_t)g->rows, ldy);
   return e == cudaSuccess ? QK_OK : fail(c, e, "qk_gemm_gather_dev");
 }
 

@@ -353,11 +353,26 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     }
     pdl_wait();  // the x image and y belong to the previous kernel until it has finished
     QK_STAMP(true, 120);
-    // sharded output: this call's tag (the buffer's call count was left by the previous kernel on it)
-    const unsigned tag = (PEER && peers.n) ? *reinterpret_cast<const volatile unsigned *>(peers.epoch) + 1u : 0u;
     if (!INCTA && lane == 0) {
       mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
       bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
+    }
+    // Sharded output: this call's tag is the object's call count + 1.  Lane 0 reads the
+    // count, then counts this CTA in (the add carries a dependency on the value read, so it
+    // cannot overtake the read); the CTA that is counted in last knows that every CTA of the
+    // launch has read the count and moves it on.  The round trips run while the compute
+    // warps load the activations; nothing of this sits at the end of the kernel.
+    unsigned e_count = 0, uwant = 0;
+    if (PEER && peers.unpack_n)  // needed further down; asked for now, together with the count
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(uwant) : "l"(peers.unpack_epoch) : "memory");
+    if (PEER && peers.n && lane == 0) {
+      unsigned one;
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(e_count) : "l"(peers.epoch) : "memory");
+      asm volatile("and.b32 %0, %1, 0;\n\tadd.u32 %0, %0, 1;" : "=r"(one) : "r"(e_count));
+      if (atomicAdd(peers.counter, one) == gridDim.x - 1) {
+        *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
+        *reinterpret_cast<volatile unsigned *>(peers.epoch) = e_count + 1u;
+      }
     }
     if (npre < nstage) {
       // The rest of the first ring fill goes out once the compute warps' activation loads
@@ -367,12 +382,59 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       if (lane == 0)
         for (; item < (uint32_t)nstage && item < my_items; item++) issue();
     }
+    const unsigned tag = (PEER && peers.n) ? __shfl_sync(0xffffffffu, e_count, 0) + 1u : 0u;
+    // this lane's two destination ranks (lane / 8 and lane / 8 + 4), held in registers: an
+    // indexed read of the kernel parameters per chunk costs a constant-cache miss each time
+    unsigned long long *slots_a = nullptr, *slots_b = nullptr;
+    if (PEER && peers.n) {
+      const uint32_t q = lane >> 3;
+#pragma unroll
+      for (uint32_t p = 0; p < QK_MAX_PEERS; p++) {
+        if (p == q && p < peers.n) slots_a = peers.slots[p];
+        if (p == q + 4 && p < peers.n) slots_b = peers.slots[p];
+      }
+    }
+    if (PEER && peers.unpack_n) {
+      // In passing: the previous sharded call's gathered result goes from its slots into its
+      // plain buffer.  The producer warps of all CTAs share the slots, eight loads in flight
+      // per lane; this warp has nothing else to do until the first chunk is reduced.
+      const uint64_t stride = (uint64_t)gridDim.x * 32;
+      bool arrived = true;
+      for (uint64_t base = (uint64_t)blockIdx.x * 32 + lane; base < peers.unpack_n; base += 8 * stride) {
+        unsigned long long w[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const uint64_t i = base + j * stride;
+          w[j] = i < peers.unpack_n ? qkpeer::slot_load(peers.unpack_slots + i) : 0ull;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const uint64_t i = base + j * stride;
+          if (i >= peers.unpack_n) break;
+          float v = __uint_as_float((unsigned)w[j]);
+          if ((unsigned)(w[j] >> 32) != uwant) {  // not there yet: the bounded wait
+            if (arrived && !qkpeer::slot_wait(peers.unpack_slots + i, uwant, v)) {
+              arrived = false;
+              atomicOr(status, QK_DEV_TIMEOUT);
+            }
+            if (!arrived) v = 0.f;
+          }
+          peers.unpack_out[i] = v;
+        }
+      }
+    }
     uint32_t slot = 0, sph = 0;
     for (uint32_t c = 0; c < my_chunks; c++) {
       if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, sph)) {
         if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
         break;
       }
+      // Every warp of the owning group released the chunk's stages before it posted its
+      // partials: refill them first, the sums and stores below follow the copies out.  (The
+      // partial-sum ring is one slot deeper than the stage ring, so a group that runs ahead
+      // through the refilled stages cannot reach the slot that is being read here.)
+      if (lane == 0)
+        for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
       const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (WG * M * 8);
       float v = 0.f;
       if (lane < 8 * M) {
@@ -389,26 +451,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 #pragma unroll
         for (int m = 0; m < M; m++) {
           const float vm = __shfl_sync(0xffffffffu, v, m * 8 + (int)r);
-          if (row < L.rows)
-            for (uint32_t p = lane >> 3; p < peers.n; p += 4)
-              qkpeer::slot_store(peers.slots[p] + (uint64_t)m * ldy + row, vm, tag);
+          if (row < L.rows) {
+            if (slots_a) qkpeer::slot_store(slots_a + (uint64_t)m * ldy + row, vm, tag);
+            if (slots_b) qkpeer::slot_store(slots_b + (uint64_t)m * ldy + row, vm, tag);
+          }
         }
       }
       __syncwarp();
       QK_STAMP(c < 30, 64 + c);
       if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
-      // every warp of the owning group released the chunk's stages before it posted
-      // its partials
-      if (lane == 0)
-        for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
-    }
-    if (PEER && peers.n && lane == 0) {
-      // The last CTA to finish records that the buffer has seen one more call.  The count
-      // only orders this bookkeeping: the data needs no fence (see QkPeers).
-      if (atomicAdd(peers.counter, 1u) == gridDim.x - 1) {
-        *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
-        *reinterpret_cast<volatile unsigned *>(peers.epoch) = tag;
-      }
     }
     return;
   }
@@ -438,7 +489,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   } else if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
     dead = true;
   }
-
   float accA[M], accB[M], mt[M];
 #pragma unroll
   for (int m = 0; m < M; m++) accA[m] = accB[m] = mt[m] = 0.f;

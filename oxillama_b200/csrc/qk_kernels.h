@@ -60,14 +60,22 @@ cudaError_t qk_launch_quantize_q8_0(const float *x, uint64_t n, uint8_t *out, cu
 #define QK_MAX_PEERS 8
 struct QkPeers {
   unsigned long long *slots[QK_MAX_PEERS];  // each rank's slot array, already offset to this rank's columns
-  unsigned *counter;                        // local: CTAs finished in this launch (returns to 0)
-  unsigned *epoch;                          // local: calls completed so far on this buffer (the last tag used)
+  unsigned *counter;                        // local: CTAs of this launch counted in (returns to 0)
+  unsigned *epoch;                          // local: calls issued so far on this buffer (the latest tag)
   uint32_t n, rank;
   // optional: the activations are the gathered output of an earlier sharded call and are
   // read straight from its slots, each read waiting (bounded) for the tag *wait_epoch
   const unsigned long long *wait_slots;     // slot of x[0][0]; row stride = wait_ld slots
   const unsigned *wait_epoch;
   uint64_t wait_ld;
+  // optional: while its first weight tiles are on their way the kernel also unpacks the
+  // latest call of another gather object (unpack_n slots, each waited for with a bound, tag
+  // *unpack_epoch) into that object's plain buffer: the gather's completion costs no kernel
+  // of its own and no gap between two matvecs
+  const unsigned long long *unpack_slots;
+  const unsigned *unpack_epoch;
+  float *unpack_out;
+  uint64_t unpack_n;
 };
 
 // Bandwidth-bound decode path (m <= QK_GEMV_MAX_M): bulk-copied tiles, integer dot.

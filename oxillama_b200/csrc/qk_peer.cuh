@@ -7,7 +7,13 @@ namespace qkpeer {
 
 __device__ __forceinline__ void slot_store(unsigned long long *p, float v, unsigned tag) {
   const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+#if defined(QK_SLOT_NONE)
+  (void)p, (void)w;
+#elif defined(QK_SLOT_WEAK)
+  asm volatile("st.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+#else
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+#endif
 }
 __device__ __forceinline__ unsigned long long slot_load(const unsigned long long *p) {
   unsigned long long w;

@@ -202,17 +202,21 @@ class PeerGather:
         ptr = self.ctx.lib.qk_gather_buffer(self.handle)
         self.buffer = torch.as_tensor(_DevPtr(ptr, (self.m_cap, self.world * self.rows)), device="cuda")
 
-    def gemm(self, dw, x: torch.Tensor, m: int = 1, after: "PeerGather | None" = None, stream=None) -> None:
+    def gemm(self, dw, x: torch.Tensor, m: int = 1, after: "PeerGather | None" = None,
+             unpack: "PeerGather | None" = None, stream=None) -> None:
         """Enqueues this rank's shard matvec with its result fanned out to every rank.
 
         `after`: x lies inside `after.buffer` and stands for the gathered output of the latest
         call on that PeerGather; the kernels read it from the arriving slots (or unpack it
-        first where they cannot)."""
+        first where they cannot).  `unpack`: the latest call on that other PeerGather is
+        unpacked into its `buffer` in passing (what `unpack.wait()` does, without a kernel of
+        its own where the matvec kernel can do it)."""
         import ctypes as C
         from .device import _stream_ptr
-        self.ctx.check(self.ctx.lib.qk_gemm_gather_after_dev(
+        self.ctx.check(self.ctx.lib.qk_gemm_gather_unpack_dev(
             self.ctx.handle, dw.handle, C.c_void_p(x.data_ptr()), m, self.handle,
-            after.handle if after is not None else None, _stream_ptr(stream)))
+            after.handle if after is not None else None, unpack.handle if unpack is not None else None,
+            _stream_ptr(stream)))
 
     def wait(self, stream=None) -> None:
         """Enqueues the (bounded) wait for every block of the latest call; `buffer` then holds it."""

@@ -109,6 +109,42 @@ def test_decode_chain_over_a_thousand_calls():
         d.free()
 
 
+def test_unpacking_fused_into_the_next_matvec():
+    """Four gather objects in rotation, every matvec unpacking the previous call's gathered
+    result in passing (`unpack=`): each plain buffer must hold exactly what a separate wait
+    gives, i.e. the single-GPU result."""
+    import torch
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    from oxillama_b200.sharded import PeerGather
+    world, rows, cols, calls = 4, 1024, 2048, 24
+    w = S.gen_weight(S.Q4_K, rows, cols, seed=95)
+    whole = DeviceWeights(S.Q4_K, w, rows, cols)
+    shards = _shards(S.Q4_K, w, rows, cols, world)
+    xs = [torch.from_numpy(S.gen_acts(1, cols, seed=95, stream=2000 + i)).cuda() for i in range(calls)]
+    want = torch.empty((calls, rows), device="cuda")
+    for i in range(calls):
+        whole.gemm(xs[i], want[i:i + 1], 1)
+    objs = [PeerGather.local_world(rows // world, world) for _ in range(4)]   # objs[slot][rank]
+    got = torch.empty((calls, world, rows), device="cuda")
+    for i in range(calls):
+        for r in range(world):
+            objs[i % 4][r].gemm(shards[r], xs[i], 1, unpack=objs[(i - 1) % 4][r] if i else None)
+        if i:   # call i - 1 is unpacked now (stream order): keep it before call i + 3 overwrites it
+            for r in range(world):
+                got[i - 1, r].copy_(objs[(i - 1) % 4][r].buffer[0])
+    for r in range(world):
+        objs[(calls - 1) % 4][r].wait()
+        got[calls - 1, r].copy_(objs[(calls - 1) % 4][r].buffer[0])
+    torch.cuda.synchronize()
+    check_device_status()
+    assert bool((got == want[:, None, :]).all())
+    for quad in objs:
+        for g in quad:
+            g.free()
+    for d in shards + [whole]:
+        d.free()
+
+
 def test_wait_that_runs_out_is_reported_and_nothing_hangs():
     """A rank that never delivers: the other rank's bounded waits give up after a quarter of a
     second, the status word reports QK_TIMEOUT (101) once and is clear afterwards, the places
