@@ -12,7 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libqk_cuda.so")
-SOURCES = ["qk_api.cu", "qk_simple.cu", "qk_gemv.cu", "qk_gemv_mma.cu", "qk_noalloc.cu", "qk_gemm_tc.cu", "qk_moe.cu", "qk_gather.cu"]
+SOURCES = ["qk_api.cu", "qk_simple.cu", "qk_gemv_mma.cu", "qk_gemv_imma.cu", "qk_dec_q80.cu", "qk_dec_q40.cu",
+           "qk_dec_iq4xs.cu", "qk_dec_q6k.cu", "qk_noalloc.cu", "qk_gemm_tc.cu", "qk_moe.cu", "qk_gather.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -31,7 +32,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "qk_cuda.h"))
-    objs = []
+    objs, jobs = [], []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ, src.replace(".cu", ".o"))
@@ -41,7 +42,11 @@ def build(verbose: bool = False, force: bool = False) -> str:
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
                 print(" ".join(cmd), flush=True)
-            subprocess.check_call(cmd)
+            jobs.append(cmd)
+    if jobs:  # the translation units are independent: compile them side by side
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 1)) as pool:
+            list(pool.map(subprocess.check_call, jobs))
     if force or _newer(objs, LIB):
         cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
         if verbose:

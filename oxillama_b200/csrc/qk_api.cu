@@ -315,9 +315,13 @@ static int gemm_dispatch(qk_ctx *c, const qk_weights *h, const float *x, float *
                               c->sm_count, s));
     return QK_OK;
   }
-  // the tensor-core path rounds its operands to fp16; batches the decode kernels take keep f32 activations
-  // (IQ4_XS has no decode kernel of its own: every batch size of it goes this way)
-  if (!c->force_simple && (m > QK_GEMV_MAX_M || h->L.type == QK_T_IQ4_XS) && m < (1u << 30) &&
+  // The tensor-core path rounds its operands to fp16; batches the decode kernels take keep
+  // f32-grade activations.  Decode-sized calls the decode kernels cannot take (K not a
+  // multiple of 256, activations too long for shared memory) go to the generic kernel below.
+  // (Two to four rows of a format whose decode kernel stops below four rows for register
+  // reasons also go to the tensor cores.)
+  const bool tc_small = m <= QK_GEMV_MAX_M && m > 1 && qk_gemv_fast_supported(h->L, 1);
+  if (!c->force_simple && (m > QK_GEMV_MAX_M || tc_small) && m < (1u << 30) &&
       qk_gemm_tc_supported(h->L, (uint32_t)m)) {
     int st = ensure_scratch(qk_gemm_tc_scratch_bytes(h->L, (uint32_t)m));
     if (st) return st;
@@ -504,11 +508,10 @@ static int host_gemm(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t
   if (xb) CK(c, cudaMemcpyAsync(c->sa, x, xb, cudaMemcpyHostToDevice, c->stream));
   // Decode-sized calls into pinned host memory: the kernels that serve M <= 4 only store y
   // (a few KB, 32 contiguous bytes per 8-row chunk), so they write it straight through the
-  // mapping and the device-to-host copy with its launch drops out.  (Not IQ4_XS: its
-  // tensor-core path accumulates into y.)
+  // mapping and the device-to-host copy with its launch drops out.
   float *ydev = (float *)c->sb;
   bool mapped = false;
-  if (yb && m <= QK_GEMV_MAX_M && type != QK_T_IQ4_XS) {
+  if (yb && m <= QK_GEMV_MAX_M && !c->force_simple && qk_gemv_fast_supported(h->L, (uint32_t)m)) {
     cudaPointerAttributes pa;
     if (cudaPointerGetAttributes(&pa, y) == cudaSuccess && pa.type == cudaMemoryTypeHost &&
         pa.devicePointer)

@@ -1,857 +1,27 @@
-// Q4_K decode-path dequant-dot (1..4 activation rows) on the integer tensor-core MMA.
-//
-// The matvec is HBM-bound; what limits a CUDA-core version on this part is the
-// issue rate of the per-weight multiply (dp4a runs at a quarter of the FP32
-// rate here).  So the multiply-accumulate of every 32-weight sub-block is
-// handed to mma.sync.m16n8k32 (u8 x s8 -> s32), whose k = 32 is exactly one
-// Q4_K sub-block, and the CUDA cores only unpack nibbles and apply one scale
-// per sub-block.  The matrix is NOT reshaped into a GEMM: each MMA still
-// computes plain row dot products, eight weight rows at a time.
-//
-//   A (16 x 32, u8): rows 0-7  = the eight weight rows, low nibbles of one
-//                                32-byte group            (sub-block 2p: q)
-//                    rows 8-15 = same rows, the raw bytes (q_lo + 16 q_hi)
-//   B (32 x 8,  s8): even column 2j = digit j of the activations of sub-block 2p,
-//                    odd column 2j+1 = digit j of those of sub-block 2p+1 (j = 0..2;
-//                    columns 6, 7 unused)
-//   C (16 x 8, s32): C[r][2j]     = sum q_lo D_j(2p)              wanted
-//                    C[r][2j+1]   = sum q_lo D_j(2p+1)            cross term
-//                    C[8+r][2j+1] = sum (q_lo + 16 q_hi) D_j(2p+1)
-//                    so 16 * (high-nibble dot) = C[8+r][2j+1] - C[r][2j+1]: the cross
-//                    term pays for not masking the high nibbles.  Every lane of an
-//                    MMA quad then owns digit j = lane % 4 of both sub-blocks in
-//                    fixed registers (no per-lane selects).
-//
-// Activations are split per 32-column block as x ~= sx (D0 + D1/254 + D2/254^2)
-// with |D| <= 127 (error <= amax * 6.1e-8), so the integer dots are exact and
-// the result carries f32-grade accuracy:
-//   y[row] = sum_sub  d sc_sub sx_sub (I0 + I1/254 + I2/254^2)  -  dmin mn_sub Sx_sub
-// with d, dmin, sc, mn decoded as reference/q4_k.rs:27-49,141-157 and Sx the
-// f32 sum of x over the sub-block (the `- m1` term of reference/q4_k.rs:163).
-//
-// qk_gemv_q4k_mma_kernel, persistent, one CTA per SM: a producer warp streams 8-row
-// tiles into a ring of shared-memory stages with cp.async.bulk (mbarrier completion);
-// the compute warps (8 in four groups; 12 in three for short matrices) first split x
-// into the digit planes and (sx, Sx) pairs in shared memory, then a group takes every
-// G-th chunk, each warp its share of the tile's super-block columns (header decode
-// in-lane, four MMAs per column), and leaves its row partials in a small ring; the
-// producer warp sums a chunk's partials, writes the outputs and then refills the chunk's
-// stages.  No CTA-wide barrier and no compute warp ever waits for another in steady
-// state.  When M * K is too large for every CTA to redo the split, qk_xsplit_kernel
-// does it once into a scratch image in global memory, which each CTA brings in with one
-// more bulk copy.
-// Both kernels use programmatic dependent launch: call i+1 is resident and has its first
-// weight tiles (weights are immutable) under way before call i has finished;
-// griddepcontrol.wait orders everything that touches x, y or the scratch image, and the
-// rest of the ring is issued behind the activation loads, not ahead of them.  Every wait on an
-// mbarrier is bounded: when one runs out the warp stops, QK_DEV_TIMEOUT is
-// raised in the status word, and the other warps run into their own bounds.
-#include <cstdlib>
+// Q4_K decode matvec (1..4 activation rows): the Q4_K instantiation of the integer-MMA
+// decode kernel (qk_gemv_skel.cuh with the policy of qk_dec_q4k.cuh), plus the route that
+// always takes its split activations from a caller-provided image.
+#include "qk_dec_q4k.cuh"
 
-#include "qk_formats.cuh"
-#include "qk_kernels.h"
-#include "qk_peer.cuh"
-#include "qk_pipe.cuh"
-#include <type_traits>
-
-using namespace qkpipe;
+using namespace qkdec;
 
 #ifdef QK_TRACE
-// Developer build only: block 0 timestamps its pipeline into a global buffer.
 __device__ unsigned long long *qk_trace_buf = nullptr;
-#define QK_STAMP(cond, idx)                                                        \
-  do {                                                                             \
-    if ((cond) && qk_trace_buf && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {    \
-      unsigned long long t__;                                                      \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                     \
-      qk_trace_buf[idx] = t__;                                                     \
-    }                                                                              \
-  } while (0)
 extern "C" void qk_trace_set(unsigned long long *p) {
   cudaMemcpyToSymbol(qk_trace_buf, &p, sizeof(p));
 }
-#else
-#define QK_STAMP(cond, idx) do {} while (0)
 #endif
-
-namespace {
-
-constexpr int MAX_CW = 16;                      // compute warps: 8 or 16 (+ one producer warp)
-constexpr uint32_t NBT = QK_TILE_ELEMS / 256;   // super-blocks per full k-tile (16)
-constexpr int MAX_STAGE = 12;
-constexpr int MAX_SLOT = MAX_STAGE + 1;
-
-struct SmemMma {
-  uint32_t full, redfull, xbar;  // mbarriers (8 B each)
-  uint32_t red, ximg, stage;
-  uint32_t PS;         // digit plane stride, bytes
-  uint32_t xs_off;     // offset of the (sx, Sx) table inside the x image
-  uint32_t ximg_bytes;
-};
-
-// Loads at a compile-time byte offset from a register base: the offset rides in the
-// instruction, where an address built in C++ costs an integer add per load.
-template <int OFF>
-__device__ __forceinline__ uint2 lds64o(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ uint4 lds128o(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr), "n"(OFF));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ float4 lds128fo(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr), "n"(OFF));
-  return v;
-}
-template <int I, int N, typename Fn>
-__device__ __forceinline__ void static_for(Fn &&f) {
-  if constexpr (I < N) {
-    f(std::integral_constant<int, I>{});
-    static_for<I + 1, N>(f);
-  }
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                         uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm(  // a pure function of its operands: left free for the scheduler to interleave
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%11,%12,%13};"
-      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
-}
-// Exact int -> float for |v| < 2^22 on the full-rate pipes (no I2F).
-__device__ __forceinline__ float small_int_to_float(int v) {
-  return __int_as_float(0x4B400000 + v) - 12582912.0f;
-}
-
-// Four activations of one 32-column block -> their three balanced base-254 digits, one
-// packed word per digit plane: x ~ (amax / 127) (d0 + d1 / 254 + d2 / 254^2).  Adding
-// 1.5 * 2^23 rounds to the nearest integer and leaves it, as two's complement, in the low
-// mantissa byte; with |v| <= amax every digit lies in [-127, 127] without a clamp.  (Values
-// that are not finite give arbitrary digits: the product is meaningless for them anyway.)
-__device__ __forceinline__ void split_quad(const float (&v)[4], float inv, uint32_t &w0, uint32_t &w1,
-                                           uint32_t &w2) {
-  constexpr float MAGIC = 12582912.f;
-  uint32_t b0[4], b1[4], b2[4];
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const float t0 = fmaf(v[i], inv, MAGIC);
-    const float r1 = fmaf(v[i], inv, -(t0 - MAGIC));  // exact residual of the first digit
-    const float t1 = fmaf(r1, 254.f, MAGIC);
-    const float r2 = fmaf(r1, 254.f, -(t1 - MAGIC));
-    const float t2 = fmaf(r2, 254.f, MAGIC);
-    b0[i] = __float_as_uint(t0), b1[i] = __float_as_uint(t1), b2[i] = __float_as_uint(t2);
-  }
-  w0 = __byte_perm(__byte_perm(b0[0], b0[1], 0x0040), __byte_perm(b0[2], b0[3], 0x0040), 0x5410);
-  w1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
-  w2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
-}
-
-// Activations e0 .. e0 + 3 of one row out of the tagged slots of a gathered buffer (columns
-// past `cols` read as zero); false if a slot's tag did not arrive within the wait's bound.
-__device__ __forceinline__ bool load_quad_slots(const unsigned long long *row, unsigned want, uint32_t e0,
-                                                uint32_t cols, float (&v)[4]) {
-  if (e0 + 4 <= cols) return qkpeer::slot_wait4(row + e0, want, v);
-  bool ok = true;
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    v[i] = 0.f;
-    if (e0 + i < cols) ok &= qkpeer::slot_wait(row + e0 + i, want, v[i]);
-  }
-  return ok;
-}
-
-// ---------------------------------------------------------------- x image
-// [M][3 digit planes of PS bytes, natural column order][M][Kp/32] float2 (sx, Sx)
-__global__ void __launch_bounds__(256)
-    qk_xsplit_kernel(const float *__restrict__ x, uint32_t m_rows, uint32_t cols, uint32_t Kp,
-                     uint32_t PS, uint32_t xs_off, unsigned char *__restrict__ img,
-                     const unsigned long long *wait_slots, const unsigned *wait_epoch, uint64_t wait_ld,
-                     unsigned *status) {
-  pdl_launch_dependents();
-  pdl_wait();  // x may be the previous kernel's output; the image may still be in use by it
-  const uint32_t quads = Kp / 4, total = m_rows * quads;
-  const uint32_t it = blockIdx.x * 256 + threadIdx.x;
-  if (it >= total) return;  // warp-uniform: total is a multiple of 64
-  const uint32_t m = it / quads, e0 = (it % quads) * 4;
-  float v[4];
-  if (wait_slots) {  // x is gathered from other GPUs: read it from the tagged slots as it arrives
-    if (!load_quad_slots(wait_slots + (uint64_t)m * wait_ld, *wait_epoch, e0, cols, v)) atomicOr(status, QK_DEV_TIMEOUT);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; i++) v[i] = (e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
-  }
-  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-  float s4 = (v[0] + v[1]) + (v[2] + v[3]);
-#pragma unroll
-  for (int o = 1; o < 8; o <<= 1) {  // the 8 threads of one 32-column block
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    s4 += __shfl_xor_sync(0xffffffffu, s4, o);
-  }
-  if (!(amax < 8.0e37f)) amax = 8.0e37f;  // inf/nan/huge x: keep the scale finite (__fdividef: y < 2^126)
-  const float inv = amax > 0.f ? __fdividef(127.f, amax) : 0.f;
-  uint32_t w0, w1, w2;
-  split_quad(v, inv, w0, w1, w2);
-  unsigned char *p = img + (size_t)m * 3 * PS + e0;
-  *reinterpret_cast<uint32_t *>(p) = w0;
-  *reinterpret_cast<uint32_t *>(p + PS) = w1;
-  *reinterpret_cast<uint32_t *>(p + 2 * PS) = w2;
-  if ((threadIdx.x & 7) == 0)
-    *reinterpret_cast<float2 *>(img + xs_off + ((size_t)m * (Kp / 32) + e0 / 32) * 8) =
-        make_float2(amax * (1.f / 127.f), s4);
-}
-
-// ---------------------------------------------------------------- main kernel
-// The same split as qk_xsplit_kernel, done by the compute warps straight into the
-// CTA's shared-memory x image (used when x is small enough that every CTA
-// redoing it is cheaper than a second kernel and a copy).
-template <int M, int CW, bool PEER>
-__device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32_t Kp,
-                              unsigned char *img, uint32_t PS, uint32_t xs_off, bool tell_producer,
-                              const QkPeers &peers, unsigned *status) {
-  constexpr int CT = CW * 32;  // compute threads
-  const uint32_t quads = Kp / 4, total = (uint32_t)M * quads;
-  // Every CTA of the grid reads the same few KB of x at the same moment: each starts at
-  // a different 32-column block (whole blocks, so the 8 threads of a block stay together)
-  // to spread the requests over the L2 slices, and loads 16 bytes at a time when it can.
-  const uint32_t rot = (blockIdx.x * 40u) % total;  // a multiple of 8 quads
-  const bool vec = (cols & 3u) == 0 && ((uintptr_t)x & 15u) == 0;
-  const bool from_slots = PEER && peers.wait_slots != nullptr;
-  const unsigned want = from_slots ? *peers.wait_epoch : 0u;
-  bool arrived = true;  // false once a slot has failed to arrive in time: this thread waits no more
-  constexpr int U = (M * 4096 / 4 + CT - 1) / CT < 4 ? (M * 4096 / 4 + CT - 1) / CT : 4;  // quads in flight per thread
-  for (uint32_t base = 0; base < total; base += CT * U) {
-    float v[U][4];
-    uint32_t qidx[U];
-#pragma unroll
-    for (int j = 0; j < U; j++) {
-      const uint32_t it0 = base + j * CT + threadIdx.x;
-      uint32_t it = it0 + rot;
-      if (it >= total) it -= total;
-      qidx[j] = it0 < total ? it : 0xFFFFFFFFu;
-      const uint32_t m = M == 1 ? 0u : it / quads, e0 = (M == 1 ? it : it % quads) * 4;
-      if (from_slots) {  // gathered activations: straight from the tagged slots, as they arrive
-        v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.f;
-        if (it0 < total && arrived &&
-            !load_quad_slots(peers.wait_slots + (uint64_t)m * peers.wait_ld, want, e0, cols, v[j])) {
-          arrived = false;
-          atomicOr(status, QK_DEV_TIMEOUT);
-        }
-      } else if (it0 < total && vec && e0 + 4 <= cols) {
-        const float4 q = __ldg(reinterpret_cast<const float4 *>(x + (uint64_t)m * cols + e0));
-        v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-          v[j][i] = (it0 < total && e0 + i < cols) ? __ldg(x + (uint64_t)m * cols + e0 + i) : 0.f;
-      }
-    }
-    // This thread's first activation loads are on their way: the producer may send the rest
-    // of the ring behind them.
-    if (tell_producer && base == 0) asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
-#pragma unroll
-    for (int j = 0; j < U; j++) {
-      const uint32_t it = qidx[j];
-      if (it == 0xFFFFFFFFu) continue;  // warp-uniform: total and CT are multiples of 32
-      const uint32_t m = M == 1 ? 0u : it / quads, e0 = (M == 1 ? it : it % quads) * 4;
-      float amax = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fmaxf(fabsf(v[j][2]), fabsf(v[j][3])));
-      float s4 = (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        s4 += __shfl_xor_sync(0xffffffffu, s4, o);
-      }
-      if (!(amax < 8.0e37f)) amax = 8.0e37f;
-      QK_STAMP(threadIdx.x == 0 && j == 0 && amax >= 0.f, 122);
-      const float inv = amax > 0.f ? __fdividef(127.f, amax) : 0.f;
-      uint32_t w0, w1, w2;
-      split_quad(v[j], inv, w0, w1, w2);
-      unsigned char *p = img + (size_t)m * 3 * PS + e0;
-      *reinterpret_cast<uint32_t *>(p) = w0;
-      *reinterpret_cast<uint32_t *>(p + PS) = w1;
-      *reinterpret_cast<uint32_t *>(p + 2 * PS) = w2;
-      if ((threadIdx.x & 7) == 0)
-        *reinterpret_cast<float2 *>(img + xs_off + ((size_t)m * (Kp / 32) + e0 / 32) * 8) =
-            make_float2(amax * (1.f / 127.f), s4);
-    }
-  }
-}
-
-// One super-block column of a tile as a compute warp holds it in registers:
-// row g's 16-byte header, the lane's 8 bytes of each of the four 32-byte groups,
-// and per activation row the (sx, Sx) pairs and digit fragments that meet them.
-template <int M>
-struct SbData {
-  uint4 h;
-  uint2 w[4];
-  float4 xs[M];
-  uint2 b[M][4];
-};
-
-// PEER: the variant that can store its results into every rank's tagged slots and read
-// gathered activations out of slots (kept out of the single-GPU variant, whose speed is
-// sensitive to its code size).
-template <int M, bool INCTA, int CW, int G, bool PEER>
-__global__ void __launch_bounds__((CW + 1) * 32, 1)
-    qk_gemv_q4k_mma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
-                           const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
-                           uint64_t ldy, unsigned *status, int nstage, int nslot,
-                           uint32_t stage_bytes, SmemMma S, uint32_t Kp, QkPeers peers, int npre) {
-  constexpr int WG = CW / G;  // warps per group; a group owns every G-th chunk
-  extern __shared__ __align__(128) unsigned char smem[];
-  const uint32_t sbase = smem_u32(smem);
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  const uint32_t my_chunks =
-      blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const uint32_t my_items = my_chunks * L.ktiles;
-
-  QK_STAMP(warp == 0, 0);
-  pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < nstage; s++) mbar_init(sbase + S.full + s * 8, 1);
-    for (int s = 0; s < nslot; s++) mbar_init(sbase + S.redfull + s * 8, WG);
-    mbar_init(sbase + S.xbar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  __syncthreads();
-
-  if (warp == CW) {
-    // ================= producer / reducer warp =================
-    // Lane 0 streams tiles; after a chunk's partials are complete the warp sums
-    // them, writes the 8 x M outputs, and only then refills the stages the chunk
-    // occupied.  Gating the refills on the reduction bounds how far the compute
-    // warps can run ahead, which is what makes the ring of `nslot` partial
-    // buffers safe without a second handshake.
-    uint32_t pc = 0, pkt = 0, pst = 0;  // chunk ordinal, k-tile and stage of the next item
-    auto issue = [&]() {                // lane 0 only
-      const uint32_t chunk = blockIdx.x + pc * gridDim.x;
-      const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
-      const uint32_t bar = sbase + S.full + pst * 8;
-      mbar_expect_tx(bar, bytes);
-      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, W + qk_tile_offset(L, chunk, pkt), bytes, bar);
-      if (++pkt == L.ktiles) pkt = 0, pc++;
-      if (++pst == (uint32_t)nstage) pst = 0;
-    };
-    uint32_t item = 0;
-    if (lane == 0) {
-      // weights are immutable: their prefetch need not wait for the previous kernel
-      for (; item < (uint32_t)npre && item < my_items; item++) issue();
-    }
-    pdl_wait();  // the x image and y belong to the previous kernel until it has finished
-    QK_STAMP(true, 120);
-    if (!INCTA && lane == 0) {
-      mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
-      bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
-    }
-    // Sharded output: this call's tag is the object's call count + 1.  Lane 0 reads the
-    // count, then counts this CTA in (the add carries a dependency on the value read, so it
-    // cannot overtake the read); the CTA that is counted in last knows that every CTA of the
-    // launch has read the count and moves it on.  The round trips run while the compute
-    // warps load the activations; nothing of this sits at the end of the kernel.
-    unsigned e_count = 0, uwant = 0;
-    if (PEER && peers.unpack_n)  // needed further down; asked for now, together with the count
-      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(uwant) : "l"(peers.unpack_epoch) : "memory");
-    if (PEER && peers.n && lane == 0) {
-      unsigned one;
-      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(e_count) : "l"(peers.epoch) : "memory");
-      asm volatile("and.b32 %0, %1, 0;\n\tadd.u32 %0, %0, 1;" : "=r"(one) : "r"(e_count));
-      if (atomicAdd(peers.counter, one) == gridDim.x - 1) {
-        *reinterpret_cast<volatile unsigned *>(peers.counter) = 0;
-        *reinterpret_cast<volatile unsigned *>(peers.epoch) = e_count + 1u;
-      }
-    }
-    if (npre < nstage) {
-      // The rest of the first ring fill goes out once the compute warps' activation loads
-      // have landed (named barrier 2), so that those loads do not queue behind a whole
-      // ring of weight tiles from every CTA: measured 11.1 -> 9.7 us per launch at 14336 x 4096.
-      if (INCTA) asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
-      if (lane == 0)
-        for (; item < (uint32_t)nstage && item < my_items; item++) issue();
-    }
-    const unsigned tag = (PEER && peers.n) ? __shfl_sync(0xffffffffu, e_count, 0) + 1u : 0u;
-    // this lane's two destination ranks (lane / 8 and lane / 8 + 4), held in registers: an
-    // indexed read of the kernel parameters per chunk costs a constant-cache miss each time
-    unsigned long long *slots_a = nullptr, *slots_b = nullptr;
-    if (PEER && peers.n) {
-      const uint32_t q = lane >> 3;
-#pragma unroll
-      for (uint32_t p = 0; p < QK_MAX_PEERS; p++) {
-        if (p == q && p < peers.n) slots_a = peers.slots[p];
-        if (p == q + 4 && p < peers.n) slots_b = peers.slots[p];
-      }
-    }
-    if (PEER && peers.unpack_n) {
-      // In passing: the previous sharded call's gathered result goes from its slots into its
-      // plain buffer.  The producer warps of all CTAs share the slots, eight loads in flight
-      // per lane; this warp has nothing else to do until the first chunk is reduced.
-      const uint64_t stride = (uint64_t)gridDim.x * 32;
-      bool arrived = true;
-      for (uint64_t base = (uint64_t)blockIdx.x * 32 + lane; base < peers.unpack_n; base += 8 * stride) {
-        unsigned long long w[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const uint64_t i = base + j * stride;
-          w[j] = i < peers.unpack_n ? qkpeer::slot_load(peers.unpack_slots + i) : 0ull;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const uint64_t i = base + j * stride;
-          if (i >= peers.unpack_n) break;
-          float v = __uint_as_float((unsigned)w[j]);
-          if ((unsigned)(w[j] >> 32) != uwant) {  // not there yet: the bounded wait
-            if (arrived && !qkpeer::slot_wait(peers.unpack_slots + i, uwant, v)) {
-              arrived = false;
-              atomicOr(status, QK_DEV_TIMEOUT);
-            }
-            if (!arrived) v = 0.f;
-          }
-          peers.unpack_out[i] = v;
-        }
-      }
-    }
-    uint32_t slot = 0, sph = 0;
-    for (uint32_t c = 0; c < my_chunks; c++) {
-      if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, sph)) {
-        if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
-        break;
-      }
-      // Every warp of the owning group released the chunk's stages before it posted its
-      // partials: refill them first, the sums and stores below follow the copies out.  (The
-      // partial-sum ring is one slot deeper than the stage ring, so a group that runs ahead
-      // through the refilled stages cannot reach the slot that is being read here.)
-      if (lane == 0)
-        for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
-      const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (WG * M * 8);
-      float v = 0.f;
-      if (lane < 8 * M) {
-        const uint32_t m = lane >> 3, r = lane & 7u;
-#pragma unroll
-        for (int wv = 0; wv < WG; wv++) v += red[(wv * M + m) * 8 + r];
-        const uint32_t row = (blockIdx.x + c * gridDim.x) * 8 + r;
-        if (!(PEER && peers.n) && row < L.rows) y[(uint64_t)m * ldy + row] = v;
-      }
-      if (PEER && peers.n) {
-        // The same (value, tag) word into the slot of every rank: lane (q, r) stores row r
-        // to ranks q, q + 4 (eight consecutive slots = 64 bytes per rank and activation row).
-        const uint32_t r = lane & 7u, row = (blockIdx.x + c * gridDim.x) * 8 + r;
-#pragma unroll
-        for (int m = 0; m < M; m++) {
-          const float vm = __shfl_sync(0xffffffffu, v, m * 8 + (int)r);
-          if (row < L.rows) {
-            if (slots_a) qkpeer::slot_store(slots_a + (uint64_t)m * ldy + row, vm, tag);
-            if (slots_b) qkpeer::slot_store(slots_b + (uint64_t)m * ldy + row, vm, tag);
-          }
-        }
-      }
-      __syncwarp();
-      QK_STAMP(c < 30, 64 + c);
-      if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
-    }
-    return;
-  }
-
-  // ================= compute warps =================
-  const uint32_t group = warp / WG, wl = warp % WG;
-  const uint32_t g = lane >> 2, tig = lane & 3;
-  // lane (g, tig) owns digit j = tig of both sub-blocks of a group (see the header
-  // comment); tig == 3 holds the two unused columns: weight 0.  The x16 of the
-  // high-nibble dot is folded into the sub-block scale.
-  const float kD = tig == 0 ? 1.f : tig == 1 ? 1.f / 254.f : tig == 2 ? 1.f / (254.f * 254.f) : 0.f;
-  // B column g of this lane: digit g / 2 of sub-block 2p (g even) or 2p + 1 (g odd);
-  // columns 6 and 7 are never used, so they may hold anything (digit plane 2 again)
-  const uint32_t b_off = (g < 6 ? (g >> 1) : 2u) * S.PS + (g & 1u) * 32u + tig * 8;
-  // header decode constants of this lane (it unpacks sub-blocks 2 tig and 2 tig + 1)
-  const bool hi_half = tig >= 2;
-  const uint32_t m1 = hi_half ? 0x0F0F0F0Fu : 0x3F3F3F3Fu, m2 = hi_half ? 0x30303030u : 0u;
-  const uint32_t sel0 = 0x7540u | (2u * (tig & 1u)), sel1 = sel0 + 1u;
-
-  pdl_wait();  // x may be the previous kernel's output; y may be read or written by it
-  QK_STAMP(warp == 0, 121);
-  bool dead = false;
-  if (INCTA) {
-    xsplit_in_cta<M, CW, PEER>(x, L.cols, Kp, smem + S.ximg, S.PS, S.xs_off, npre < nstage, peers, status);
-    QK_STAMP(warp == 0, 123);
-    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");  // compute warps only
-  } else if (!mbar_wait_bounded(sbase + S.xbar, 0)) {
-    dead = true;
-  }
-  float accA[M], accB[M], mt[M];
-#pragma unroll
-  for (int m = 0; m < M; m++) accA[m] = accB[m] = mt[m] = 0.f;
-
-  // Every shared-memory load of one super-block column, issued together.  Column J of this
-  // warp is super-block wl + J * WG of the tile; the four bases are per tile, the rest of
-  // each address is a compile-time offset.
-  struct TileBase {
-    uint32_t h, q, x, xs;
-  };
-  // lane constants: header of row g, the lane's 8 nibble bytes, its digit fragment and scales
-  const uint32_t hl = wl * 1152 + g * 16, ql = wl * 1152 + 128 + g * 32 + tig * 8;
-  const uint32_t xl = sbase + S.ximg + b_off + wl * 256;
-  const uint32_t xsl = sbase + S.ximg + S.xs_off + (wl * 8 + 2 * tig) * 8;
-  const uint32_t xm = 3 * S.PS, xsm = (Kp / 32) * 8;  // per activation row
-  auto load_sb = [&](SbData<M> &D, const TileBase &B, auto jt) {
-    constexpr int J = decltype(jt)::value;
-    // block-major tile: super-block column sb = 1152 bytes, 8 headers then 4 x 8 x 32 nibbles
-    D.h = lds128o<J * WG * 1152>(B.h);
-    static_for<0, 4>([&](auto gq) {
-      D.w[decltype(gq)::value] = lds64o<J * WG * 1152 + decltype(gq)::value * 256>(B.q);
-    });
-#pragma unroll
-    for (int m = 0; m < M; m++) {
-      D.xs[m] = lds128fo<J * WG * 64>(B.xs + m * xsm);
-      const uint32_t xb = B.x + m * xm;
-      static_for<0, 4>([&](auto gq) {
-        D.b[m][decltype(gq)::value] = lds64o<J * WG * 256 + decltype(gq)::value * 64>(xb);
-      });
-    }
-  };
-  auto compute_sb = [&](const SbData<M> &D) {
-    // this lane decodes sub-blocks (2 tig, 2 tig + 1) of row g's header:
-    // reference/q4_k.rs:27-49 on four 6-bit fields at a time, then byte -> f32 by
-    // dropping the byte into the mantissa of 2^23
-    const uint4 h = D.h;
-    const float d = h2f_bits(h.x), dmin = h2f_bits(h.x >> 16);
-    const uint32_t scw = ((hi_half ? h.w : h.y) & m1) | ((h.y >> 2) & m2);
-    const uint32_t mnw = ((hi_half ? (h.w >> 4) : h.z) & m1) | ((h.z >> 2) & m2);
-    const float ds0 = d * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel0)) - 8388608.f);
-    const float ds1 =
-        d * (1.f / 16.f) * (__int_as_float(__byte_perm(scw, 0x4B000000u, sel1)) - 8388608.f);
-    const float dm0 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel0)) - 8388608.f);
-    const float dm1 = dmin * (__int_as_float(__byte_perm(mnw, 0x4B000000u, sel1)) - 8388608.f);
-#pragma unroll
-    for (int m = 0; m < M; m++) {
-      const float tx = ds0 * D.xs[m].x, ty = ds1 * D.xs[m].z;
-      mt[m] = fmaf(dm0, D.xs[m].y, mt[m]);
-      mt[m] = fmaf(dm1, D.xs[m].w, mt[m]);
-      // four MMAs back to back (one per 32-byte group), then their scaling
-      int c[4][4];
-#pragma unroll
-      for (int gq = 0; gq < 4; gq++)
-        mma_u8s8(c[gq], D.w[gq].x & 0x0F0F0F0Fu, D.w[gq].x, D.w[gq].y & 0x0F0F0F0Fu, D.w[gq].y,
-                 D.b[m][gq].x, D.b[m][gq].y);
-#pragma unroll
-      for (int gq = 0; gq < 4; gq++) {
-        // lane gq of this lane's group of four (width 4: the source lane is an immediate)
-        const float sx = __shfl_sync(0xffffffffu, tx, gq, 4);
-        const float sy = __shfl_sync(0xffffffffu, ty, gq, 4);
-        accA[m] = fmaf(sx, __int2float_rn(c[gq][0]), accA[m]);
-        accB[m] = fmaf(sy, __int2float_rn(c[gq][3] - c[gq][1]), accB[m]);
-      }
-    }
-  };
-
-  QK_STAMP(warp == 0, 1);
-  // loop state kept as counters: no integer division on the critical path
-  uint32_t st = 0, fph = 0, slot = 0;
-  auto advance_stage = [&](uint32_t n) {
-    st += n;
-    while (st >= (uint32_t)nstage) st -= nstage, fph ^= 1;
-  };
-  advance_stage(group * L.ktiles);
-  slot = group % nslot;
-  uint32_t tstamp = 0;
-  for (uint32_t c = group; c < my_chunks && !dead; c += G) {
-    for (uint32_t kt = 0; kt < L.ktiles; kt++) {
-      const uint32_t nbt = qk_tile_nb(L, kt);
-      const uint32_t tile = sbase + S.stage + st * stage_bytes;
-      if (!mbar_wait_bounded(sbase + S.full + st * 8, fph)) {
-        dead = true;
-        break;
-      }
-      QK_STAMP(warp == 0 && tstamp < 30, 2 + 2 * tstamp);
-      // software pipeline over this warp's columns (fully unrolled, two register
-      // buffers): the next column's loads are in flight while the current one is
-      // decoded, multiplied and scaled.  A full tile (all but the last k-tile of a K that
-      // is not a multiple of the tile width) runs without the per-column bound checks.
-      const TileBase B = {tile + hl, tile + ql, xl + kt * (QK_TILE_ELEMS / 32) * 32,
-                          xsl + kt * (QK_TILE_ELEMS / 32) * 8};
-      auto tile_body = [&](auto full_tag) {
-        constexpr bool FULL = decltype(full_tag)::value;
-        constexpr int NSB = NBT / WG;  // columns of a full tile per warp
-        SbData<M> d0, d1;
-        if (FULL || wl < nbt) load_sb(d0, B, std::integral_constant<int, 0>{});
-        static_for<0, (NSB + 1) / 2>([&](auto pt) {
-          constexpr int J = 2 * decltype(pt)::value;
-          const uint32_t sb0 = wl + J * WG, sb1 = sb0 + WG, sb2 = sb1 + WG;
-          if constexpr (J + 1 < NSB)
-            if (FULL || sb1 < nbt) load_sb(d1, B, std::integral_constant<int, J + 1>{});
-          if (FULL || sb0 < nbt) compute_sb(d0);
-          if constexpr (J + 2 < NSB)
-            if (FULL || sb2 < nbt) load_sb(d0, B, std::integral_constant<int, J + 2>{});
-          if constexpr (J + 1 < NSB)
-            if (FULL || sb1 < nbt) compute_sb(d1);
-        });
-      };
-      if (nbt == NBT)
-        tile_body(std::true_type{});
-      else
-        tile_body(std::false_type{});
-      QK_STAMP(warp == 0 && tstamp < 30, 3 + 2 * tstamp);
-      tstamp++;
-      advance_stage(1);
-    }
-    if (dead) break;
-    // chunk finished: leave the row partials for the reducer
-    float *red = reinterpret_cast<float *>(smem + S.red) + slot * (WG * M * 8);
-#pragma unroll
-    for (int m = 0; m < M; m++) {
-      float v = kD * (accA[m] + accB[m]) - mt[m];
-      v += __shfl_xor_sync(0xffffffffu, v, 1);
-      v += __shfl_xor_sync(0xffffffffu, v, 2);
-      if (tig == 0) red[(wl * M + m) * 8 + g] = v;
-      accA[m] = accB[m] = mt[m] = 0.f;
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(sbase + S.redfull + slot * 8);
-    slot += G;
-    while (slot >= (uint32_t)nslot) slot -= nslot;
-    advance_stage((G - 1) * L.ktiles);
-  }
-  if (dead) atomicOr(status, QK_DEV_TIMEOUT);  // a bounded wait ran out: results are invalid
-  QK_STAMP(warp == 0, 100);
-}
-
-struct PlanMma {
-  SmemMma S;
-  uint32_t Kp, stage_bytes, total;
-  int nstage, nslot, groups, cw;
-};
-
-// Compute warps per CTA (+ one producer / reducer warp).  With 16 the register budget is 96
-// per thread and the column pipeline spills; 8 warps (up to 255 registers) stream as fast or
-// faster at every M (14336 x 4096, M = 1: 8.2 us against 8.8 us).  12 warps in three groups
-// (128 registers) start and finish sooner when a CTA has few chunks: 3.3 against 3.8 us at
-// 1024 rows, 4.6 against 4.7 us at 4096, level from 14336 rows on.  QK_CW overrides
-// (developer knob: 8, 12 or 16).
-int compute_warps(const QkLayout &L, uint32_t m) {
-  static int cw_env = -1;
-  if (cw_env < 0) {
-    const char *e = qk_knob("QK_CW");
-    const int v = e ? atoi(e) : 0;
-    cw_env = (v == 8 || v == 12 || v == 16) ? v : 0;
-  }
-  if (m >= 2) return cw_env == 16 ? 16 : 8;  // the 12-warp kernel is built for M = 1 only
-  if (cw_env) return cw_env;
-  return (L.ktiles == 1 && L.chunks <= 1024) ? 12 : 8;
-}
-
-// force_cw8: always the 8-warp kernel (the route that takes its split activations from a
-// caller-provided image is built for 8 warps only).
-bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P, bool force_cw8 = false) {
-  if (L.nb == 0 || L.chunks == 0) return false;  // nothing to stream: the callers handle empty shapes
-  uint32_t Kp = L.nb * 256u;
-  uint32_t nbt_max = L.nb < L.nbt ? L.nb : L.nbt;
-  uint32_t stage_bytes = QK_TILE_ROWS * nbt_max * L.bb;
-  stage_bytes = (stage_bytes + 127u) & ~127u;
-  SmemMma S;
-  uint32_t off = 0;
-  S.full = off, off += MAX_STAGE * 8;
-  S.redfull = off, off += MAX_SLOT * 8;
-  S.xbar = off, off += 8;
-  off = (off + 127u) & ~127u;
-  S.red = off, off += MAX_SLOT * MAX_CW * m * 8 * 4;
-  off = (off + 127u) & ~127u;
-  S.PS = Kp + 64;
-  S.xs_off = m * 3 * S.PS;
-  S.ximg_bytes = S.xs_off + m * (Kp / 32) * 8;  // multiple of 16: PS and Kp/32*8 both are
-  S.ximg = off, off += S.ximg_bytes;
-  off = (off + 127u) & ~127u;
-  S.stage = off;
-  const uint32_t budget = 227u * 1024u - 1024u;
-  if (off + 2 * stage_bytes > budget) return false;
-  int nstage = (int)((budget - off) / stage_bytes);
-  if (nstage > MAX_STAGE) nstage = MAX_STAGE;
-  if (const char *e = qk_knob("QK_NSTAGE")) {  // developer knob: shallower ring
-    int v = atoi(e);
-    if (v >= 2 && v < nstage) nstage = v;
-  }
-  // a chunk's stages are refilled only once the whole chunk is reduced: its k-tiles
-  // must all fit in the ring with room to prefetch the next chunk
-  if ((uint32_t)nstage < L.ktiles + 1) return false;
-  // largest group count whose G * ktiles divides a ring depth we can afford
-  int groups = 1;
-  const char *ge = qk_knob("QK_GROUPS");
-  const int gmax = ge ? atoi(ge) : 4;
-  int cw = force_cw8 ? 8 : compute_warps(L, m);
-  if (cw == 12) {  // three groups of four warps, if the ring can hold three chunks
-    const int unit = 3 * (int)L.ktiles;
-    if (nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1)
-      groups = 3, nstage = (nstage / unit) * unit;
-    else
-      cw = 8;
-  }
-  for (int gtry = 4; gtry >= 2 && cw != 12; gtry >>= 1) {
-    const int unit = gtry * (int)L.ktiles;
-    if (gtry <= gmax && nstage / unit >= 1 && (nstage / unit) * unit >= (int)L.ktiles + 1) {
-      groups = gtry;
-      nstage = (nstage / unit) * unit;
-      break;
-    }
-  }
-  P->S = S, P->Kp = Kp, P->stage_bytes = stage_bytes, P->nstage = nstage, P->nslot = nstage + 1, P->groups = groups, P->cw = cw;
-  P->total = off + nstage * stage_bytes;
-  return true;
-}
-
-template <int M, bool INCTA, int CW, int G, bool PEER = false>
-cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
-                       unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
-                       cudaStream_t s, const QkPeers *peers = nullptr) {
-  auto kern = qk_gemv_q4k_mma_kernel<M, INCTA, CW, G, PEER>;
-  static QkPerDevice attr_set;
-  if (attr_set.first()) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return attr_set.reset(), e;
-  }
-  static int use_pdl = -1;
-  if (use_pdl < 0) {
-    const char *e = qk_knob("QK_PDL");
-    use_pdl = (e && e[0] == '0') ? 0 : 1;
-  }
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-
-  if (!INCTA) {
-    const uint32_t quads = (uint32_t)M * P.Kp / 4;
-    cudaLaunchConfig_t c0 = {};
-    c0.gridDim = dim3((quads + 255) / 256), c0.blockDim = dim3(256), c0.stream = s;
-    c0.attrs = at, c0.numAttrs = use_pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&c0, qk_xsplit_kernel, x, (uint32_t)M, L.cols, P.Kp,
-                                       P.S.PS, P.S.xs_off, ximg, peers ? peers->wait_slots : nullptr,
-                                       peers ? peers->wait_epoch : nullptr, peers ? peers->wait_ld : (uint64_t)0, status);
-    if (e != cudaSuccess) return e;
-  }
-  static int ctas = -1;  // developer knob: persistent CTAs per SM (they must fit: see QK_CW, QK_NSTAGE)
-  if (ctas < 0) {
-    const char *e = qk_knob("QK_CTAS");
-    ctas = (e && atoi(e) == 2) ? 2 : 1;
-  }
-  uint32_t grid = (uint32_t)sm_count * (uint32_t)ctas;  // persistent
-  if (grid > L.chunks) grid = L.chunks;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1) * 32), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
-  cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
-  QkPeers pv = {};
-  if (peers) pv = *peers;
-  // Weight tiles issued before the wait on the previous kernel; the rest of the ring follows
-  // the activation loads.  Measured at 14336 x 4096, M = 1, 8 warps: 1 tile 8.2 us, 2 8.3,
-  // 3 8.6, 4 8.8, 6 9.2; M = 2: 2 tiles 13.1 us, 3 12.9, 4 12.7.  QK_PRE overrides
-  // (developer knob).
-  static int npre_env = -1;
-  if (npre_env < 0) {
-    const char *e = qk_knob("QK_PRE");
-    npre_env = e ? atoi(e) : 0;
-  }
-  int npre = npre_env > 0 ? npre_env : (M == 1 ? (CW == 12 ? 2 : 1) : (M == 2 ? 4 : 3));
-  if (npre > P.nstage) npre = P.nstage;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, x, (const unsigned char *)ximg, y, ldy, status,
-                            P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv, npre);
-}
-
-// Every CTA redoing the split costs ~M*K/512 quads per thread; past this size the
-// separate split kernel plus one bulk copy of its image is cheaper.
-bool split_in_cta(const PlanMma &P, uint32_t m) {
-  static int force = -2;
-  if (force == -2) {
-    const char *e = qk_knob("QK_XSPLIT");
-    force = e ? atoi(e) : -1;  // 0: always the split kernel, 1: always in-CTA
-  }
-  if (force >= 0) return force == 1;
-  return m * P.Kp <= 8192;
-}
-
-template <int M>
-cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, float *y,
-                         uint64_t ldy, unsigned *status, unsigned char *ximg, int sm_count,
-                         const PlanMma &P, cudaStream_t s, const QkPeers *peers) {
-  // Warp groups: a group owns every G-th chunk.  A stage must always be consumed by
-  // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
-  // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
-  const int cw = P.cw;
-  const bool peer = peers != nullptr;
-#define QK_LAUNCH1(CWV, GV, PV)                                                                       \
-  return split_in_cta(P, M)                                                                           \
-             ? launch_mma<M, true, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
-             : launch_mma<M, false, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers)
-#define QK_LAUNCH(CWV, GV)          \
-  do {                              \
-    if (peer) {                     \
-      QK_LAUNCH1(CWV, GV, true);    \
-    } else {                        \
-      QK_LAUNCH1(CWV, GV, false);   \
-    }                               \
-  } while (0)
-  if constexpr (M == 1)
-    if (cw == 12) QK_LAUNCH(12, 3);
-#ifdef QK_DEV_KNOBS  // the 16-warp variants exist for experiments only (QK_CW=16)
-  if (cw == 16) {
-    switch (P.groups) {
-      case 4:
-        QK_LAUNCH(16, 4);
-      case 2:
-        QK_LAUNCH(16, 2);
-      default:
-        QK_LAUNCH(16, 1);
-    }
-  }
-#endif
-  switch (P.groups) {
-    case 4:
-      QK_LAUNCH(8, 4);
-    case 2:
-      QK_LAUNCH(8, 2);
-    default:
-      QK_LAUNCH(8, 1);
-  }
-#undef QK_LAUNCH1
-#undef QK_LAUNCH
-}
-
-}  // namespace
 
 bool qk_gemv_mma_supported(const QkLayout &L, uint32_t m) {
-  if (L.type != QK_T_Q4_K || m < 1 || m > 4) return false;
-  PlanMma P;
-  return make_plan_mma(L, m, &P);
+  return L.type == QK_T_Q4_K && supported<DecQ4K>(L, m);
 }
 
-size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m) {
-  PlanMma P;
-  return make_plan_mma(L, m, &P) ? P.S.ximg_bytes : 0;
-}
+size_t qk_gemv_mma_scratch_bytes(const QkLayout &L, uint32_t m) { return scratch_bytes<DecQ4K>(L, m); }
 
 cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                                int sm_count, cudaStream_t s, const QkPeers *peers) {
-  PlanMma P;
-  if (!make_plan_mma(L, m, &P)) return cudaErrorInvalidConfiguration;
-  switch (m) {
-    case 1:
-      return launch_mma_m<1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
-    case 2:
-      return launch_mma_m<2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
-    case 3:
-      return launch_mma_m<3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
-    default:
-      return launch_mma_m<4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
-  }
+  return launch<DecQ4K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, peers);
 }
 
 // Same matvec, always through qk_xsplit_kernel + the x image in `scratch` (never the
@@ -860,15 +30,15 @@ cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, co
                                      float *y, uint32_t m, uint64_t ldy, unsigned *status,
                                      unsigned char *scratch, int sm_count, cudaStream_t s) {
   PlanMma P;
-  if (!make_plan_mma(L, m, &P, true)) return cudaErrorInvalidConfiguration;
-#define QK_SPLIT(MV)                                                                             \
-  switch (P.groups) {                                                                            \
-    case 4:                                                                                      \
-      return launch_mma<MV, false, 8, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
-    case 2:                                                                                      \
-      return launch_mma<MV, false, 8, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
-    default:                                                                                     \
-      return launch_mma<MV, false, 8, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s); \
+  if (!make_plan_mma(L, m, &P, DecQ4K::XSB, true)) return cudaErrorInvalidConfiguration;
+#define QK_SPLIT(MV)                                                                                       \
+  switch (P.groups) {                                                                                      \
+    case 4:                                                                                                \
+      return launch_mma<DecQ4K, MV, false, 8, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);   \
+    case 2:                                                                                                \
+      return launch_mma<DecQ4K, MV, false, 8, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);   \
+    default:                                                                                               \
+      return launch_mma<DecQ4K, MV, false, 8, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s);   \
   }
   switch (m) {
     case 1:

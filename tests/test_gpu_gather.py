@@ -54,10 +54,10 @@ def test_gathered_result_equals_single_gpu_and_oracle(world, t, m):
         torch.cuda.synchronize()
         for r in range(world):
             got = ranks[r].buffer[:m]
-            if m <= 4 and t != S.IQ4_XS:   # decode kernels: the shard computes each row exactly as the whole matrix does
+            if m <= 4:   # decode kernels: the shard computes each row exactly as the whole matrix does
                 assert torch.equal(got, y1 * f), (r, call)
             err = np.abs(got.cpu().numpy() - ref * f).max() / np.abs(ref).max() / f
-            assert err <= (1e-3 if (m > 4 or t == S.IQ4_XS) else 2e-5), err
+            assert err <= (1e-3 if m > 4 else 2e-5), err
     check_device_status()
     for g in ranks:
         g.free()
