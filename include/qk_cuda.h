@@ -12,7 +12,7 @@
  *  - The caller owns every buffer; the library keeps only what it allocated
  *    itself (contexts, uploaded weights, its own scratch).
  *  - `type` is the GGUF tensor type id (crates/oxillama-gguf/src/types.rs:70-125):
- *    Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q6_K = 14, IQ4_XS = 23.
+ *    Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_XS = 23.
  *  - A weight matrix is [n_rows = out_features][n_cols = in_features], stored as
  *    n_rows consecutive rows of ceil(n_cols / block_size) blocks in GGUF byte
  *    layout (reference/q4_k.rs:110-131).  A partial last block is legal; the
@@ -51,6 +51,7 @@ typedef enum qk_status {
 #define QK_TYPE_Q4_0 2
 #define QK_TYPE_Q8_0 8
 #define QK_TYPE_Q4_K 12
+#define QK_TYPE_Q5_K 13 /* generic kernels only so far: exact, not tuned */
 #define QK_TYPE_Q6_K 14
 #define QK_TYPE_IQ4_XS 23
 
@@ -66,7 +67,7 @@ int qk_last_error(qk_ctx *ctx, char *buf, size_t buf_len);
 /* ---- trait getters: QuantKernel::{block_size, block_bytes, name} (traits.rs:175-182) ---- */
 size_t qk_block_size(int type);   /* 0 for an unsupported type */
 size_t qk_block_bytes(int type);  /* 0 for an unsupported type */
-const char *qk_name(int type);    /* "Q4_0", "Q8_0", "Q4_K", "Q6_K", "IQ4_XS", or NULL */
+const char *qk_name(int type);    /* "Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "IQ4_XS", or NULL */
 
 /* ================= host-pointer entry points (the trait methods) ================= */
 
@@ -106,6 +107,26 @@ int qk_matvec_q8_fused(qk_ctx *ctx, int type, const uint8_t *w, size_t w_len,
  * n must be a multiple of 32 (else QK_DIMENSION_MISMATCH); out needs n/32*34 bytes. */
 int qk_quantize_q8_0(qk_ctx *ctx, const float *x, size_t n, uint8_t *out, size_t out_len);
 
+/* ---- the reference's second operator surface: GpuKernel (crates/oxillama-gpu) ---- */
+
+/* GpuKernel::gemv(ctx, weight_bytes, input, output, rows, cols)
+ * (crates/oxillama-gpu/src/kernels/mod.rs:91-106; per type e.g. kernels/q4_k.rs:170-195):
+ * output[i] = sum_j weight[i][j] input[j], output overwritten.  Same arithmetic and element
+ * order as qk_gemv, i.e. the CPU crate's (that crate's own host-side Q4_K / Q6_K dequant
+ * orders elements differently, kernels/q4_k.rs:138-157, kernels/q6_k.rs:94-121; it is not
+ * followed).  Checks in that implementation's order: output_len < rows, input_len < cols,
+ * weight_len short: each is its GpuError::BufferSize { expected, got }, returned here as
+ * QK_BUFFER_TOO_SMALL with "Buffer size mismatch: expected E, got G" in qk_last_error;
+ * GpuError::UnsupportedType is QK_UNSUPPORTED_TYPE. */
+int qk_gpu_gemv(qk_ctx *ctx, int type, const uint8_t *weight_bytes, size_t weight_len, const float *input,
+                size_t input_len, float *output, size_t output_len, size_t rows, size_t cols);
+
+/* Batched form, Y[b][r] = sum_c A[r][c] X[b][c] (kernels/batched_gemv.rs:36-50), with A
+ * still quantised.  vectors_len must equal batch_size * cols exactly, as there. */
+int qk_gpu_gemv_batched(qk_ctx *ctx, int type, const uint8_t *weight_bytes, size_t weight_len,
+                        const float *vectors, size_t vectors_len, float *output, size_t output_len,
+                        size_t rows, size_t cols, size_t batch_size);
+
 /* The host-pointer calls above keep the device copy of a weight matrix they
  * have seen, keyed by (pointer, length, type, shape) — weights are immutable
  * after load in the reference (llama/model.rs:805-822).  Call this before
@@ -122,6 +143,29 @@ int qk_weights_free(qk_ctx *ctx, qk_weights *h);
 /* Shard shape: rows held, columns, and the algorithmic bytes of the shard
  * (rows * ceil(cols/block_size) * block_bytes). */
 int qk_weights_info(const qk_weights *h, int *type, size_t *rows, size_t *cols, size_t *bytes);
+
+/* ---- GGUF file -> device (new; stands where load_quant_linear copies tensor_data(name) into a
+ * QuantTensor, crates/oxillama-arch/src/llama/model.rs:805-822) ---- */
+typedef struct qk_gguf qk_gguf;
+/* Parses header, metadata (only general.alignment is kept) and tensor infos of a GGUF v1-v3
+ * file (crates/oxillama-gguf/src/parser.rs:34-60, 166-212); tensor data is not read.  *out is
+ * set even when parsing fails, so that qk_gguf_last_error can say why: close it either way. */
+int qk_gguf_open(const char *path, qk_gguf **out);
+int qk_gguf_close(qk_gguf *g);
+int qk_gguf_last_error(const qk_gguf *g, char *buf, size_t buf_len);
+int qk_gguf_tensor_count(const qk_gguf *g, size_t *n);
+int qk_gguf_tensor_name(const qk_gguf *g, size_t index, char *buf, size_t buf_len);
+/* type = GGUF type id; dims in file order, unused ones 1; file_offset absolute; nbytes =
+ * TensorInfo::data_size (tensor_info.rs:47-56), 0 for a type this library does not serve. */
+int qk_gguf_tensor_info(const qk_gguf *g, const char *name, int *type, size_t *n_dims, uint64_t dims[4],
+                        uint64_t *file_offset, uint64_t *nbytes);
+/* qk_weights_upload of rows [row_begin, row_end) of the named tensor, rows = dimensions[0] and
+ * columns = dimensions[1] as the reference reads them, straight from the file: the row range
+ * is one contiguous byte range, read through pinned staging buffers, never copied into
+ * pageable memory.  Unknown name: QK_INVALID_ARGUMENT; a type outside the five served:
+ * QK_UNSUPPORTED_TYPE; data past the end of the file: QK_BUFFER_TOO_SMALL. */
+int qk_weights_upload_gguf(qk_ctx *ctx, const qk_gguf *g, const char *name, size_t row_begin, size_t row_end,
+                           qk_weights **out);
 
 /* y_dev[0..rows) = W_shard x_dev.  Device pointers; enqueued on `stream`
  * (a cudaStream_t; NULL is the legacy default stream); returns without waiting. */

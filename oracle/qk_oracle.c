@@ -38,6 +38,7 @@
 #define T_Q4_K 12
 #define T_Q6_K 14
 #define T_IQ4_XS 23
+#define T_Q5_K 13
 
 #define Q8_0_BLOCK_BYTES 34
 
@@ -114,6 +115,7 @@ size_t qk_oracle_block_size(int type) {
     case T_Q8_0:
       return 32;
     case T_Q4_K:
+    case T_Q5_K:
     case T_Q6_K:
     case T_IQ4_XS:
       return 256;
@@ -130,6 +132,8 @@ size_t qk_oracle_block_bytes(int type) {
       return 34;
     case T_Q4_K:
       return 144;
+    case T_Q5_K:
+      return 176;
     case T_Q6_K:
       return 210;
     case T_IQ4_XS:
@@ -211,6 +215,38 @@ static void dq_q4_k(const uint8_t *b, float *out) {
   }
 }
 
+/* reference/q5_k.rs:53-111: d @0, dmin @2, 12 bytes of 6-bit scales / mins @4 (same packing as
+ * Q4_K, q5_k.rs:27-50), qh @16 (32 bytes: bit g of byte l is the fifth bit of the low-nibble
+ * quant of group g, bit g + 4 that of the high-nibble quant), qs @48 (128 bytes). */
+static void dq_q5_k(const uint8_t *b, float *out) {
+  float d = rd_f16(b), dmin = rd_f16(b + 2);
+  const uint8_t *qh = b + 16, *qs = b + 48;
+  uint8_t sc[8], mn[8];
+  decode_scales_mins(b + 4, sc, mn);
+  int is = 0, qo = 0, oo = 0;
+  for (int g = 0; g < 4; g++) {
+    float d1 = d * (float)sc[is];
+    float m1 = dmin * (float)mn[is];
+    float d2 = d * (float)sc[is + 1];
+    float m2 = dmin * (float)mn[is + 1];
+    for (int l = 0; l < 32; l++) {
+      uint8_t hb = (uint8_t)((qh[l] >> g) & 1);
+      float q = (float)(uint8_t)((qs[qo + l] & 0x0F) | (hb << 4));
+      float t = d1 * q;
+      out[oo + l] = t - m1;
+    }
+    for (int l = 0; l < 32; l++) {
+      uint8_t hb = (uint8_t)((qh[l] >> (g + 4)) & 1);
+      float q = (float)(uint8_t)(((qs[qo + l] >> 4) & 0x0F) | (hb << 4));
+      float t = d2 * q;
+      out[oo + 32 + l] = t - m2;
+    }
+    is += 2;
+    qo += 32;
+    oo += 64;
+  }
+}
+
 /* reference/q6_k.rs:25-75 */
 static void dq_q6_k(const uint8_t *b, float *out) {
   const uint8_t *ql = b, *qh = b + 128, *scales = b + 192;
@@ -267,6 +303,9 @@ int qk_oracle_dequant_block(int type, const uint8_t *block, size_t block_len, fl
       break;
     case T_Q4_K:
       dq_q4_k(block, out);
+      break;
+    case T_Q5_K:
+      dq_q5_k(block, out);
       break;
     case T_Q6_K:
       dq_q6_k(block, out);
@@ -388,6 +427,49 @@ int qk_oracle_dequant_matrix(int type, const uint8_t *w, size_t w_len, size_t n_
     }                                                                                          \
     return (float)sum;                                                                         \
   }                                                                                            \
+  /* reference/q5_k.rs:137-189 */                                                              \
+  static float row_q5_k##SUFFIX(const uint8_t *row, size_t bpr, size_t n_cols, const float *x) {\
+    ACC sum = 0;                                                                               \
+    for (size_t blk = 0; blk < bpr; blk++) {                                                   \
+      const uint8_t *b = row + blk * 176;                                                      \
+      float d = rd_f16(b), dmin = rd_f16(b + 2);                                               \
+      const uint8_t *qh = b + 16, *qs = b + 48;                                                \
+      uint8_t sc[8], mn[8];                                                                    \
+      decode_scales_mins(b + 4, sc, mn);                                                       \
+      int is = 0;                                                                              \
+      size_t qo = 0, wo = blk * 256;                                                           \
+      for (int g = 0; g < 4; g++) {                                                            \
+        float d1 = d * (float)sc[is], m1 = dmin * (float)mn[is];                               \
+        float d2 = d * (float)sc[is + 1], m2 = dmin * (float)mn[is + 1];                       \
+        for (int l = 0; l < 32; l++) {                                                         \
+          size_t idx = wo + (size_t)l;                                                         \
+          if (idx < n_cols) {                                                                  \
+            uint8_t hb = (uint8_t)((qh[l] >> g) & 1);                                          \
+            float q = (float)(uint8_t)((qs[qo + l] & 0x0F) | (hb << 4));                       \
+            float t = d1 * q;                                                                  \
+            float w = t - m1;                                                                  \
+            float p = w * x[idx];                                                              \
+            sum += p;                                                                          \
+          }                                                                                    \
+        }                                                                                      \
+        for (int l = 0; l < 32; l++) {                                                         \
+          size_t idx = wo + 32 + (size_t)l;                                                    \
+          if (idx < n_cols) {                                                                  \
+            uint8_t hb = (uint8_t)((qh[l] >> (g + 4)) & 1);                                    \
+            float q = (float)(uint8_t)(((qs[qo + l] >> 4) & 0x0F) | (hb << 4));                \
+            float t = d2 * q;                                                                  \
+            float w = t - m2;                                                                  \
+            float p = w * x[idx];                                                              \
+            sum += p;                                                                          \
+          }                                                                                    \
+        }                                                                                      \
+        is += 2;                                                                               \
+        qo += 32;                                                                              \
+        wo += 64;                                                                              \
+      }                                                                                        \
+    }                                                                                          \
+    return (float)sum;                                                                         \
+  }                                                                                            \
   /* reference/q6_k.rs:106-169 */                                                              \
   static float row_q6_k##SUFFIX(const uint8_t *row, size_t bpr, size_t n_cols, const float *x) { \
     ACC sum = 0;                                                                               \
@@ -483,6 +565,8 @@ static row_fn pick_row(int type, int wide) {
       return wide ? row_q8_0_f64 : row_q8_0_f32;
     case T_Q4_K:
       return wide ? row_q4_k_f64 : row_q4_k_f32;
+    case T_Q5_K:
+      return wide ? row_q5_k_f64 : row_q5_k_f32;
     case T_Q6_K:
       return wide ? row_q6_k_f64 : row_q6_k_f32;
     case T_IQ4_XS:
@@ -656,6 +740,63 @@ static float fused_row_q4_k(const uint8_t *row, size_t bpr, size_t n_cols, const
   return sum;
 }
 
+/* reference/q5_k.rs:236-347: per sub-block (da * dot - m * sum_a) * d_a, sums in f32. */
+static float fused_row_q5_k(const uint8_t *row, size_t bpr, size_t n_cols, const uint8_t *acts) {
+  float sum = 0.0f;
+  for (size_t blk = 0; blk < bpr; blk++) {
+    const uint8_t *b = row + blk * 176;
+    float d = rd_f16(b), dmin = rd_f16(b + 2);
+    uint8_t sc[8], mn[8];
+    decode_scales_mins(b + 4, sc, mn);
+    const uint8_t *qh = b + 16, *qs = b + 48;
+    size_t is = 0, qo = 0, wo = blk * 256;
+    for (int g = 0; g < 4; g++) {
+      const uint8_t *alo = acts + (blk * 8 + is) * Q8_0_BLOCK_BYTES;
+      float d_a_lo = rd_f16(alo);
+      float da_lo = d * (float)sc[is], m_lo = dmin * (float)mn[is];
+      const uint8_t *ahi = acts + (blk * 8 + is + 1) * Q8_0_BLOCK_BYTES;
+      float d_a_hi = rd_f16(ahi);
+      float da_hi = d * (float)sc[is + 1], m_hi = dmin * (float)mn[is + 1];
+      float dot_lo = 0.0f, sum_a_lo = 0.0f;
+      for (int l = 0; l < 32; l++) {
+        if (wo + (size_t)l < n_cols) {
+          uint8_t hb = (uint8_t)((qh[l] >> g) & 1);
+          float q_w = (float)(uint8_t)((qs[qo + l] & 0x0F) | (hb << 4)), q_a = (float)(int8_t)alo[2 + l];
+          float p = q_w * q_a;
+          dot_lo += p;
+          sum_a_lo += q_a;
+        }
+      }
+      {
+        float a = da_lo * dot_lo, c = m_lo * sum_a_lo;
+        float t = a - c;
+        t = t * d_a_lo;
+        sum += t;
+      }
+      float dot_hi = 0.0f, sum_a_hi = 0.0f;
+      for (int l = 0; l < 32; l++) {
+        if (wo + 32 + (size_t)l < n_cols) {
+          uint8_t hb = (uint8_t)((qh[l] >> (g + 4)) & 1);
+          float q_w = (float)(uint8_t)(((qs[qo + l] >> 4) & 0x0F) | (hb << 4)), q_a = (float)(int8_t)ahi[2 + l];
+          float p = q_w * q_a;
+          dot_hi += p;
+          sum_a_hi += q_a;
+        }
+      }
+      {
+        float a = da_hi * dot_hi, c = m_hi * sum_a_hi;
+        float t = a - c;
+        t = t * d_a_hi;
+        sum += t;
+      }
+      is += 2;
+      qo += 32;
+      wo += 64;
+    }
+  }
+  return sum;
+}
+
 /* reference/q6_k.rs:212-354: sum += (s * q) * (d_a * q_a). */
 static float fused_row_q6_k(const uint8_t *row, size_t bpr, size_t n_cols, const uint8_t *acts) {
   float sum = 0.0f;
@@ -737,6 +878,9 @@ int qk_oracle_matvec_q8_fused(int type, const uint8_t *w, size_t w_len, const ui
         break;
       case T_Q4_K:
         s = fused_row_q4_k(row, bpr, n_cols, acts);
+        break;
+      case T_Q5_K:
+        s = fused_row_q5_k(row, bpr, n_cols, acts);
         break;
       case T_Q6_K:
         s = fused_row_q6_k(row, bpr, n_cols, acts);

@@ -30,9 +30,19 @@ SIGNATURES = {
     "qk_gemm": (C.c_int, [vp, C.c_int, vp, sz, vp, sz, vp, sz, sz, sz, sz]),
     "qk_matvec_q8_fused": (C.c_int, [vp, C.c_int, vp, sz, vp, sz, vp, sz, sz, sz]),
     "qk_quantize_q8_0": (C.c_int, [vp, vp, sz, vp, sz]),
+    "qk_gpu_gemv": (C.c_int, [vp, C.c_int, vp, sz, vp, sz, vp, sz, sz, sz]),
+    "qk_gpu_gemv_batched": (C.c_int, [vp, C.c_int, vp, sz, vp, sz, vp, sz, sz, sz, sz]),
     "qk_weights_cache_evict": (C.c_int, [vp, vp]),
     "qk_weights_upload": (C.c_int, [vp, C.c_int, vp, sz, sz, sz, sz, sz, C.POINTER(vp)]),
     "qk_weights_free": (C.c_int, [vp, vp]),
+    "qk_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
+    "qk_gguf_close": (C.c_int, [vp]),
+    "qk_gguf_last_error": (C.c_int, [vp, C.c_char_p, sz]),
+    "qk_gguf_tensor_count": (C.c_int, [vp, C.POINTER(sz)]),
+    "qk_gguf_tensor_name": (C.c_int, [vp, sz, C.c_char_p, sz]),
+    "qk_gguf_tensor_info": (C.c_int, [vp, C.c_char_p, C.POINTER(C.c_int), C.POINTER(sz), C.POINTER(C.c_uint64 * 4),
+                                      C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "qk_weights_upload_gguf": (C.c_int, [vp, vp, C.c_char_p, sz, sz, C.POINTER(vp)]),
     "qk_weights_info": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]),
     "qk_gemv_dev": (C.c_int, [vp, vp, vp, vp, vp]),
     "qk_gemm_dev": (C.c_int, [vp, vp, vp, vp, sz, sz, vp]),

@@ -24,7 +24,7 @@
   } while (0)
 
 static bool type_ok(int t) {
-  return t == QK_TYPE_Q4_0 || t == QK_TYPE_Q8_0 || t == QK_TYPE_Q4_K || t == QK_TYPE_Q6_K ||
+  return t == QK_TYPE_Q4_0 || t == QK_TYPE_Q8_0 || t == QK_TYPE_Q4_K || t == QK_TYPE_Q5_K || t == QK_TYPE_Q6_K ||
          t == QK_TYPE_IQ4_XS;
 }
 
@@ -34,6 +34,7 @@ extern "C" size_t qk_block_size(int type) {
     case QK_TYPE_Q8_0:
       return 32;
     case QK_TYPE_Q4_K:
+    case QK_TYPE_Q5_K:
     case QK_TYPE_Q6_K:
     case QK_TYPE_IQ4_XS:
       return 256;
@@ -50,6 +51,8 @@ extern "C" size_t qk_block_bytes(int type) {
       return 34;
     case QK_TYPE_Q4_K:
       return 144;
+    case QK_TYPE_Q5_K:
+      return 176;
     case QK_TYPE_Q6_K:
       return 210;
     case QK_TYPE_IQ4_XS:
@@ -67,6 +70,8 @@ extern "C" const char *qk_name(int type) {
       return "Q8_0";
     case QK_TYPE_Q4_K:
       return "Q4_K";
+    case QK_TYPE_Q5_K:
+      return "Q5_K";
     case QK_TYPE_Q6_K:
       return "Q6_K";
     case QK_TYPE_IQ4_XS:
@@ -547,6 +552,55 @@ extern "C" int qk_gemm(qk_ctx *c, int type, const uint8_t *w, size_t w_len, cons
   if (m == 0 || n == 0) return QK_OK;
   if (!w || !y || (k && !x)) return QK_INVALID_ARGUMENT;
   return host_gemm(c, type, w, w_len, n, k, x, y, m);
+}
+
+// ------------------------------------------------------------ GpuKernel-shaped entry points
+// crates/oxillama-gpu/src/kernels/mod.rs:91-106 (e.g. kernels/q4_k.rs:170-195): raw weight
+// bytes and dimensions instead of a QuantTensor; checks in that implementation's order, every
+// failed size check being its GpuError::BufferSize { expected, got } (text in qk_last_error).
+static int buffer_size(qk_ctx *c, size_t expected, size_t got) {
+  c->err = "Buffer size mismatch: expected " + std::to_string(expected) + ", got " + std::to_string(got);
+  return QK_BUFFER_TOO_SMALL;
+}
+
+extern "C" int qk_gpu_gemv(qk_ctx *c, int type, const uint8_t *weight_bytes, size_t weight_len,
+                           const float *input, size_t input_len, float *output, size_t output_len,
+                           size_t rows, size_t cols) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) {
+    c->err = "Unsupported quant type for GPU: type id " + std::to_string(type);
+    return QK_UNSUPPORTED_TYPE;
+  }
+  if (output_len < rows) return buffer_size(c, rows, output_len);
+  if (input_len < cols) return buffer_size(c, cols, input_len);
+  if (weight_len < need_bytes(type, rows, cols)) return buffer_size(c, need_bytes(type, rows, cols), weight_len);
+  if (rows == 0) return QK_OK;
+  if (!weight_bytes && need_bytes(type, rows, cols)) return QK_INVALID_ARGUMENT;
+  if (!output || (cols && !input)) return QK_INVALID_ARGUMENT;
+  return host_gemm(c, type, weight_bytes, weight_len, rows, cols, input, output, 1);
+}
+
+// Y[b][r] = sum_c A[r][c] X[b][c]: kernels/batched_gemv.rs:36-50 with the matrix still
+// quantised (that function takes it dequantised to f32; its callers dequantise first).
+extern "C" int qk_gpu_gemv_batched(qk_ctx *c, int type, const uint8_t *weight_bytes, size_t weight_len,
+                                   const float *vectors, size_t vectors_len, float *output, size_t output_len,
+                                   size_t rows, size_t cols, size_t batch_size) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (!type_ok(type)) {
+    c->err = "Unsupported quant type for GPU: type id " + std::to_string(type);
+    return QK_UNSUPPORTED_TYPE;
+  }
+  if (weight_len < need_bytes(type, rows, cols)) return buffer_size(c, need_bytes(type, rows, cols), weight_len);
+  if (vectors_len != batch_size * cols) return buffer_size(c, batch_size * cols, vectors_len);  // exact, as there
+  if (output_len < batch_size * rows) return buffer_size(c, batch_size * rows, output_len);
+  if (rows == 0 || batch_size == 0) return QK_OK;
+  if (!output) return QK_INVALID_ARGUMENT;
+  if (cols == 0) {  // batched_gemv.rs:88-90: zeros
+    memset(output, 0, batch_size * rows * sizeof(float));
+    return QK_OK;
+  }
+  if (!weight_bytes || !vectors) return QK_INVALID_ARGUMENT;
+  return host_gemm(c, type, weight_bytes, weight_len, rows, cols, vectors, output, batch_size);
 }
 
 extern "C" int qk_matvec_q8_fused(qk_ctx *c, int type, const uint8_t *w, size_t w_len,

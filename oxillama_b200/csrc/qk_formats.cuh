@@ -54,6 +54,18 @@ __device__ __forceinline__ float qk_dequant_elem(const QkLayout &L, const uint8_
       float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
       return __fsub_rn(__fmul_rn(d1, (float)q), m1);
     }
+    case QK_T_Q5_K: {  // reference/q5_k.rs:66-108: Q4_K plus a fifth bit from qh (bit g for the low-nibble
+                       // quant of group g, bit g + 4 for the high-nibble one)
+      const uint8_t *h = at(0, 0);
+      float d = qk_h2f(h), dmin = qk_h2f(h + 2);
+      int sub = i >> 5, g = i >> 6, l = i & 31;
+      uint8_t byte = *at(2, 32 * g + l), hb = *at(1, l);
+      int q = (sub & 1) ? ((byte >> 4) | (((hb >> (g + 4)) & 1) << 4)) : ((byte & 0x0F) | (((hb >> g) & 1) << 4));
+      int sc, mn;
+      qk_q4k_scale_min(h + 4, sub, sc, mn);
+      float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
+      return __fsub_rn(__fmul_rn(d1, (float)q), m1);
+    }
     case QK_T_Q6_K: {  // reference/q6_k.rs:39-71
       const uint8_t *sc = at(1, 0);
       float d = qk_h2f(at(2, 0));

@@ -18,6 +18,7 @@
 //     Q4_K   d,dmin,scales 16 B (g 16)    | nibbles 128 B (g 32)         8 x 144 = 1152 B
 //     Q6_K   ql+qh  192 B (g 16) | scales 16 B (g 16) | d 2 B (g 2)      8 x 210 = 1680 B
 //     IQ4_XS nibbles 128 B (g 16)         | d,scales_h,scales_l 8 B (g 8) 8 x 136 = 1088 B
+//     Q5_K   d,dmin,scales 16 B (g 16) | qh 32 B (g 32) | nibbles 128 B (g 32)  8 x 176 = 1408 B
 //
 //   The same 16- or 32-byte group of all 8 rows lies in one 128- or 256-byte
 //   span: eight lanes that hold the eight rows read it from HBM as full sectors
@@ -44,6 +45,7 @@
 #define QK_T_Q4_K 12
 #define QK_T_Q6_K 14
 #define QK_T_IQ4_XS 23
+#define QK_T_Q5_K 13
 
 struct QkLayout {
   int type;
@@ -80,6 +82,12 @@ static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayo
     case QK_T_Q4_K:
       l.bs = 256; l.bb = 144; l.nplanes = 2;
       l.pw[0] = 16; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 128; l.po[1] = 16; l.pg[1] = 32;
+      l.bm = 1;
+      break;
+    case QK_T_Q5_K:  // d, dmin, scales 16 B | qh 32 B | qs 128 B
+      l.bs = 256; l.bb = 176; l.nplanes = 3;
+      l.pw[0] = 16; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 32; l.po[1] = 16; l.pg[1] = 32;
+      l.pw[2] = 128; l.po[2] = 48; l.pg[2] = 32;
       l.bm = 1;
       break;
     case QK_T_Q6_K:

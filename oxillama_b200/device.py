@@ -37,6 +37,25 @@ class DeviceWeights:
         self.ctx.lib.qk_weights_info(h, C.byref(t), C.byref(r), C.byref(c), C.byref(b))
         self.algo_bytes = b.value
 
+    @classmethod
+    def from_gguf(cls, gguf, name: str, row_begin: int = 0, row_end: int | None = None,
+                  ctx: Context | None = None) -> "DeviceWeights":
+        """Rows [row_begin, row_end) of tensor `name` of an open `gguf.GgufFile`, read from the file
+        through pinned staging memory (`qk_weights_upload_gguf`)."""
+        self = cls.__new__(cls)
+        self.ctx = ctx or default_context()
+        info = gguf.info(name)
+        n_rows = info.dims[0] if info.n_dims else 0
+        row_end = n_rows if row_end is None else row_end
+        h = C.c_void_p()
+        self.ctx.check(self.ctx.lib.qk_weights_upload_gguf(self.ctx.handle, gguf.handle, name.encode(), row_begin,
+                                                           row_end, C.byref(h)))
+        self.handle, self.tensor_type = h, info.tensor_type
+        t, r, c, b = C.c_int(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+        self.ctx.lib.qk_weights_info(h, C.byref(t), C.byref(r), C.byref(c), C.byref(b))
+        self.rows, self.cols, self.algo_bytes = r.value, c.value, b.value
+        return self
+
     def free(self):
         if self.handle:
             self.ctx.lib.qk_weights_free(self.ctx.handle, self.handle)

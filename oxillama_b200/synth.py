@@ -14,9 +14,10 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K, IQ4_XS = 2, 8, 12, 14, 23
-BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, IQ4_XS: 256}
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, IQ4_XS: 136}
-NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ4_XS: "IQ4_XS"}
+Q5_K = 13  # served by the generic kernels; not one of the benchmark's formats
+BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, IQ4_XS: 256, Q5_K: 256}
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, IQ4_XS: 136, Q5_K: 176}
+NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ4_XS: "IQ4_XS", Q5_K: "Q5_K"}
 ALL_TYPES = (Q4_0, Q8_0, Q4_K, Q6_K, IQ4_XS)
 
 
@@ -54,6 +55,10 @@ def gen_blocks(qtype: int, n_blocks: int, seed: int = 0, stream: int = 0,
         out[:, 2:4] = _f16_bytes(rng, *d_range, n_blocks)
         # any 12 bytes are a bijective packing of sixteen uniform 6-bit fields
         out[:, 4:] = rng.integers(0, 256, (n_blocks, 140), dtype=np.uint8)
+    elif qtype == Q5_K:
+        out[:, 0:2] = _f16_bytes(rng, *d_range, n_blocks)
+        out[:, 2:4] = _f16_bytes(rng, *d_range, n_blocks)
+        out[:, 4:] = rng.integers(0, 256, (n_blocks, 172), dtype=np.uint8)
     elif qtype == Q6_K:
         out[:, 0:192] = rng.integers(0, 256, (n_blocks, 192), dtype=np.uint8)
         out[:, 192:208] = rng.integers(-32, 32, (n_blocks, 16), dtype=np.int8).view(np.uint8)

@@ -294,7 +294,7 @@ def test_error_codes(K, disp):
         k.gemv(K.QuantTensor(blk[:10], (1, 32), S.Q4_0), np.zeros(32, np.float32), np.zeros(1, np.float32))
     assert e.value.kind == "BufferTooSmall"
     with pytest.raises(K.QuantError) as e:
-        disp.get_kernel(13)  # Q5_K: not part of this backend
+        disp.get_kernel(10)  # Q2_K: not part of this backend
     assert e.value.kind == "UnsupportedType"
     k4 = disp.get_kernel(S.Q4_K)
     w = S.gen_weight(S.Q4_K, 2, 256, seed=1)
@@ -492,3 +492,116 @@ def test_peer_gather_single_rank(t, m):
 def K_err():
     from oxillama_b200.kernels import QuantError
     return QuantError
+
+
+# ---------------------------------------------------------------- the GpuKernel-shaped surface (oxillama-gpu)
+@pytest.mark.parametrize("t", S.ALL_TYPES)
+def test_gpu_kernel_surface(t):
+    """`GpuKernel::gemv(ctx, weight_bytes, input, output, rows, cols)` and the batched form
+    (crates/oxillama-gpu/src/kernels/mod.rs:91-106, batched_gemv.rs:36-50): same results as the
+    oracle's gemv (the CPU crate's element order), the reference's size checks in its order."""
+    from oxillama_b200 import gpu_kernels as G
+    cls = {S.Q4_0: G.Q4_0GpuKernel, S.Q8_0: G.Q8_0GpuKernel, S.Q4_K: G.Q4_KGpuKernel, S.Q6_K: G.Q6_KGpuKernel,
+           S.IQ4_XS: G.Iq4XsGpuKernel}[t]
+    ctx, k = G.GpuContext(), cls()
+    rows, cols = 24, 1024
+    w = S.gen_weight(t, rows, cols, seed=33)
+    x = S.gen_acts(5, cols, seed=33)
+    out = np.full(rows, np.nan, np.float32)
+    k.gemv(ctx, w, x[0], out, rows, cols)
+    assert rel_inf(out, O.gemv(t, w, rows, cols, x[0])[1]) <= TOL_F32
+    y = G.batched_gemv(ctx, t, w, x, rows, cols, 5)
+    assert rel_inf(y, O.gemm(t, w, x, 5, rows, cols)[1]) <= TOL
+    for bad in (lambda: k.gemv(ctx, w, x[0], np.zeros(rows - 1, np.float32), rows, cols),   # q4_k.rs:183-188
+                lambda: k.gemv(ctx, w, x[0][:-1], out, rows, cols),                          # q4_k.rs:189-194
+                lambda: k.gemv(ctx, w[:-1], x[0], out, rows, cols),                          # q4_k.rs:114-119
+                lambda: G.batched_gemv(ctx, t, w, x[:, :-1], rows, cols, 5)):                # batched_gemv.rs:80-86
+        with pytest.raises(G.GpuError) as e:
+            bad()
+        assert e.value.kind == "BufferSize" and "expected" in str(e.value)
+    assert np.all(G.batched_gemv(ctx, t, w[:0], np.zeros((3, 0), np.float32), 4, 0, 3) == 0)  # batched_gemv.rs:88-90
+
+
+# ---------------------------------------------------------------- GGUF file -> device
+def test_upload_from_gguf_file(tmp_path):
+    """Weights uploaded straight from a GGUF file (`qk_weights_upload_gguf`), whole and as a row
+    shard, give the oracle's results; tensors of other types and truncated files are refused."""
+    import torch
+    import gguf_writer as W
+    from oxillama_b200.device import DeviceWeights, check_device_status
+    from oxillama_b200.gguf import GgufFile
+    from oxillama_b200.kernels import QuantError
+    rows, cols = 72, 1024
+    ws = {t: S.gen_weight(t, rows, cols, seed=34) for t in S.ALL_TYPES}
+    tensors = [(f"w.{S.NAMES[t]}", (rows, cols), t, ws[t]) for t in S.ALL_TYPES] + [("norm", (cols,), 0, np.zeros(4 * cols, np.uint8))]
+    path = str(tmp_path / "m.gguf")
+    W.write_gguf(path, tensors, [("general.architecture", "str", "llama")])
+    g = GgufFile(path)
+    x = S.gen_acts(1, cols, seed=34)[0]
+    xd = torch.from_numpy(x).cuda()
+    for t in S.ALL_TYPES:
+        ref = O.gemv(t, ws[t], rows, cols, x)[1]
+        dw = DeviceWeights.from_gguf(g, f"w.{S.NAMES[t]}")
+        assert (dw.rows, dw.cols, dw.tensor_type) == (rows, cols, t)
+        y = torch.empty(rows, device="cuda")
+        dw.gemv(xd, y)
+        check_device_status()
+        assert rel_inf(y.cpu().numpy(), ref) <= TOL_F32
+        sh = DeviceWeights.from_gguf(g, f"w.{S.NAMES[t]}", 16, 56)   # a row shard: one byte range of the file
+        ys = torch.empty(40, device="cuda")
+        sh.gemv(xd, ys)
+        assert torch.equal(ys, y[16:56])
+        dw.free(), sh.free()
+    with pytest.raises(QuantError) as e:
+        DeviceWeights.from_gguf(g, "norm")
+    assert e.value.kind == "UnsupportedType"
+    with pytest.raises(KeyError):
+        DeviceWeights.from_gguf(g, "absent")
+    g.close()
+    blob = open(path, "rb").read()
+    cut = str(tmp_path / "cut.gguf")
+    open(cut, "wb").write(blob[: len(blob) // 2])
+    g2 = GgufFile(cut)
+    with pytest.raises(QuantError) as e:
+        DeviceWeights.from_gguf(g2, f"w.{S.NAMES[S.IQ4_XS]}")
+    assert e.value.kind == "BufferTooSmall"
+    g2.close()
+
+
+# ---------------------------------------------------------------- Q5_K (generic kernels: exact, not tuned)
+def test_q5_k_through_every_entry_point(K, disp):
+    """reference/q5_k.rs: dequant bit-exact, gemv / gemm / fused against the oracle, the reference's
+    known answers (q5_k.rs:376-440) through the GPU, a row shard on the device."""
+    import torch
+    from oxillama_b200.device import DeviceWeights
+    t = S.Q5_K
+    k = disp.get_kernel(t)
+    assert (k.block_size(), k.block_bytes(), k.name()) == (256, 176, "Q5_K")
+    sc1 = [1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]
+    out = np.empty(256, np.float32)
+    k.dequant_block(np.concatenate([f16b(1.0), f16b(0.0), np.array(sc1, np.uint8), np.full(32, 0xFF, np.uint8),
+                                    np.zeros(128, np.uint8)]), out)
+    assert np.all(out == 16.0)
+    for rows, cols in ((19, 768), (5, 256 + 128 + 3), (33, 4096)):
+        w = S.gen_weight(t, rows, cols, seed=35)
+        dq = np.empty((rows, cols), np.float32)
+        k.dequant_matrix(K.QuantTensor(w, (rows, cols), t), dq)
+        assert np.array_equal(dq.view(np.uint32), O.dequant_matrix(t, w, rows, cols).view(np.uint32))
+        for m in (1, 3, 9):
+            x = S.gen_acts(m, cols, seed=35)
+            y = np.full((m, rows), np.nan, np.float32)
+            k.gemm(K.QuantTensor(w, (rows, cols), t), x, y, m, rows, cols)
+            assert rel_inf(y, O.gemm(t, w, x, m, rows, cols)[1]) <= TOL_F32
+    rows, cols = 37, 2048
+    w = S.gen_weight(t, rows, cols, seed=36)
+    x = S.gen_acts(1, cols, seed=36)[0]
+    a = K.quantize_f32_to_q8_0(x)
+    init = np.linspace(-3, 3, rows, dtype=np.float32)
+    got = init.copy()
+    k.matvec_q8_fused(w, a, got, rows, cols)
+    assert rel_inf(got, O.matvec_q8_fused(t, w, a, init, rows, cols)[1]) <= TOL_F32
+    dw = DeviceWeights(t, w, rows, cols, 8, 24)
+    ys = torch.empty(16, device="cuda")
+    dw.gemv(torch.from_numpy(x).cuda(), ys)
+    assert rel_inf(ys.cpu().numpy(), O.gemv(t, w, rows, cols, x)[1][8:24]) <= TOL_F32
+    dw.free()

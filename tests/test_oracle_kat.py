@@ -46,6 +46,54 @@ Q8_VALS_A = [1, -2, 3, -4, 5, -6, 7, -8, 9, -10, 11, -12, 13, -14, 15, -16,
              -1, 2, -3, 4, -5, 6, -7, 8, -9, 10, -11, 12, -13, 14, -15, 16]
 
 
+def q5_k_block(d, dmin, scales, qh, qs):
+    return np.concatenate([f16b(d), f16b(dmin), np.asarray(scales, np.uint8), np.asarray(qh, np.uint8),
+                           np.asarray(qs, np.uint8)])
+
+
+# ------------------------------------------------------------------ Q5_K (a "next" format: generic kernels)
+Q5_SC1 = [1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]
+
+
+def test_q5_k_dequant():  # reference/q5_k.rs:376-440
+    st, out = O.dequant_block(S.Q5_K, q5_k_block(0.0, 0.0, [0] * 12, [0] * 32, [0] * 128))
+    assert st == OK and np.all(out == 0.0)
+    st, out = O.dequant_block(S.Q5_K, q5_k_block(1.0, 0.0, Q5_SC1, [0] * 32, [0x88] * 128))
+    assert st == OK and np.all(out == 8.0)
+    st, out = O.dequant_block(S.Q5_K, q5_k_block(1.0, 0.0, Q5_SC1, [0xFF] * 32, [0] * 128))
+    assert st == OK and np.all(out == 16.0)   # the fifth bit alone
+
+
+def test_q5_k_high_bit_positions():  # reference/q5_k.rs:87-101: bit g for low nibbles of group g, bit g + 4 for high
+    for bit in range(8):
+        st, out = O.dequant_block(S.Q5_K, q5_k_block(1.0, 0.0, Q5_SC1, [1 << bit] * 32, [0] * 128))
+        g, hi = bit % 4, bit // 4
+        want = np.zeros(256, np.float32)
+        want[64 * g + 32 * hi: 64 * g + 32 * hi + 32] = 16.0
+        assert st == OK and np.array_equal(out, want), bit
+
+
+def test_q5_k_gemv_matches_dequant_dot():  # reference/q5_k.rs:442-475
+    scales = [(i * 17 + 3) & 0xFF for i in range(12)]
+    qh = [(i * 13 + 7) & 0xFF for i in range(32)]
+    qs = [(i * 5 + 11) & 0xFF for i in range(128)]
+    blk = q5_k_block(0.5, 0.25, scales, qh, qs)
+    st, dq = O.dequant_block(S.Q5_K, blk)
+    x = (np.arange(256, dtype=np.float32) * np.float32(0.01)) - np.float32(1.28)
+    st, y = O.gemv(S.Q5_K, blk, 1, 256, x)
+    assert st == OK and abs(float(y[0]) - float((dq * x).sum())) < 0.1
+
+
+def test_q5_k_fused_matches_unfused():  # reference/q5_k.rs:236-347 vs :137-189
+    w = S.gen_weight(S.Q5_K, 3, 512, seed=12)
+    x = S.gen_acts(1, 512, seed=12)[0]
+    st, a = O.quantize_q8_0(x)
+    st, out = O.matvec_q8_fused(S.Q5_K, w, a, np.zeros(3, np.float32), 3, 512)
+    st2, y = O.gemv(S.Q5_K, w, 3, 512, x)
+    assert st == OK and st2 == OK
+    assert np.abs(out - y).max() / np.abs(y).max() < 2e-2   # activations rounded to 8 bits
+
+
 # ------------------------------------------------------------------ Q4_0
 def test_q4_0_dequant_zeros():  # reference/q4_0.rs:246-256
     st, out = O.dequant_block(S.Q4_0, q4_0_block(1.0, [0x88] * 16))
