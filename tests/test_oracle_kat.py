@@ -337,7 +337,7 @@ def test_iq4_xs_table_and_interleave():  # reference/iq_shared.rs:16-18, iq4_xs.
 # ------------------------------------------------------------------ unsupported / shapes
 def test_unsupported_type():
     assert O.dequant_block(3, np.zeros(64, np.uint8), out_len=32)[0] == UNSUPPORTED
-    assert O.gemv(13, np.zeros(176, np.uint8), 1, 256, np.zeros(256, np.float32))[0] == UNSUPPORTED
+    assert O.gemv(10, np.zeros(84, np.uint8), 1, 256, np.zeros(256, np.float32))[0] == UNSUPPORTED   # Q2_K
 
 
 @pytest.mark.parametrize("qtype", S.ALL_TYPES)
