@@ -581,6 +581,12 @@ def run_ours(args):
             matvec_rate(torch, ctx, S.Q8_0, 4096, 4096, 1, stream),
             matvec_rate(torch, ctx, S.IQ4_XS, 14336, 4096, 1, stream),    # config[4] expert gate / up
         ]
+        for r, (qt, rr, cc) in zip(extras["decode_shapes"], ((S.Q4_0, 4096, 4096), (S.Q6_K, 128256, 4096),
+                                                             (S.Q6_K, 4096, 14336), (S.Q8_0, 4096, 4096),
+                                                             (S.IQ4_XS, 14336, 4096))):
+            # the reference's best CPU tier on the same shape, all host cores, about a second each
+            c = cpu_gemv_rate(1.0, qtype=qt, rows=rr, cols=cc, w=big_weight(qt, rr, cc, 0, 97))
+            r["cpu_all_cores"] = {"value": c["value"], "unit": UNIT, "cores": c["cores"], "sample": c["sample"]}
         extras["small_batch"] = matvec_rates(torch, ctx, S.Q4_K, 14336, 4096, (2, 4, 8, 32, 64, 128), stream)
         extras["layer"] = layer_rates(torch, ctx, (1, 8, 32, 512), stream)
         extras["prefill"] = [matvec_rate(torch, ctx, S.Q4_K, 14336, 4096, 512, stream, bound="tensor", launches=96),
