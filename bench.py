@@ -175,6 +175,21 @@ def layer_rates(torch, ctx, ms, stream, copies=3):
         flops = sum(2.0 * m * d.rows * d.cols for d in layers[0])
         out = {"workload": f"config[3]: q,k,v,o,gate,up Q4_K + down Q6_K of one layer, M={m}", "us_per_layer": us,
                "weight_bytes": nbytes}
+        if m <= 4:
+            # the same layer with its feed-forward block as one call (gate and up in one launch,
+            # silu(g) * u formed in its reducer, then down)
+            from oxillama_b200.device import ffn
+
+            def fn_fused():
+                for lw in layers:
+                    for d in lw[:4]:
+                        d.gemm(xs[d.cols], ys[d.rows], m)
+                    ffn(lw[4], lw[5], lw[6], xs[4096], ys[4096], m)
+            us = graph_us(torch, stream, fn_fused, copies, launches=60)
+            check_device_status(ctx, stream)
+            out["us_per_layer_separate_calls"] = out["us_per_layer"]
+            out["us_per_layer"] = us
+            out["note"] = "feed-forward block through qk_ffn_dev (5 launches per layer instead of 7)"
         if m <= 64:
             peak, which = peaks()
             out.update({"weight_gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "bound": "hbm",

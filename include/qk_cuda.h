@@ -177,6 +177,18 @@ int qk_gemv_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_d
 int qk_gemm_dev(qk_ctx *ctx, const qk_weights *h, const float *x_dev, float *y_dev, size_t m,
                 size_t ldy, void *stream);
 
+/* The dense feed-forward block around the path (new as one call; the reference's
+ * feed_forward does it as three QuantLinear::forward calls and swiglu_inplace,
+ * crates/oxillama-arch/src/llama/model.rs:281-310, crates/oxillama-arch/src/common/swiglu.rs:15-21):
+ *   y_dev[i][:] = down( silu(gate x_i) * (up x_i) ),  i < m,  x_dev [m x hidden], y_dev [m x down rows].
+ * gate and up are [inter x hidden], down is [rows x inter].  For Q4_K gate / up and m <= 4 the
+ * two projections run as one launch over both matrices (they share the split activations) and
+ * silu(g) * u is formed where the dot products are reduced, so neither g nor u is ever
+ * written out; otherwise the three matmuls and an element-wise pass are enqueued in turn.
+ * Keeps its own scratch for the hidden activations, grown on first use. */
+int qk_ffn_dev(qk_ctx *ctx, const qk_weights *gate, const qk_weights *up, const qk_weights *down,
+               const float *x_dev, float *y_dev, size_t m, void *stream);
+
 /* out_dev[rows x cols] f32 = dequantised shard, bit-identical to dequant_block. */
 int qk_dequant_dev(qk_ctx *ctx, const qk_weights *h, float *out_dev, void *stream);
 

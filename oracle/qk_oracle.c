@@ -894,6 +894,35 @@ int qk_oracle_matvec_q8_fused(int type, const uint8_t *w, size_t w_len, const ui
   return QK_OK;
 }
 
+/* ------------------------------ dense feed-forward block ------------------------------ */
+/* swiglu_inplace, crates/oxillama-arch/src/common/swiglu.rs:15-21 */
+void qk_oracle_swiglu_inplace(float *gate, const float *up, size_t n) {
+  for (size_t i = 0; i < n; i++) {
+    float e = expf(-gate[i]);
+    float den = 1.0f + e;
+    float sigmoid = 1.0f / den;
+    float t = gate[i] * sigmoid;
+    gate[i] = t * up[i];
+  }
+}
+
+/* feed_forward, dense branch (crates/oxillama-arch/src/llama/model.rs:281-310), for m rows of x:
+ * gate = gate_proj(x); up = up_proj(x); swiglu_inplace(gate, up); y = down_proj(gate). */
+int qk_oracle_ffn(int type_gu, const uint8_t *gate, const uint8_t *up, size_t gu_len, int type_d,
+                  const uint8_t *down, size_t d_len, const float *x, float *y, size_t m, size_t hidden,
+                  size_t inter, size_t out_rows, float *scratch /* 2 * inter floats */) {
+  for (size_t i = 0; i < m; i++) {
+    int st = qk_oracle_gemv(type_gu, gate, gu_len, inter, hidden, x + i * hidden, hidden, scratch, inter);
+    if (st) return st;
+    st = qk_oracle_gemv(type_gu, up, gu_len, inter, hidden, x + i * hidden, hidden, scratch + inter, inter);
+    if (st) return st;
+    qk_oracle_swiglu_inplace(scratch, scratch + inter, inter);
+    st = qk_oracle_gemv(type_d, down, d_len, out_rows, inter, scratch, inter, y + i * out_rows, out_rows);
+    if (st) return st;
+  }
+  return QK_OK;
+}
+
 /* ---------------------------- Q8_0 activation encoder ---------------------------- */
 /* quantize.rs:58-75,190-210.  `q` uses the f32 scale; the stored scale is its
  * f16 rounding.  Rust's f32::round is round-half-away-from-zero (roundf); the

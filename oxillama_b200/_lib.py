@@ -46,6 +46,7 @@ SIGNATURES = {
     "qk_weights_info": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]),
     "qk_gemv_dev": (C.c_int, [vp, vp, vp, vp, vp]),
     "qk_gemm_dev": (C.c_int, [vp, vp, vp, vp, sz, sz, vp]),
+    "qk_ffn_dev": (C.c_int, [vp, vp, vp, vp, vp, vp, sz, vp]),
     "qk_dequant_dev": (C.c_int, [vp, vp, vp, vp]),
     "qk_matvec_q8_fused_dev": (C.c_int, [vp, vp, vp, vp, vp]),
     "qk_quantize_q8_0_dev": (C.c_int, [vp, vp, sz, vp, vp]),

@@ -129,6 +129,7 @@ extern "C" int qk_shutdown(qk_ctx *c) {
   cudaFreeHost((void *)c->status_host);
   if (c->scratch) cudaFree(c->scratch);
   if (c->moe) cudaFree(c->moe);
+  if (c->ffn) cudaFree(c->ffn);
   cudaStreamDestroy(c->stream);
   delete c;
   return QK_OK;
@@ -422,6 +423,51 @@ extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk
     CK(c, qk_launch_moe_scatter(o, list, wts, (uint32_t)m, (uint32_t)top_k, (uint32_t)hidden, y_dev, s));
   }
   return QK_OK;
+}
+
+// ------------------------------------------------------------ feed-forward block
+// FFN(x) = down(silu(gate x) * up x): the dense branch of feed_forward
+// (crates/oxillama-arch/src/llama/model.rs:281-310) with swiglu_inplace
+// (crates/oxillama-arch/src/common/swiglu.rs:15-21).
+extern "C" int qk_ffn_dev(qk_ctx *c, const qk_weights *gate, const qk_weights *up, const qk_weights *down,
+                          const float *x_dev, float *y_dev, size_t m, void *stream) {
+  if (!c || !gate || !up || !down || !x_dev || !y_dev) return QK_INVALID_ARGUMENT;
+  if (gate->device != c->device || up->device != c->device || down->device != c->device) return QK_INVALID_ARGUMENT;
+  const size_t hidden = gate->L.cols, inter = gate->L.rows;
+  if (up->L.cols != hidden || up->L.rows != inter || down->L.cols != inter) return QK_DIMENSION_MISMATCH;
+  if (m == 0 || down->L.rows == 0) return QK_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  // scratch: h (and, on the unfused route, the up projection) [m x inter] each
+  const size_t need = 2 * m * (inter ? inter : 1) * sizeof(float);
+  if (need > c->ffn_cap) {
+    CK(c, cudaDeviceSynchronize());
+    if (c->ffn) cudaFree(c->ffn);
+    c->ffn = nullptr, c->ffn_cap = 0;
+    CK(c, cudaMalloc(&c->ffn, need));
+    c->ffn_cap = need;
+  }
+  float *h = (float *)c->ffn, *u = h + m * inter;
+  const bool fused = !c->force_simple && gate->L.type == QK_T_Q4_K && up->L.type == QK_T_Q4_K && hidden > 0 &&
+                     inter > 0 && m <= QK_GEMV_MAX_M && qk_gemv_dual_supported(gate->L, (uint32_t)m);
+  if (fused) {
+    // gate and up in one launch (they share the split activations), silu(g) * u in its reducer
+    const size_t sneed = qk_gemv_mma_scratch_bytes(gate->L, (uint32_t)m);
+    if (sneed > c->scratch_cap) {
+      CK(c, cudaDeviceSynchronize());
+      cudaFree(c->scratch);
+      c->scratch = nullptr, c->scratch_cap = 0;
+      CK(c, cudaMalloc(&c->scratch, sneed * 2));
+      c->scratch_cap = sneed * 2;
+    }
+    CK(c, qk_launch_gemv_dual(gate->L, gate->dev, up->dev, x_dev, h, (uint32_t)m, inter, c->status_dev, c->scratch,
+                              c->sm_count, s));
+  } else {
+    int st = gemm_dispatch(c, gate, x_dev, h, m, inter, s);
+    if (st) return st;
+    if ((st = gemm_dispatch(c, up, x_dev, u, m, inter, s))) return st;
+    CK(c, qk_launch_swiglu(h, u, (uint64_t)m * inter, s));
+  }
+  return gemm_dispatch(c, down, h, y_dev, m, down->L.rows, s);
 }
 
 extern "C" int qk_dequant_dev(qk_ctx *c, const qk_weights *h, float *out_dev, void *stream) {

@@ -24,6 +24,15 @@ cudaError_t qk_launch_gemv_mma(const QkLayout &L, const uint8_t *tiled, const fl
   return launch<DecQ4K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, peers);
 }
 
+// Gate and up projection of a feed-forward block in one launch: h[i][j] = silu(gate_j . x_i) * (up_j . x_i).
+bool qk_gemv_dual_supported(const QkLayout &L, uint32_t m) { return qk_gemv_mma_supported(L, m); }
+
+cudaError_t qk_launch_gemv_dual(const QkLayout &L, const uint8_t *gate_tiled, const uint8_t *up_tiled, const float *x,
+                                float *h, uint32_t m, uint64_t ldh, unsigned *status, unsigned char *scratch,
+                                int sm_count, cudaStream_t s) {
+  return launch<DecQ4K>(L, gate_tiled, x, h, m, ldh, status, scratch, sm_count, s, nullptr, up_tiled);
+}
+
 // Same matvec, always through qk_xsplit_kernel + the x image in `scratch` (never the
 // in-CTA split), for callers that hand in their own scratch.
 cudaError_t qk_launch_gemv_mma_split(const QkLayout &L, const uint8_t *tiled, const float *x,

@@ -274,19 +274,29 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
 // sensitive to its code size).
 // F: the weight format's policy (tile geometry, register image of one 256-column span,
 // its loads and its arithmetic; see qk_dec_*.cuh).
-template <class F, int M, bool INCTA, int CW, int G, bool PEER>
+// MODE: 0 = one matrix, results into y; 1 = the same with the sharded-layer fan-out (the
+// old PEER: results as tagged words into every rank's slots, activations optionally out of
+// slots); 2 = two matrices of the same shape and format at once, W as the gate and W2 as the
+// up projection of a feed-forward block: a CTA's chunks alternate (gate rows 8 i .., up rows
+// 8 i ..), both see the same split activations, and the reducer writes
+// silu(gate) * up (crates/oxillama-arch/src/common/swiglu.rs:15-21) where a plain matvec
+// writes its dot products.
+template <class F, int M, bool INCTA, int CW, int G, int MODE>
 __global__ void __launch_bounds__((CW + 1) * 32, 1)
-    qk_gemv_imma_kernel(QkLayout L, const uint8_t *__restrict__ W, const float *__restrict__ x,
+    qk_gemv_imma_kernel(QkLayout L, const uint8_t *__restrict__ W, const uint8_t *__restrict__ W2,
+                           const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
                            uint64_t ldy, unsigned *status, int nstage, int nslot,
                            uint32_t stage_bytes, SmemMma S, uint32_t Kp, QkPeers peers, int npre) {
   constexpr int WG = CW / G;  // warps per group; a group owns every G-th chunk
+  constexpr bool PEER = MODE == 1, DUAL = MODE == 2;
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  // chunks of this CTA, in the order it takes them; with two matrices every 8-row group counts twice
   const uint32_t my_chunks =
-      blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      (blockIdx.x < L.chunks ? (L.chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) * (DUAL ? 2u : 1u);
   const uint32_t my_items = my_chunks * L.ktiles;
 
   QK_STAMP(warp == 0, 0);
@@ -309,11 +319,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     // buffers safe without a second handshake.
     uint32_t pc = 0, pkt = 0, pst = 0;  // chunk ordinal, k-tile and stage of the next item
     auto issue = [&]() {                // lane 0 only
-      const uint32_t chunk = blockIdx.x + pc * gridDim.x;
+      const uint32_t chunk = blockIdx.x + (DUAL ? pc >> 1 : pc) * gridDim.x;
+      const uint8_t *Wc = (DUAL && (pc & 1u)) ? W2 : W;
       const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
       const uint32_t bar = sbase + S.full + pst * 8;
       mbar_expect_tx(bar, bytes);
-      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, W + qk_tile_offset(L, chunk, pkt), bytes, bar);
+      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, Wc + qk_tile_offset(L, chunk, pkt), bytes, bar);
       if (++pkt == L.ktiles) pkt = 0, pc++;
       if (++pst == (uint32_t)nstage) pst = 0;
     };
@@ -395,6 +406,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       }
     }
     uint32_t slot = 0, sph = 0;
+    float gate_v = 0.f;  // two matrices: the gate chunk's sum, kept until the up chunk's arrives
     for (uint32_t c = 0; c < my_chunks; c++) {
       if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, sph)) {
         if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
@@ -412,8 +424,18 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         const uint32_t m = lane >> 3, r = lane & 7u;
 #pragma unroll
         for (int wv = 0; wv < WG; wv++) v += red[(wv * M + m) * 8 + r];
-        const uint32_t row = (blockIdx.x + c * gridDim.x) * 8 + r;
-        if (!(PEER && peers.n) && row < L.rows) y[(uint64_t)m * ldy + row] = v;
+        const uint32_t row = (blockIdx.x + (DUAL ? c >> 1 : c) * gridDim.x) * 8 + r;
+        if (DUAL) {
+          if ((c & 1u) == 0) {
+            gate_v = v;
+          } else if (row < L.rows) {
+            // swiglu_inplace: sigmoid = 1 / (1 + exp(-g)); g * sigmoid * u, each step rounded
+            const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-gate_v)));
+            y[(uint64_t)m * ldy + row] = __fmul_rn(__fmul_rn(gate_v, sg), v);
+          }
+        } else if (!(PEER && peers.n) && row < L.rows) {
+          y[(uint64_t)m * ldy + row] = v;
+        }
       }
       if (PEER && peers.n) {
         // The same (value, tag) word into the slot of every rank: lane (q, r) stores row r
@@ -613,11 +635,11 @@ inline bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P, uint32_t xs
   return true;
 }
 
-template <class F, int M, bool INCTA, int CW, int G, bool PEER = false>
+template <class F, int M, bool INCTA, int CW, int G, int MODE = 0>
 cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint64_t ldy,
                        unsigned *status, unsigned char *ximg, int sm_count, const PlanMma &P,
-                       cudaStream_t s, const QkPeers *peers = nullptr) {
-  auto kern = qk_gemv_imma_kernel<F, M, INCTA, CW, G, PEER>;
+                       cudaStream_t s, const QkPeers *peers = nullptr, const uint8_t *W2 = nullptr) {
+  auto kern = qk_gemv_imma_kernel<F, M, INCTA, CW, G, MODE>;
   static QkPerDevice attr_set;
   if (attr_set.first()) {
     cudaError_t e =
@@ -666,7 +688,7 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   }
   int npre = npre_env > 0 ? npre_env : (M == 1 ? (CW == 12 ? 2 : 1) : (M == 2 ? 4 : 3));
   if (npre > P.nstage) npre = P.nstage;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, x, (const unsigned char *)ximg, y, ldy, status,
+  return cudaLaunchKernelEx(&cfg, kern, L, W, W2, x, (const unsigned char *)ximg, y, ldy, status,
                             P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv, npre);
 }
 
@@ -685,23 +707,28 @@ inline bool split_in_cta(const PlanMma &P, uint32_t m) {
 template <class F, int M>
 cudaError_t launch_mma_m(const QkLayout &L, const uint8_t *W, const float *x, float *y,
                          uint64_t ldy, unsigned *status, unsigned char *ximg, int sm_count,
-                         const PlanMma &P, cudaStream_t s, const QkPeers *peers) {
+                         const PlanMma &P, cudaStream_t s, const QkPeers *peers, const uint8_t *W2 = nullptr) {
   // Warp groups: a group owns every G-th chunk.  A stage must always be consumed by
   // the same group (a waiter on an mbarrier may be at most one phase ahead of it),
   // so the ring depth is a multiple of G * ktiles; P.groups was chosen to allow that.
   const int cw = P.cw;
   const bool peer = peers != nullptr;
-#define QK_LAUNCH1(CWV, GV, PV)                                                                       \
-  return split_in_cta(P, M)                                                                           \
-             ? launch_mma<F, M, true, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers) \
-             : launch_mma<F, M, false, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers)
-#define QK_LAUNCH(CWV, GV)          \
-  do {                              \
-    if (peer) {                     \
-      QK_LAUNCH1(CWV, GV, true);    \
-    } else {                        \
-      QK_LAUNCH1(CWV, GV, false);   \
-    }                               \
+#define QK_LAUNCH1(CWV, GV, PV)                                                                               \
+  return split_in_cta(P, M)                                                                                   \
+             ? launch_mma<F, M, true, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers, W2)  \
+             : launch_mma<F, M, false, CWV, GV, PV>(L, W, x, y, ldy, status, ximg, sm_count, P, s, peers, W2)
+#define QK_LAUNCH(CWV, GV)                \
+  do {                                    \
+    if constexpr (F::HAS_DUAL) {          \
+      if (W2) {                           \
+        QK_LAUNCH1(CWV, GV, 2);           \
+      }                                   \
+    }                                     \
+    if (peer) {                           \
+      QK_LAUNCH1(CWV, GV, 1);             \
+    } else {                              \
+      QK_LAUNCH1(CWV, GV, 0);             \
+    }                                     \
   } while (0)
   if constexpr (M == 1)
     if (cw == 12) QK_LAUNCH(12, 3);
@@ -744,19 +771,22 @@ size_t scratch_bytes(const QkLayout &L, uint32_t m) {
   return make_plan_mma(L, m, &P, F::XSB) ? P.S.ximg_bytes : 0;
 }
 
+// tiled2 != nullptr: the two-matrix (feed-forward gate and up) mode, formats with F::HAS_DUAL only.
 template <class F>
 cudaError_t launch(const QkLayout &L, const uint8_t *tiled, const float *x, float *y, uint32_t m, uint64_t ldy,
-                   unsigned *status, unsigned char *scratch, int sm_count, cudaStream_t s, const QkPeers *peers) {
+                   unsigned *status, unsigned char *scratch, int sm_count, cudaStream_t s, const QkPeers *peers,
+                   const uint8_t *tiled2 = nullptr) {
   PlanMma P;
   if (!make_plan_mma(L, m, &P, F::XSB)) return cudaErrorInvalidConfiguration;
   if (m < 1 || m > (uint32_t)F::MAX_M) return cudaErrorInvalidConfiguration;
-  if (m == 1) return launch_mma_m<F, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
+  if (tiled2 && (!F::HAS_DUAL || peers)) return cudaErrorInvalidConfiguration;
+  if (m == 1) return launch_mma_m<F, 1>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers, tiled2);
   if constexpr (F::MAX_M >= 2)
-    if (m == 2) return launch_mma_m<F, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
+    if (m == 2) return launch_mma_m<F, 2>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers, tiled2);
   if constexpr (F::MAX_M >= 3)
-    if (m == 3) return launch_mma_m<F, 3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
+    if (m == 3) return launch_mma_m<F, 3>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers, tiled2);
   if constexpr (F::MAX_M >= 4)
-    if (m == 4) return launch_mma_m<F, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers);
+    if (m == 4) return launch_mma_m<F, 4>(L, tiled, x, y, ldy, status, scratch, sm_count, P, s, peers, tiled2);
   return cudaErrorInvalidConfiguration;
 }
 

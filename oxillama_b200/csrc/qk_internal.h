@@ -41,5 +41,8 @@ struct qk_ctx {
   // scratch of qk_moe_ffn_dev (routing tables and per-expert activations); grown on demand
   void *moe = nullptr;
   size_t moe_cap = 0;
+  // scratch of qk_ffn_dev (the hidden activations between the projections); grown on demand
+  void *ffn = nullptr;
+  size_t ffn_cap = 0;
 };
 

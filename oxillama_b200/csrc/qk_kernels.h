@@ -100,6 +100,13 @@ size_t qk_gemv_peer_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_peer(const QkLayout &L, const uint8_t *tiled, const float *x, uint32_t m,
                                 uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
                                 cudaStream_t s, const QkPeers *peers);
+// Gate and up projection of a feed-forward block in one launch (two matrices of the same
+// shape and format, Q4_K): h[i * ldh + j] = silu(gate_j . x_i) * (up_j . x_i).  Scratch as
+// qk_gemv_mma_scratch_bytes.
+bool qk_gemv_dual_supported(const QkLayout &L, uint32_t m);
+cudaError_t qk_launch_gemv_dual(const QkLayout &L, const uint8_t *gate_tiled, const uint8_t *up_tiled, const float *x,
+                                float *h, uint32_t m, uint64_t ldh, unsigned *status, unsigned char *scratch,
+                                int sm_count, cudaStream_t s);
 size_t qk_gemv_fast_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                                 uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
@@ -121,5 +128,7 @@ cudaError_t qk_launch_moe_lists(const int *ids, uint32_t tokens, uint32_t top_k,
 cudaError_t qk_launch_moe_gather(const float *x, const int *list, uint32_t n, uint32_t top_k,
                                  uint32_t hidden, float *xe, cudaStream_t s);
 cudaError_t qk_launch_moe_silu_mul(const float *g, float *u, uint64_t n, cudaStream_t s);
+// g <- silu(g) * u (swiglu_inplace of the dense feed-forward block)
+cudaError_t qk_launch_swiglu(float *g, const float *u, uint64_t n, cudaStream_t s);
 cudaError_t qk_launch_moe_scatter(const float *o, const int *list, const float *wts, uint32_t n,
                                   uint32_t top_k, uint32_t hidden, float *y, cudaStream_t s);

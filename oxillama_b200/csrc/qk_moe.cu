@@ -84,6 +84,16 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// g <- silu(g) * u: swiglu_inplace (crates/oxillama-arch/src/common/swiglu.rs:15-21), each step rounded
+__global__ void __launch_bounds__(256)
+    qk_swiglu_kernel(float *__restrict__ g, const float *__restrict__ u, uint64_t n) {
+  for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n; i += (uint64_t)gridDim.x * 256) {
+    const float v = g[i];
+    const float sig = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v)));
+    g[i] = __fmul_rn(__fmul_rn(v, sig), u[i]);
+  }
+}
+
 // y[token] += w * o[i]; a token occurs at most once in one expert's list.
 __global__ void __launch_bounds__(256)
     qk_moe_scatter_kernel(const float *__restrict__ o, const int *__restrict__ list,
@@ -124,6 +134,13 @@ cudaError_t qk_launch_moe_silu_mul(const float *g, float *u, uint64_t n, cudaStr
   qk_moe_silu_mul_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, s>>>(g, u, n);
   return cudaGetLastError();
 }
+cudaError_t qk_launch_swiglu(float *g, const float *u, uint64_t n, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const uint64_t blocks = (n + 255) / 256;
+  qk_swiglu_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, s>>>(g, u, n);
+  return cudaGetLastError();
+}
+
 cudaError_t qk_launch_moe_scatter(const float *o, const int *list, const float *wts, uint32_t n,
                                   uint32_t top_k, uint32_t hidden, float *y, cudaStream_t s) {
   if (n == 0) return cudaSuccess;

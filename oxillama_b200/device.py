@@ -114,3 +114,14 @@ def quantize_q8_0_dev(x: torch.Tensor, out: torch.Tensor, ctx: Context | None = 
 def check_device_status(ctx: Context | None = None, stream=None) -> None:
     ctx = ctx or default_context()
     ctx.check(ctx.lib.qk_check_device_status(ctx.handle, _stream_ptr(stream)))
+
+
+def ffn(gate: DeviceWeights, up: DeviceWeights, down: DeviceWeights, x: torch.Tensor, y: torch.Tensor, m: int = 1,
+        stream=None) -> None:
+    """y[m x down.rows] = down(silu(gate x) * up x): the dense branch of the reference's
+    `feed_forward` (crates/oxillama-arch/src/llama/model.rs:281-310) as one call (`qk_ffn_dev`)."""
+    DeviceWeights._chk(x, torch.float32, m * gate.cols, "input")
+    DeviceWeights._chk(y, torch.float32, m * down.rows, "output")
+    ctx = gate.ctx
+    ctx.check(ctx.lib.qk_ffn_dev(ctx.handle, gate.handle, up.handle, down.handle, C.c_void_p(x.data_ptr()),
+                                 C.c_void_p(y.data_ptr()), m, _stream_ptr(stream)))

@@ -137,5 +137,19 @@ def moe_ffn_f32(gate, up, down, logits, x, top_k, token_begin=0, token_end=None)
     return y
 
 
+def ffn(type_gu, gate, up, type_d, down, x, m, hidden, inter, out_rows):
+    """down(silu(gate x) * up x) for m rows of x (feed_forward's dense branch with swiglu_inplace)."""
+    gb, gp = _u8(gate)
+    ub, up_ = _u8(up)
+    db, dp = _u8(down)
+    xb, xp = _f32(x)
+    y = np.zeros((m, out_rows), np.float32)
+    scratch = np.zeros(2 * inter, np.float32)
+    st = lib().qk_oracle_ffn(C.c_int(type_gu), gp, up_, C.c_size_t(gb.size), C.c_int(type_d), dp, C.c_size_t(db.size),
+                             xp, y.ctypes.data_as(_f32p), C.c_size_t(m), C.c_size_t(hidden), C.c_size_t(inter),
+                             C.c_size_t(out_rows), scratch.ctypes.data_as(_f32p))
+    return st, y
+
+
 def f16_bits(x: float) -> int:
     return int(lib().qk_oracle_f32_to_f16(C.c_float(x)))

@@ -605,3 +605,48 @@ def test_q5_k_through_every_entry_point(K, disp):
     dw.gemv(torch.from_numpy(x).cuda(), ys)
     assert rel_inf(ys.cpu().numpy(), O.gemv(t, w, rows, cols, x)[1][8:24]) <= TOL_F32
     dw.free()
+
+
+# ---------------------------------------------------------------- the dense feed-forward block
+@pytest.mark.parametrize("tgu,td", [(S.Q4_K, S.Q6_K), (S.Q4_K, S.Q4_K), (S.Q8_0, S.Q8_0), (S.IQ4_XS, S.IQ4_XS)])
+@pytest.mark.parametrize("m", [1, 3, 9])
+def test_ffn_matches_oracle(tgu, td, m):
+    """down(silu(gate x) * up x) (llama/model.rs:281-310 with swiglu.rs:15-21): for Q4_K gate / up
+    and m <= 4 the fused two-matrix launch, else the unfused sequence; both against the oracle."""
+    import torch
+    from oxillama_b200.device import DeviceWeights, check_device_status, ffn
+    hidden, inter = 1024, 2816
+    g = S.gen_weight(tgu, inter, hidden, seed=37, stream=0, d_range=(1e-3, 3e-3))
+    u = S.gen_weight(tgu, inter, hidden, seed=37, stream=1, d_range=(1e-3, 3e-3))
+    d = S.gen_weight(td, hidden, inter, seed=37, stream=2, d_range=(1e-3, 3e-3))
+    x = S.gen_acts(m, hidden, seed=37) * np.float32(0.25)
+    st, ref = O.ffn(tgu, g, u, td, d, x, m, hidden, inter, hidden)
+    assert st == 0 and np.all(np.isfinite(ref))
+    dg, du, dd = DeviceWeights(tgu, g, inter, hidden), DeviceWeights(tgu, u, inter, hidden), DeviceWeights(td, d, hidden, inter)
+    y = torch.full((m, hidden), float("nan"), device="cuda")
+    ffn(dg, du, dd, torch.from_numpy(x).cuda(), y, m)
+    check_device_status()
+    tol = TOL if (m > 4 or (td == S.Q6_K and m > 2)) else 1e-4   # two chained stages; exp differs in the last place
+    assert rel_inf(y.cpu().numpy(), ref) <= tol, rel_inf(y.cpu().numpy(), ref)
+    for w in (dg, du, dd):
+        w.free()
+
+
+def test_ffn_layer_shape():
+    """The decoder-layer configuration's FFN (gate, up Q4_K 14336 x 4096; down Q6_K 4096 x 14336), one token."""
+    import torch
+    from oxillama_b200.device import DeviceWeights, check_device_status, ffn
+    hidden, inter = 4096, 14336
+    g = S.gen_weight(S.Q4_K, inter, hidden, seed=4, stream=4)
+    u = S.gen_weight(S.Q4_K, inter, hidden, seed=4, stream=5)
+    d = S.gen_weight(S.Q6_K, hidden, inter, seed=4, stream=6)
+    x = S.gen_acts(1, hidden, seed=4) * np.float32(0.01)   # keeps silu away from saturation on random weights
+    st, ref = O.ffn(S.Q4_K, g, u, S.Q6_K, d, x, 1, hidden, inter, hidden)
+    assert st == 0
+    dg, du, dd = DeviceWeights(S.Q4_K, g, inter, hidden), DeviceWeights(S.Q4_K, u, inter, hidden), DeviceWeights(S.Q6_K, d, hidden, inter)
+    y = torch.empty((1, hidden), device="cuda")
+    ffn(dg, du, dd, torch.from_numpy(x).cuda(), y, 1)
+    check_device_status()
+    assert rel_inf(y.cpu().numpy(), ref) <= 1e-4
+    for w in (dg, du, dd):
+        w.free()
