@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libqk_cuda.so")
 SOURCES = ["qk_api.cu", "qk_simple.cu", "qk_gemv_mma.cu", "qk_gemv_imma.cu", "qk_dec_q80.cu", "qk_dec_q40.cu",
-           "qk_dec_iq4xs.cu", "qk_dec_q6k.cu", "qk_noalloc.cu", "qk_gemm_tc.cu", "qk_moe.cu", "qk_gather.cu", "qk_gguf.cu"]
+           "qk_dec_iq4xs.cu", "qk_dec_q6k.cu", "qk_noalloc.cu", "qk_gemm_sb.cu", "qk_gemm_tc.cu", "qk_moe.cu", "qk_gather.cu", "qk_gguf.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -321,6 +321,14 @@ static int gemm_dispatch(qk_ctx *c, const qk_weights *h, const float *x, float *
                               c->sm_count, s));
     return QK_OK;
   }
+  // 5 .. 16 rows of a tall Q4_K matrix: the streaming fp16-MMA kernel (measured faster than
+  // the tcgen05 kernel from eight 8-row chunks per SM up; below that it is not)
+  if (!c->force_simple && !qk_knob("QK_NO_SB") && qk_gemm_sb_preferred(h->L, (uint32_t)m, c->sm_count)) {
+    int st = ensure_scratch(qk_gemm_sb_scratch_bytes(h->L, (uint32_t)m));
+    if (st) return st;
+    CK(c, qk_launch_gemm_sb(h->L, h->dev, x, y, (uint32_t)m, ldy, c->status_dev, c->scratch, c->sm_count, s));
+    return QK_OK;
+  }
   // The tensor-core path rounds its operands to fp16; batches the decode kernels take keep
   // f32-grade activations.  Decode-sized calls the decode kernels cannot take (K not a
   // multiple of 256, activations too long for shared memory) go to the generic kernel below.

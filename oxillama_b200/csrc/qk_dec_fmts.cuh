@@ -253,11 +253,22 @@ struct DecIQ4XS {
   // Four nibbles (the low 16 bits of s) -> their table values as four s8, in nibble order:
   // the low three bits of each nibble pick one of eight bytes from each half of the table,
   // the top bit picks the half.
-  __device__ static __forceinline__ uint32_t lookup4(uint32_t s) {
+  // `lo3` holds the low three bits of each nibble, `pick` = 0x3210 + 4 * (top bit of each nibble),
+  // both already shifted so that the four nibbles wanted sit in bits 0-15.
+  __device__ static __forceinline__ uint32_t lookup4(uint32_t lo3, uint32_t pick) {
     constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;  // K[0..15] as bytes
-    const uint32_t lo3 = s & 0x7777u;
-    const uint32_t va = __byte_perm(T0, T1, lo3), vb = __byte_perm(T2, T3, lo3);
-    return __byte_perm(va, vb, ((s >> 1) & 0x4444u) | 0x3210u);
+    uint32_t va, vb, r;  // prmt reads only bits 0-15 of its selector
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(va) : "r"(T0), "r"(T1), "r"(lo3));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(vb) : "r"(T2), "r"(T3), "r"(lo3));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(va), "r"(vb), "r"(pick));
+    return r;
+  }
+  // Eight nibbles of one word -> two fragments (elements 0-3 and 4-7): the masks are formed
+  // once for the whole word.
+  __device__ static __forceinline__ void lookup8(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const uint32_t lo3 = w & 0x77777777u, pick = ((w >> 1) & 0x44444444u) | 0x32103210u;
+    lo = lookup4(lo3, pick);
+    hi = lookup4(lo3 >> 16, pick >> 16);
   }
   template <int M>
   struct Data {
@@ -299,8 +310,8 @@ struct DecIQ4XS {
     uint32_t a[4][4];
 #pragma unroll
     for (int gq = 0; gq < 4; gq++) {
-      a[gq][0] = lookup4(D.w[2 * gq]), a[gq][2] = lookup4(D.w[2 * gq] >> 16);
-      a[gq][1] = lookup4(D.w[2 * gq + 1]), a[gq][3] = lookup4(D.w[2 * gq + 1] >> 16);
+      lookup8(D.w[2 * gq], a[gq][0], a[gq][2]);
+      lookup8(D.w[2 * gq + 1], a[gq][1], a[gq][3]);
     }
 #pragma unroll
     for (int m = 0; m < M; m++) {

@@ -318,13 +318,14 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     // warps can run ahead, which is what makes the ring of `nslot` partial
     // buffers safe without a second handshake.
     uint32_t pc = 0, pkt = 0, pst = 0;  // chunk ordinal, k-tile and stage of the next item
+    const uint64_t policy = stream_policy();
     auto issue = [&]() {                // lane 0 only
       const uint32_t chunk = blockIdx.x + (DUAL ? pc >> 1 : pc) * gridDim.x;
       const uint8_t *Wc = (DUAL && (pc & 1u)) ? W2 : W;
       const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
       const uint32_t bar = sbase + S.full + pst * 8;
       mbar_expect_tx(bar, bytes);
-      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, Wc + qk_tile_offset(L, chunk, pkt), bytes, bar);
+      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, Wc + qk_tile_offset(L, chunk, pkt), bytes, bar, policy);
       if (++pkt == L.ktiles) pkt = 0, pc++;
       if (++pst == (uint32_t)nstage) pst = 0;
     };

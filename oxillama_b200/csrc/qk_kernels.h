@@ -112,6 +112,15 @@ cudaError_t qk_launch_gemv_fast(const QkLayout &L, const uint8_t *tiled, const f
                                 uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                                 int sm_count, cudaStream_t s);
 
+// Small batches (1 .. 16 rows) of Q4_K on the fp16 mma.sync with the decode path's streaming
+// structure.  `scratch`: qk_gemm_sb_scratch_bytes(L, m) bytes.  _preferred: the shapes where
+// it was measured faster than the tcgen05 kernel (5 .. 16 rows, at least eight chunks per SM).
+bool qk_gemm_sb_supported(const QkLayout &L, uint32_t m);
+bool qk_gemm_sb_preferred(const QkLayout &L, uint32_t m, int sm_count);
+size_t qk_gemm_sb_scratch_bytes(const QkLayout &L, uint32_t m);
+cudaError_t qk_launch_gemm_sb(const QkLayout &L, const uint8_t *tiled, const float *x, float *y, uint32_t m,
+                              uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count, cudaStream_t s);
+
 // Q4_K batched matmul on tcgen05 / TMEM (any m; used for m > QK_GEMV_MAX_M).  `scratch`
 // holds the fp16 copy of the activations: qk_gemm_tc_scratch_bytes(L, m) bytes.
 bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m);

@@ -31,10 +31,16 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 // The same copy for data that is read once (weights streaming through a decode matvec):
 // marked evict-first in L2, so that it does not push out the small buffers every launch
 // re-reads (the activations, the outputs).
-__device__ __forceinline__ void bulk_g2s_stream(uint32_t dst, const void *src, uint32_t bytes,
-                                                uint32_t bar) {
+__device__ __forceinline__ uint64_t stream_policy() {
   uint64_t policy;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+// `policy` from stream_policy(), made once per thread: creating it costs the issuing thread a
+// few hundred cycles (measured: a producer loop that made one per copy issued a copy every
+// 250 ns).
+__device__ __forceinline__ void bulk_g2s_stream(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar,
+                                                uint64_t policy) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
           dst),

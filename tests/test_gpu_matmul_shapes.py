@@ -116,6 +116,56 @@ def test_prefill_config_full_band(t):
     check_against_oracle(t, rows, cols, m, seed=0, band=1024)
 
 
+# ---- 5 .. 16 tokens of a tall Q4_K matrix: the streaming fp16-MMA kernel
+# It takes over from eight 8-row chunks per SM (9472 rows on 148 SMs).  The shapes reach its
+# branches: two warps per stage and one pass (14336 rows), one warp per stage (21000 rows:
+# 18 chunks per CTA; ragged last chunk), several passes (40000 rows: 34 chunks per CTA), a
+# last slice shorter than 1024 columns (cols = 1280, 256), and token counts on both sides of
+# the 8-token half of the MMA tile.
+SMALL_BATCH = [(14336, 4096, 8), (14336, 4096, 16), (14336, 4096, 5), (21003, 1280, 11), (40000, 256, 7),
+               (9600, 512, 16), (12000, 2048, 13)]
+
+
+@pytest.mark.parametrize("rows,cols,m", SMALL_BATCH)
+def test_small_batch_streaming_kernel(rows, cols, m):
+    check_against_oracle(S.Q4_K, rows, cols, m, seed=300 + m, band=256)
+
+
+def test_small_batch_streaming_kernel_is_reproducible():
+    """One warp group owns a chunk's sums and adds its partials in a fixed order, so the
+    streaming kernel (unlike the tcgen05 matmul) gives the same bits on every run."""
+    import torch
+    rows, cols, m = 14336, 4096, 12
+    w = S.gen_weight(S.Q4_K, rows, cols, seed=9)
+    x = S.gen_acts(m, cols, seed=9)
+    dw, xd, yd, y0 = run_matmul(S.Q4_K, w, rows, cols, x, m)
+    for _ in range(3):
+        yd.fill_(float("nan"))
+        dw.gemm(xd, yd, m)
+        torch.cuda.synchronize()
+        assert np.array_equal(yd.cpu().numpy(), y0)
+    dw.free()
+
+
+def test_small_batch_outlier_and_zero_rows():
+    """Per-token power-of-two scaling: a token row of zeros, one with a 1e4 outlier and one of
+    1e-6-sized values come out at the same relative error as the rest."""
+    rows, cols, m = 14336, 4096, 8
+    w = S.gen_weight(S.Q4_K, rows, cols, seed=11)
+    x = S.gen_acts(m, cols, seed=11)
+    x[1] = 0.0
+    x[2, 77] = 1.0e4
+    x[3] *= 1.0e-6
+    dw, xd, yd, y = run_matmul(S.Q4_K, w, rows, cols, x, m)
+    wd = O.dequant_matrix(S.Q4_K, w, rows, cols)
+    ref = x.astype(np.float64) @ wd.astype(np.float64).T
+    assert np.all(y[1] == 0.0)
+    for t in range(m):
+        if t != 1:
+            assert rel_inf(y[t], ref[t]) <= (2e-3 if t == 2 else TOL), (t, rel_inf(y[t], ref[t]))
+    dw.free()
+
+
 # ---- run-to-run reproducibility
 @pytest.mark.parametrize("t", S.ALL_TYPES)
 def test_unsplit_matmul_agrees_between_runs(t):
