@@ -51,7 +51,7 @@ METRIC = "q4_k_gemv_weight_bandwidth"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the
 # ncu capture summarised in profiles/q4k_gemv_14336x4096_m1_ncu.md
-DRAM_BYTES_PER_LAUNCH = 33082112
+DRAM_BYTES_PER_LAUNCH = 33108480
 WORKLOAD = "config[1]: Q4_K 14336x4096 matvec, M=1, f32 N(0,1) activations, seed 0"
 
 
@@ -685,11 +685,19 @@ def main():
     ap.add_argument("--quick", action="store_true", help="the headline metric only (no other configurations)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="N = 1: only the batched-matmul measurements (a short run, e.g. for a profiler)")
+    ap.add_argument("--small-batch-only", action="store_true",
+                    help="N = 1: only Q4_K 14336x4096 at 8 and 16 activation rows (a short run, e.g. for a profiler)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the shard outputs reach all ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.small_batch_only:
+        import torch
+        from oxillama_b200.kernels import Context
+        torch.cuda.set_device(0)
+        ctx, stream = Context(0), torch.cuda.Stream()
+        print(json.dumps({"small_batch": matvec_rates(torch, ctx, S.Q4_K, 14336, 4096, (8, 16), stream)}))
     elif args.prefill_only:
         import torch
         from oxillama_b200.kernels import Context
