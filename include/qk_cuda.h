@@ -12,7 +12,7 @@
  *  - The caller owns every buffer; the library keeps only what it allocated
  *    itself (contexts, uploaded weights, its own scratch).
  *  - `type` is the GGUF tensor type id (crates/oxillama-gguf/src/types.rs:70-125):
- *    Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_XS = 23.
+ *    Q4_0 = 2, Q8_0 = 8, Q2_K = 10, Q3_K = 11, Q4_K = 12, Q5_K = 13, Q6_K = 14, Q8_K = 15, IQ4_XS = 23.
  *  - A weight matrix is [n_rows = out_features][n_cols = in_features], stored as
  *    n_rows consecutive rows of ceil(n_cols / block_size) blocks in GGUF byte
  *    layout (reference/q4_k.rs:110-131).  A partial last block is legal; the
@@ -51,7 +51,10 @@ typedef enum qk_status {
 #define QK_TYPE_Q4_0 2
 #define QK_TYPE_Q8_0 8
 #define QK_TYPE_Q4_K 12
-#define QK_TYPE_Q5_K 13 /* generic kernels only so far: exact, not tuned */
+#define QK_TYPE_Q5_K 13 /* Q5_K, Q2_K, Q3_K, Q8_K: generic kernels only so far (exact, not tuned) */
+#define QK_TYPE_Q2_K 10
+#define QK_TYPE_Q3_K 11
+#define QK_TYPE_Q8_K 15
 #define QK_TYPE_Q6_K 14
 #define QK_TYPE_IQ4_XS 23
 
@@ -67,7 +70,7 @@ int qk_last_error(qk_ctx *ctx, char *buf, size_t buf_len);
 /* ---- trait getters: QuantKernel::{block_size, block_bytes, name} (traits.rs:175-182) ---- */
 size_t qk_block_size(int type);   /* 0 for an unsupported type */
 size_t qk_block_bytes(int type);  /* 0 for an unsupported type */
-const char *qk_name(int type);    /* "Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "IQ4_XS", or NULL */
+const char *qk_name(int type);    /* "Q4_0", "Q8_0", "Q2_K" .. "Q6_K", "Q8_K", "IQ4_XS", or NULL */
 
 /* ================= host-pointer entry points (the trait methods) ================= */
 

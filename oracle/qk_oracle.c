@@ -39,6 +39,9 @@
 #define T_Q6_K 14
 #define T_IQ4_XS 23
 #define T_Q5_K 13
+#define T_Q2_K 10
+#define T_Q3_K 11
+#define T_Q8_K 15
 
 #define Q8_0_BLOCK_BYTES 34
 
@@ -114,9 +117,12 @@ size_t qk_oracle_block_size(int type) {
     case T_Q4_0:
     case T_Q8_0:
       return 32;
+    case T_Q2_K:
+    case T_Q3_K:
     case T_Q4_K:
     case T_Q5_K:
     case T_Q6_K:
+    case T_Q8_K:
     case T_IQ4_XS:
       return 256;
     default:
@@ -134,6 +140,12 @@ size_t qk_oracle_block_bytes(int type) {
       return 144;
     case T_Q5_K:
       return 176;
+    case T_Q2_K:
+      return 84;
+    case T_Q3_K:
+      return 110;
+    case T_Q8_K:
+      return 292;
     case T_Q6_K:
       return 210;
     case T_IQ4_XS:
@@ -247,6 +259,80 @@ static void dq_q5_k(const uint8_t *b, float *out) {
   }
 }
 
+/* reference/q2_k.rs:27-82: scales @0 (16 bytes: low nibble = scale, high nibble = min of a
+ * 16-weight sub-block), qs @16 (64 bytes, four 2-bit quants per byte), d @80, dmin @82. */
+static void dq_q2_k(const uint8_t *b, float *out) {
+  const uint8_t *scales = b, *qs = b + 16;
+  float d = rd_f16(b + 80), dmin = rd_f16(b + 82);
+  int is = 0;
+  size_t qo = 0, oo = 0;
+  for (int n = 0; n < 2; n++) {
+    for (int shift = 0; shift < 8; shift += 2) {
+      for (int h = 0; h < 2; h++) {
+        uint8_t sb = scales[is++];
+        float dl = d * (float)(sb & 0x0F);
+        float ml = dmin * (float)(sb >> 4);
+        for (int l = 0; l < 16; l++) {
+          uint8_t q = (uint8_t)((qs[qo + 16 * h + l] >> shift) & 3);
+          float t = dl * (float)q;
+          out[oo + l] = t - ml;
+        }
+        oo += 16;
+      }
+    }
+    qo += 32;
+  }
+}
+
+/* reference/q3_k.rs:29-59: sixteen 6-bit scales from 12 bytes, then -32. */
+static void decode_scales_q3_k(const uint8_t *r, float *sc) {
+  uint32_t u[16];
+  for (int j = 0; j < 4; j++) u[j] = r[j] & 0x3Fu;
+  for (int j = 0; j < 4; j++) u[4 + j] = r[4 + j] & 0x3Fu;
+  for (int j = 0; j < 4; j++) u[8 + j] = (uint32_t)(r[8 + j] & 0x0F) | (((uint32_t)(r[j] >> 6) & 3u) << 4);
+  for (int j = 0; j < 4; j++) u[12 + j] = (uint32_t)((r[8 + j] >> 4) & 0x0F) | (((uint32_t)(r[4 + j] >> 6) & 3u) << 4);
+  for (int i = 0; i < 16; i++) sc[i] = (float)((int32_t)u[i] - 32);
+}
+
+/* reference/q3_k.rs:61-121: hmask @0 (32 bytes; bit set: subtract 0, clear: subtract 4), qs @32
+ * (64 bytes, low two bits of each quant), scales @96, d @108. */
+static void dq_q3_k(const uint8_t *b, float *out) {
+  const uint8_t *hmask = b, *qs = b + 32;
+  float d = rd_f16(b + 108);
+  float sc[16];
+  decode_scales_q3_k(b + 96, sc);
+  int is = 0;
+  size_t oo = 0;
+  uint8_t m = 1;
+  for (int group = 0; group < 2; group++) {
+    size_t qs_base = (size_t)group * 32;
+    for (int shift = 0; shift < 8; shift += 2) {
+      for (int n = 0; n < 2; n++) {
+        float dl = d * sc[is++];
+        for (int l = 0; l < 16; l++) {
+          int q_lo = (qs[qs_base + (size_t)n * 16 + l] >> shift) & 3;
+          int sub = (hmask[n * 16 + l] & m) ? 0 : 4;
+          out[oo + l] = dl * (float)(q_lo - sub);
+        }
+        oo += 16;
+      }
+      m = (uint8_t)(m << 1);
+    }
+  }
+}
+
+/* reference/q8_k.rs:26-50: d (f32) @0, 256 int8 quants @4, sixteen i16 block sums @260 (unused). */
+static float rd_f32(const uint8_t *p) {
+  uint32_t u = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+static void dq_q8_k(const uint8_t *b, float *out) {
+  float d = rd_f32(b);
+  for (int i = 0; i < 256; i++) out[i] = d * (float)(int8_t)b[4 + i];
+}
+
 /* reference/q6_k.rs:25-75 */
 static void dq_q6_k(const uint8_t *b, float *out) {
   const uint8_t *ql = b, *qh = b + 128, *scales = b + 192;
@@ -303,6 +389,15 @@ int qk_oracle_dequant_block(int type, const uint8_t *block, size_t block_len, fl
       break;
     case T_Q4_K:
       dq_q4_k(block, out);
+      break;
+    case T_Q2_K:
+      dq_q2_k(block, out);
+      break;
+    case T_Q3_K:
+      dq_q3_k(block, out);
+      break;
+    case T_Q8_K:
+      dq_q8_k(block, out);
       break;
     case T_Q5_K:
       dq_q5_k(block, out);
@@ -424,6 +519,94 @@ int qk_oracle_dequant_matrix(int type, const uint8_t *w, size_t w_len, size_t n_
         qo += 32;                                                                              \
         wo += 64;                                                                              \
       }                                                                                        \
+    }                                                                                          \
+    return (float)sum;                                                                         \
+  }                                                                                            \
+  /* reference/q2_k.rs:84-166 */                                                               \
+  static float row_q2_k##SUFFIX(const uint8_t *row, size_t bpr, size_t n_cols, const float *x) {\
+    ACC sum = 0;                                                                               \
+    for (size_t blk = 0; blk < bpr; blk++) {                                                   \
+      const uint8_t *b = row + blk * 84;                                                       \
+      const uint8_t *scales = b, *qs = b + 16;                                                 \
+      float d = rd_f16(b + 80), dmin = rd_f16(b + 82);                                         \
+      int is = 0;                                                                              \
+      size_t qo = 0, wo = blk * 256;                                                           \
+      for (int n = 0; n < 2; n++) {                                                            \
+        for (int shift = 0; shift < 8; shift += 2) {                                           \
+          for (int h = 0; h < 2; h++) {                                                        \
+            uint8_t sb = scales[is++];                                                         \
+            float dl = d * (float)(sb & 0x0F);                                                 \
+            float ml = dmin * (float)(sb >> 4);                                                \
+            for (int l = 0; l < 16; l++) {                                                     \
+              size_t idx = wo + (size_t)l;                                                     \
+              if (idx < n_cols) {                                                              \
+                uint8_t q = (uint8_t)((qs[qo + 16 * h + l] >> shift) & 3);                     \
+                float t = dl * (float)q;                                                       \
+                float w = t - ml;                                                              \
+                float p = w * x[idx];                                                          \
+                sum += p;                                                                      \
+              }                                                                                \
+            }                                                                                  \
+            wo += 16;                                                                          \
+          }                                                                                    \
+        }                                                                                      \
+        qo += 32;                                                                              \
+      }                                                                                        \
+    }                                                                                          \
+    return (float)sum;                                                                         \
+  }                                                                                            \
+  /* reference/q3_k.rs:123-199 */                                                              \
+  static float row_q3_k##SUFFIX(const uint8_t *row, size_t bpr, size_t n_cols, const float *x) {\
+    ACC sum = 0;                                                                               \
+    for (size_t blk = 0; blk < bpr; blk++) {                                                   \
+      const uint8_t *b = row + blk * 110;                                                      \
+      const uint8_t *hmask = b, *qs = b + 32;                                                  \
+      float d = rd_f16(b + 108);                                                               \
+      float sc[16];                                                                            \
+      decode_scales_q3_k(b + 96, sc);                                                          \
+      int is = 0;                                                                              \
+      size_t wo = blk * 256;                                                                   \
+      uint8_t m = 1;                                                                           \
+      for (int group = 0; group < 2; group++) {                                                \
+        size_t qs_base = (size_t)group * 32;                                                   \
+        for (int shift = 0; shift < 8; shift += 2) {                                           \
+          for (int n = 0; n < 2; n++) {                                                        \
+            float dl = d * sc[is++];                                                           \
+            for (int l = 0; l < 16; l++) {                                                     \
+              size_t idx = wo + (size_t)l;                                                     \
+              if (idx < n_cols) {                                                              \
+                int q_lo = (qs[qs_base + (size_t)n * 16 + l] >> shift) & 3;                    \
+                int sub = (hmask[n * 16 + l] & m) ? 0 : 4;                                     \
+                float w = dl * (float)(q_lo - sub);                                            \
+                float p = w * x[idx];                                                          \
+                sum += p;                                                                      \
+              }                                                                                \
+            }                                                                                  \
+            wo += 16;                                                                          \
+          }                                                                                    \
+          m = (uint8_t)(m << 1);                                                               \
+        }                                                                                      \
+      }                                                                                        \
+    }                                                                                          \
+    return (float)sum;                                                                         \
+  }                                                                                            \
+  /* reference/q8_k.rs:52-101: the quants of a block are summed against x first, the block     \
+   * scale applied once.  (The reference walks all 256 quants of every block; it is defined    \
+   * only when n_cols is a multiple of 256, and columns beyond n_cols are skipped here.) */    \
+  static float row_q8_k##SUFFIX(const uint8_t *row, size_t bpr, size_t n_cols, const float *x) {\
+    ACC sum = 0;                                                                               \
+    for (size_t blk = 0; blk < bpr; blk++) {                                                   \
+      const uint8_t *b = row + blk * 292;                                                      \
+      float d = rd_f32(b);                                                                     \
+      ACC block_sum = 0;                                                                       \
+      for (int i = 0; i < 256; i++) {                                                          \
+        size_t idx = blk * 256 + (size_t)i;                                                    \
+        if (idx < n_cols) {                                                                    \
+          float p = (float)(int8_t)b[4 + i] * x[idx];                                          \
+          block_sum += p;                                                                      \
+        }                                                                                      \
+      }                                                                                        \
+      sum += (ACC)((ACC)d * block_sum);                                                        \
     }                                                                                          \
     return (float)sum;                                                                         \
   }                                                                                            \
@@ -567,6 +750,12 @@ static row_fn pick_row(int type, int wide) {
       return wide ? row_q4_k_f64 : row_q4_k_f32;
     case T_Q5_K:
       return wide ? row_q5_k_f64 : row_q5_k_f32;
+    case T_Q2_K:
+      return wide ? row_q2_k_f64 : row_q2_k_f32;
+    case T_Q3_K:
+      return wide ? row_q3_k_f64 : row_q3_k_f32;
+    case T_Q8_K:
+      return wide ? row_q8_k_f64 : row_q8_k_f32;
     case T_Q6_K:
       return wide ? row_q6_k_f64 : row_q6_k_f32;
     case T_IQ4_XS:
@@ -740,6 +929,116 @@ static float fused_row_q4_k(const uint8_t *row, size_t bpr, size_t n_cols, const
   return sum;
 }
 
+/* reference/q2_k.rs:187-297: per 16-weight sub-block (dl * dot - ml * sum_a) * d_a, sums in f32. */
+static float fused_row_q2_k(const uint8_t *row, size_t bpr, size_t n_cols, const uint8_t *acts) {
+  float sum = 0.0f;
+  for (size_t blk = 0; blk < bpr; blk++) {
+    const uint8_t *b = row + blk * 84;
+    const uint8_t *scales = b, *qs = b + 16;
+    float d = rd_f16(b + 80), dmin = rd_f16(b + 82);
+    size_t left = n_cols > blk * 256 ? n_cols - blk * 256 : 0;  /* n_cols.saturating_sub(blk * 256) */
+    int is = 0;
+    size_t qo = 0, col_off = 0;
+    for (int group = 0; group < 2; group++) {
+      for (int shift = 0; shift < 8; shift += 2) {
+        for (int h = 0; h < 2; h++) {
+          uint8_t sb = scales[is++];
+          float dl = d * (float)(sb & 0x0F);
+          float ml = dmin * (float)(sb >> 4);
+          const uint8_t *a = acts + (blk * 8 + col_off / 32) * Q8_0_BLOCK_BYTES;
+          size_t lane = col_off % 32;
+          float d_a = rd_f16(a);
+          float dot = 0.0f, sum_a = 0.0f;
+          for (int l = 0; l < 16; l++) {
+            if (col_off + (size_t)l < left) {
+              float q2 = (float)(uint8_t)((qs[qo + 16 * h + l] >> shift) & 3);
+              float q_a = (float)(int8_t)a[2 + lane + l];
+              float p = q2 * q_a;
+              dot += p;
+              sum_a += q_a;
+            }
+          }
+          float t1 = dl * dot, t2 = ml * sum_a;
+          float t = t1 - t2;
+          t = t * d_a;
+          sum += t;
+          col_off += 16;
+        }
+      }
+      qo += 32;
+    }
+  }
+  return sum;
+}
+
+/* reference/q3_k.rs:217-336: per 16-weight sub-block dl * dot * d_a, sums in f32. */
+static float fused_row_q3_k(const uint8_t *row, size_t bpr, size_t n_cols, const uint8_t *acts) {
+  float sum = 0.0f;
+  for (size_t blk = 0; blk < bpr; blk++) {
+    const uint8_t *b = row + blk * 110;
+    const uint8_t *hmask = b, *qs = b + 32;
+    float d = rd_f16(b + 108);
+    float sc[16];
+    decode_scales_q3_k(b + 96, sc);
+    size_t left = n_cols > blk * 256 ? n_cols - blk * 256 : 0;
+    if (left > 256) left = 256;
+    int is = 0;
+    size_t col_off = 0;
+    uint8_t m = 1;
+    for (int group = 0; group < 2; group++) {
+      size_t qs_base = (size_t)group * 32;
+      for (int shift = 0; shift < 8; shift += 2) {
+        for (int n = 0; n < 2; n++) {
+          float dl = d * sc[is++];
+          const uint8_t *a = acts + (blk * 8 + col_off / 32) * Q8_0_BLOCK_BYTES;
+          size_t lane = col_off % 32;
+          float d_a = rd_f16(a);
+          float dot = 0.0f;
+          for (int l = 0; l < 16; l++) {
+            if (col_off + (size_t)l < left) {
+              int q_lo = (qs[qs_base + (size_t)n * 16 + l] >> shift) & 3;
+              int sub = (hmask[n * 16 + l] & m) ? 0 : 4;
+              float q3 = (float)(q_lo - sub);
+              float q_a = (float)(int8_t)a[2 + lane + l];
+              float p = q3 * q_a;
+              dot += p;
+            }
+          }
+          float t = dl * dot;
+          t = t * d_a;
+          sum += t;
+          col_off += 16;
+        }
+        m = (uint8_t)(m << 1);
+      }
+    }
+  }
+  return sum;
+}
+
+/* Q8_K has no override of matvec_q8_fused, and the trait default (traits.rs:89-173) pairs one
+ * weight block with one 32-value activation block, which for a 256-weight block reads past
+ * that block (a panic in the reference): undefined there, PARITY UNPINNED.  Here, by analogy
+ * with the default's arithmetic: eight activation blocks per weight block, the dequantised
+ * weight times the dequantised activation (q_a * d_a), summed in f32 in column order. */
+static float fused_row_q8_k(const uint8_t *row, size_t bpr, size_t n_cols, const uint8_t *acts) {
+  float sum = 0.0f;
+  float w[256];
+  for (size_t blk = 0; blk < bpr; blk++) {
+    dq_q8_k(row + blk * 292, w);
+    for (int i = 0; i < 256; i++) {
+      size_t idx = blk * 256 + (size_t)i;
+      if (idx < n_cols) {
+        const uint8_t *a = acts + (idx / 32) * Q8_0_BLOCK_BYTES;
+        float av = (float)(int8_t)a[2 + idx % 32] * rd_f16(a);
+        float p = w[i] * av;
+        sum += p;
+      }
+    }
+  }
+  return sum;
+}
+
 /* reference/q5_k.rs:236-347: per sub-block (da * dot - m * sum_a) * d_a, sums in f32. */
 static float fused_row_q5_k(const uint8_t *row, size_t bpr, size_t n_cols, const uint8_t *acts) {
   float sum = 0.0f;
@@ -881,6 +1180,15 @@ int qk_oracle_matvec_q8_fused(int type, const uint8_t *w, size_t w_len, const ui
         break;
       case T_Q5_K:
         s = fused_row_q5_k(row, bpr, n_cols, acts);
+        break;
+      case T_Q2_K:
+        s = fused_row_q2_k(row, bpr, n_cols, acts);
+        break;
+      case T_Q3_K:
+        s = fused_row_q3_k(row, bpr, n_cols, acts);
+        break;
+      case T_Q8_K:
+        s = fused_row_q8_k(row, bpr, n_cols, acts);
         break;
       case T_Q6_K:
         s = fused_row_q6_k(row, bpr, n_cols, acts);

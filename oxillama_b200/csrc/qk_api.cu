@@ -25,7 +25,7 @@
 
 static bool type_ok(int t) {
   return t == QK_TYPE_Q4_0 || t == QK_TYPE_Q8_0 || t == QK_TYPE_Q4_K || t == QK_TYPE_Q5_K || t == QK_TYPE_Q6_K ||
-         t == QK_TYPE_IQ4_XS;
+         t == QK_TYPE_IQ4_XS || t == QK_TYPE_Q2_K || t == QK_TYPE_Q3_K || t == QK_TYPE_Q8_K;
 }
 
 extern "C" size_t qk_block_size(int type) {
@@ -33,9 +33,12 @@ extern "C" size_t qk_block_size(int type) {
     case QK_TYPE_Q4_0:
     case QK_TYPE_Q8_0:
       return 32;
+    case QK_TYPE_Q2_K:
+    case QK_TYPE_Q3_K:
     case QK_TYPE_Q4_K:
     case QK_TYPE_Q5_K:
     case QK_TYPE_Q6_K:
+    case QK_TYPE_Q8_K:
     case QK_TYPE_IQ4_XS:
       return 256;
     default:
@@ -53,6 +56,12 @@ extern "C" size_t qk_block_bytes(int type) {
       return 144;
     case QK_TYPE_Q5_K:
       return 176;
+    case QK_TYPE_Q2_K:
+      return 84;
+    case QK_TYPE_Q3_K:
+      return 110;
+    case QK_TYPE_Q8_K:
+      return 292;
     case QK_TYPE_Q6_K:
       return 210;
     case QK_TYPE_IQ4_XS:
@@ -72,6 +81,12 @@ extern "C" const char *qk_name(int type) {
       return "Q4_K";
     case QK_TYPE_Q5_K:
       return "Q5_K";
+    case QK_TYPE_Q2_K:
+      return "Q2_K";
+    case QK_TYPE_Q3_K:
+      return "Q3_K";
+    case QK_TYPE_Q8_K:
+      return "Q8_K";
     case QK_TYPE_Q6_K:
       return "Q6_K";
     case QK_TYPE_IQ4_XS:

@@ -66,6 +66,35 @@ __device__ __forceinline__ float qk_dequant_elem(const QkLayout &L, const uint8_
       float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
       return __fsub_rn(__fmul_rn(d1, (float)q), m1);
     }
+    case QK_T_Q2_K: {  // reference/q2_k.rs:42-79: sub-block is = 8 n + 2 j + h of 16 weights, shift 2 j
+      const uint8_t *dm = at(2, 0);
+      float d = qk_h2f(dm), dmin = qk_h2f(dm + 2);
+      int n = i >> 7, r = i & 127, j = r >> 5, h = (r >> 4) & 1, l = r & 15;
+      uint8_t sb = *at(0, 8 * n + 2 * j + h);
+      int q = (*at(1, 32 * n + 16 * h + l) >> (2 * j)) & 3;
+      float dl = __fmul_rn(d, (float)(sb & 0x0F)), ml = __fmul_rn(dmin, (float)(sb >> 4));
+      return __fsub_rn(__fmul_rn(dl, (float)q), ml);
+    }
+    case QK_T_Q3_K: {  // reference/q3_k.rs:29-59 (scales), :79-118 (weights)
+      float d = qk_h2f(at(3, 0));
+      int grp = i >> 7, r = i & 127, j = r >> 5, n = (r >> 4) & 1, l = r & 15, is = 8 * grp + 2 * j + n;
+      int raw;
+      if (is < 8) {
+        raw = *at(2, is) & 0x3F;
+      } else if (is < 12) {
+        raw = (*at(2, is) & 0x0F) | (((*at(2, is - 8) >> 6) & 3) << 4);
+      } else {
+        raw = ((*at(2, is - 4) >> 4) & 0x0F) | (((*at(2, is - 8) >> 6) & 3) << 4);
+      }
+      int q_lo = (*at(1, 32 * grp + 16 * n + l) >> (2 * j)) & 3;
+      int sub = ((*at(0, 16 * n + l) >> (4 * grp + j)) & 1) ? 0 : 4;
+      float dl = __fmul_rn(d, (float)(raw - 32));
+      return __fmul_rn(dl, (float)(q_lo - sub));
+    }
+    case QK_T_Q8_K: {  // reference/q8_k.rs:40-47
+      float d = *reinterpret_cast<const float *>(at(0, 0));
+      return __fmul_rn(d, (float)(int8_t)*at(1, i));
+    }
     case QK_T_Q6_K: {  // reference/q6_k.rs:39-71
       const uint8_t *sc = at(1, 0);
       float d = qk_h2f(at(2, 0));

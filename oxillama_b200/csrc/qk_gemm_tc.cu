@@ -962,7 +962,13 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_blocks, row_blocks, ks, status, S);
 }
 
-int pick_bn(uint32_t m) { return m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
+int pick_bn(uint32_t m) {
+  if (const char *e = qk_knob("QK_GEMM_BN")) {  // developer knob: force the token-tile width
+    const int v = atoi(e);
+    if (v == 32 || v == 64 || v == 128 || v == 256) return v;
+  }
+  return m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
+}
 
 template <int T>
 cudaError_t launch_fmt(const QkLayout &L, const uint8_t *tiled, const float *x, float *y, uint32_t m,

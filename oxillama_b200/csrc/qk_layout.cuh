@@ -19,6 +19,9 @@
 //     Q6_K   ql+qh  192 B (g 16) | scales 16 B (g 16) | d 2 B (g 2)      8 x 210 = 1680 B
 //     IQ4_XS nibbles 128 B (g 16)         | d,scales_h,scales_l 8 B (g 8) 8 x 136 = 1088 B
 //     Q5_K   d,dmin,scales 16 B (g 16) | qh 32 B (g 32) | nibbles 128 B (g 32)  8 x 176 = 1408 B
+//     Q2_K   scales 16 B (g 16) | qs 64 B (g 16) | d,dmin 4 B (g 4)             8 x 84 = 672 B
+//     Q3_K   hmask 32 B (g 16) | qs 64 B (g 16) | scales 12 B (g 4) | d 2 B (g 2)  8 x 110 = 880 B
+//     Q8_K   d 4 B (g 4) | qs 256 B (g 16) | bsums 32 B (g 16)                  8 x 292 = 2336 B
 //
 //   The same 16- or 32-byte group of all 8 rows lies in one 128- or 256-byte
 //   span: eight lanes that hold the eight rows read it from HBM as full sectors
@@ -46,6 +49,9 @@
 #define QK_T_Q6_K 14
 #define QK_T_IQ4_XS 23
 #define QK_T_Q5_K 13
+#define QK_T_Q2_K 10
+#define QK_T_Q3_K 11
+#define QK_T_Q8_K 15
 
 struct QkLayout {
   int type;
@@ -54,9 +60,9 @@ struct QkLayout {
   uint32_t nbt;          // blocks per full k-tile
   uint32_t ktiles;       // k-tiles per chunk
   uint32_t nplanes;
-  uint32_t pw[3];        // plane widths, bytes per block
-  uint32_t po[3];        // offset of the plane's field inside the GGUF block
-  uint32_t pg[3];        // 0: row-major plane; g > 0: interleaved with granule g bytes
+  uint32_t pw[4];        // plane widths, bytes per block
+  uint32_t po[4];        // offset of the plane's field inside the GGUF block
+  uint32_t pg[4];        // 0: row-major plane; g > 0: interleaved with granule g bytes
   uint32_t bm;           // 1: block-major tile (every plane interleaved, planes of a block adjacent)
   uint32_t rows, cols;   // logical shape of this shard
   uint32_t chunks;       // ceil(rows / 8)
@@ -88,6 +94,24 @@ static inline bool qk_make_layout(int type, uint64_t rows, uint64_t cols, QkLayo
       l.bs = 256; l.bb = 176; l.nplanes = 3;
       l.pw[0] = 16; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 32; l.po[1] = 16; l.pg[1] = 32;
       l.pw[2] = 128; l.po[2] = 48; l.pg[2] = 32;
+      l.bm = 1;
+      break;
+    case QK_T_Q2_K:  // scales 16 B | qs 64 B | d, dmin 4 B
+      l.bs = 256; l.bb = 84; l.nplanes = 3;
+      l.pw[0] = 16; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 64; l.po[1] = 16; l.pg[1] = 16;
+      l.pw[2] = 4; l.po[2] = 80; l.pg[2] = 4;
+      l.bm = 1;
+      break;
+    case QK_T_Q3_K:  // hmask 32 B | qs 64 B | scales 12 B | d 2 B
+      l.bs = 256; l.bb = 110; l.nplanes = 4;
+      l.pw[0] = 32; l.po[0] = 0; l.pg[0] = 16; l.pw[1] = 64; l.po[1] = 32; l.pg[1] = 16;
+      l.pw[2] = 12; l.po[2] = 96; l.pg[2] = 4; l.pw[3] = 2; l.po[3] = 108; l.pg[3] = 2;
+      l.bm = 1;
+      break;
+    case QK_T_Q8_K:  // d (f32) 4 B | qs 256 B | bsums 32 B
+      l.bs = 256; l.bb = 292; l.nplanes = 3;
+      l.pw[0] = 4; l.po[0] = 0; l.pg[0] = 4; l.pw[1] = 256; l.po[1] = 4; l.pg[1] = 16;
+      l.pw[2] = 32; l.po[2] = 260; l.pg[2] = 16;
       l.bm = 1;
       break;
     case QK_T_Q6_K:

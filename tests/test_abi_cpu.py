@@ -36,11 +36,11 @@ def test_exports_every_declared_symbol(lib):
 
 def test_trait_getters_need_no_gpu(lib):
     # crates/oxillama-gguf/src/types.rs:199-259
-    for t in S.ALL_TYPES + (S.Q5_K,):
+    for t in S.ALL_TYPES + S.NEXT_TYPES:
         assert lib.qk_block_size(t) == S.BLOCK_SIZE[t]
         assert lib.qk_block_bytes(t) == S.BLOCK_BYTES[t]
         assert lib.qk_name(t).decode() == S.NAMES[t]
-    assert lib.qk_block_size(10) == 0 and lib.qk_name(10) is None   # Q2_K: not served
+    assert lib.qk_block_size(16) == 0 and lib.qk_name(16) is None   # IQ2_XXS: not served
 
 
 def test_no_cpu_fallback(lib):

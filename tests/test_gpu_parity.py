@@ -294,7 +294,7 @@ def test_error_codes(K, disp):
         k.gemv(K.QuantTensor(blk[:10], (1, 32), S.Q4_0), np.zeros(32, np.float32), np.zeros(1, np.float32))
     assert e.value.kind == "BufferTooSmall"
     with pytest.raises(K.QuantError) as e:
-        disp.get_kernel(10)  # Q2_K: not part of this backend
+        disp.get_kernel(16)  # IQ2_XXS: not part of this backend
     assert e.value.kind == "UnsupportedType"
     k4 = disp.get_kernel(S.Q4_K)
     w = S.gen_weight(S.Q4_K, 2, 256, seed=1)
@@ -568,20 +568,33 @@ def test_upload_from_gguf_file(tmp_path):
     g2.close()
 
 
-# ---------------------------------------------------------------- Q5_K (generic kernels: exact, not tuned)
-def test_q5_k_through_every_entry_point(K, disp):
-    """reference/q5_k.rs: dequant bit-exact, gemv / gemm / fused against the oracle, the reference's
-    known answers (q5_k.rs:376-440) through the GPU, a row shard on the device."""
+# ---------------------------------------------------------------- Q5_K, Q2_K, Q3_K, Q8_K (generic kernels: exact, not tuned)
+def _next_kat(t):
+    """One known answer of the reference's own tests per format: (block, expected value of all 256 weights)."""
+    if t == S.Q5_K:   # reference/q5_k.rs:376-440
+        return np.concatenate([f16b(1.0), f16b(0.0), np.array([1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1], np.uint8),
+                               np.full(32, 0xFF, np.uint8), np.zeros(128, np.uint8)]), 16.0
+    if t == S.Q2_K:   # reference/q2_k.rs:362-380
+        return np.concatenate([np.full(16, 0x11, np.uint8), np.zeros(64, np.uint8), f16b(2.0), f16b(1.0)]), -1.0
+    if t == S.Q3_K:   # reference/q3_k.rs:400-433
+        return np.concatenate([np.zeros(32, np.uint8), np.zeros(64, np.uint8),
+                               np.array([0xA1] * 8 + [0x11] * 4, np.uint8), f16b(1.0)]), -4.0
+    return np.concatenate([np.array([0.25], np.float32).view(np.uint8), np.full(256, 40, np.uint8),   # reference/q8_k.rs:161-170
+                           np.zeros(32, np.uint8)]), 10.0
+
+
+@pytest.mark.parametrize("t", S.NEXT_TYPES)
+def test_next_formats_through_every_entry_point(K, disp, t):
+    """reference/{q5_k,q2_k,q3_k,q8_k}.rs: dequant bit-exact, gemv / gemm / fused against the oracle,
+    one of the reference's known answers through the GPU, a row shard on the device."""
     import torch
     from oxillama_b200.device import DeviceWeights
-    t = S.Q5_K
     k = disp.get_kernel(t)
-    assert (k.block_size(), k.block_bytes(), k.name()) == (256, 176, "Q5_K")
-    sc1 = [1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]
+    assert (k.block_size(), k.block_bytes(), k.name()) == (256, S.BLOCK_BYTES[t], S.NAMES[t])
+    blk, want = _next_kat(t)
     out = np.empty(256, np.float32)
-    k.dequant_block(np.concatenate([f16b(1.0), f16b(0.0), np.array(sc1, np.uint8), np.full(32, 0xFF, np.uint8),
-                                    np.zeros(128, np.uint8)]), out)
-    assert np.all(out == 16.0)
+    k.dequant_block(blk, out)
+    assert np.all(out == want)
     for rows, cols in ((19, 768), (5, 256 + 128 + 3), (33, 4096)):
         w = S.gen_weight(t, rows, cols, seed=35)
         dq = np.empty((rows, cols), np.float32)

@@ -94,6 +94,126 @@ def test_q5_k_fused_matches_unfused():  # reference/q5_k.rs:236-347 vs :137-189
     assert np.abs(out - y).max() / np.abs(y).max() < 2e-2   # activations rounded to 8 bits
 
 
+# ------------------------------------------------------------------ Q2_K, Q3_K, Q8_K ("next" formats: generic kernels)
+def q2_k_block(d, dmin, scales, qs):   # reference/q2_k.rs:323-330
+    return np.concatenate([np.asarray(scales, np.uint8), np.asarray(qs, np.uint8), f16b(d), f16b(dmin)])
+
+
+def q3_k_block(d, scales, hmask, qs):   # reference/q3_k.rs:357-364
+    return np.concatenate([np.asarray(hmask, np.uint8), np.asarray(qs, np.uint8), np.asarray(scales, np.uint8), f16b(d)])
+
+
+def q8_k_block(d, qs):   # reference/q8_k.rs:138-147
+    return np.concatenate([np.array([d], np.float32).view(np.uint8), np.asarray(qs, np.int8).view(np.uint8),
+                           np.zeros(32, np.uint8)])
+
+
+RAMP = (np.arange(256, dtype=np.float32) * np.float32(0.01)) - np.float32(1.28)
+Q3_SC1 = [0xA1] * 8 + [0x11] * 4   # all sixteen scales decode to +1 (raw 33), reference/q3_k.rs:405-421
+
+
+def test_q2_k_dequant():  # reference/q2_k.rs:333-380
+    st, out = O.dequant_block(S.Q2_K, q2_k_block(0.0, 0.0, [0] * 16, [0] * 64))
+    assert st == OK and np.all(out == 0.0)
+    st, out = O.dequant_block(S.Q2_K, q2_k_block(1.0, 0.0, [0x01] * 16, [0xFF] * 64))
+    assert st == OK and np.all(out == 3.0)
+    st, out = O.dequant_block(S.Q2_K, q2_k_block(2.0, 1.0, [0x11] * 16, [0x00] * 64))
+    assert st == OK and np.all(out == -1.0)
+
+
+def test_q2_k_element_order():  # reference/q2_k.rs:50-79: byte l of a 32-byte half holds weights l, 32 + l, 64 + l, 96 + l
+    for byte in (0, 17, 40, 63):
+        for shift in range(4):
+            qs = [0] * 64
+            qs[byte] = 3 << (2 * shift)
+            st, out = O.dequant_block(S.Q2_K, q2_k_block(1.0, 0.0, [0x01] * 16, qs))
+            want = np.zeros(256, np.float32)
+            want[128 * (byte // 32) + 32 * shift + byte % 32] = 3.0
+            assert st == OK and np.array_equal(out, want), (byte, shift)
+
+
+def test_q2_k_gemv_matches_dequant_dot():  # reference/q2_k.rs:382-414
+    blk = q2_k_block(0.5, 0.25, [0x21 + i for i in range(16)], [(i * 3 + 7) & 0xFF for i in range(64)])
+    st, dq = O.dequant_block(S.Q2_K, blk)
+    st, y = O.gemv(S.Q2_K, blk, 1, 256, RAMP)
+    assert st == OK and abs(float(y[0]) - float((dq * RAMP).sum())) < 0.1
+
+
+def test_q3_k_dequant():  # reference/q3_k.rs:366-458
+    st, out = O.dequant_block(S.Q3_K, q3_k_block(0.0, [0] * 12, [0] * 32, [0] * 64))
+    assert st == OK and np.all(out == 0.0)
+    st, out = O.dequant_block(S.Q3_K, q3_k_block(1.0, [0x21] * 8 + [0] * 4, [0xFF] * 32, [0] * 64))
+    assert st == OK and np.all(np.abs(out) < 0.01)
+    st, out = O.dequant_block(S.Q3_K, q3_k_block(1.0, Q3_SC1, [0x00] * 32, [0x00] * 64))
+    assert st == OK and np.all(out == -4.0)
+    st, out = O.dequant_block(S.Q3_K, q3_k_block(1.0, Q3_SC1, [0xFF] * 32, [0xFF] * 64))
+    assert st == OK and np.all(out == 3.0)
+
+
+def test_q3_k_mask_bit_and_scale_positions():  # reference/q3_k.rs:29-59, :100-117
+    # bit b of hmask byte k covers weight 32 b + k
+    for bit in range(8):
+        st, out = O.dequant_block(S.Q3_K, q3_k_block(1.0, Q3_SC1, [1 << bit] * 32, [0] * 64))
+        want = np.full(256, -4.0, np.float32)
+        want[32 * bit: 32 * bit + 32] = 0.0
+        assert st == OK and np.array_equal(out, want), bit
+    # sub-block i of 16 weights takes scale i: raw value 32 + (i + 1) packed per the 12-byte layout
+    raw = [33 + i for i in range(16)]
+    r = [0] * 12
+    for j in range(4):
+        r[j] = (raw[j] & 0x3F) | ((raw[8 + j] >> 4) << 6)
+        r[4 + j] = (raw[4 + j] & 0x3F) | ((raw[12 + j] >> 4) << 6)
+        r[8 + j] = (raw[8 + j] & 0x0F) | ((raw[12 + j] & 0x0F) << 4)
+    st, out = O.dequant_block(S.Q3_K, q3_k_block(1.0, r, [0xFF] * 32, [0x55] * 64))   # every quant = 1
+    assert st == OK and np.array_equal(out, np.repeat(np.arange(1, 17, dtype=np.float32), 16))
+
+
+def test_q3_k_gemv_matches_dequant_dot():  # reference/q3_k.rs:460-501
+    blk = q3_k_block(0.5, Q3_SC1, [(i * 7 + 3) & 0xFF for i in range(32)], [(i * 11 + 5) & 0xFF for i in range(64)])
+    st, dq = O.dequant_block(S.Q3_K, blk)
+    st, y = O.gemv(S.Q3_K, blk, 1, 256, RAMP)
+    assert st == OK and abs(float(y[0]) - float((dq * RAMP).sum())) < 0.1
+
+
+def test_q8_k_dequant_and_gemv():  # reference/q8_k.rs:150-217
+    st, out = O.dequant_block(S.Q8_K, q8_k_block(0.0, [0] * 256))
+    assert st == OK and np.all(out == 0.0)
+    st, out = O.dequant_block(S.Q8_K, q8_k_block(0.25, [40] * 256))
+    assert st == OK and np.all(out == 10.0)
+    st, out = O.dequant_block(S.Q8_K, q8_k_block(1.0, [-100] * 256))
+    assert st == OK and np.all(out == -100.0)
+    blk = q8_k_block(0.25, [max(-128, min(127, i * 3 - 128)) for i in range(256)])
+    st, dq = O.dequant_block(S.Q8_K, blk)
+    st, y = O.gemv(S.Q8_K, blk, 1, 256, RAMP)
+    assert st == OK and abs(float(y[0]) - float((dq * RAMP).sum())) < 0.1
+
+
+@pytest.mark.parametrize("t", [S.Q2_K, S.Q3_K, S.Q8_K])
+def test_next_formats_fused_matches_unfused(t):  # reference/q2_k.rs:187-297, q3_k.rs:217-336 against their gemv
+    w = S.gen_weight(t, 3, 512, seed=13)
+    x = S.gen_acts(1, 512, seed=13)[0]
+    st, a = O.quantize_q8_0(x)
+    st, out = O.matvec_q8_fused(t, w, a, np.zeros(3, np.float32), 3, 512)
+    st2, y = O.gemv(t, w, 3, 512, x)
+    assert st == OK and st2 == OK
+    assert np.abs(out - y).max() / np.abs(y).max() < 3e-2   # activations rounded to 8 bits
+
+
+@pytest.mark.parametrize("t", [S.Q2_K, S.Q3_K, S.Q8_K])
+def test_next_formats_row_dot_against_numpy(t):
+    """gemv against an independent numpy product of the oracle's own dequantised blocks (f64),
+    full and ragged column counts."""
+    for rows, cols in ((4, 768), (3, 256 + 100)):
+        w = S.gen_weight(t, rows, cols, seed=14)
+        x = S.gen_acts(1, cols, seed=14)[0]
+        bpr = S.blocks_per_row(t, cols)
+        dq = np.stack([np.concatenate([O.dequant_block(t, w[(r * bpr + b) * S.BLOCK_BYTES[t]:(r * bpr + b + 1) * S.BLOCK_BYTES[t]])[1]
+                                       for b in range(bpr)])[:cols] for r in range(rows)])
+        st, y = O.gemv(t, w, rows, cols, x)
+        ref = dq.astype(np.float64) @ x.astype(np.float64)
+        assert st == OK and np.abs(y - ref).max() / np.abs(ref).max() < 1e-5
+
+
 # ------------------------------------------------------------------ Q4_0
 def test_q4_0_dequant_zeros():  # reference/q4_0.rs:246-256
     st, out = O.dequant_block(S.Q4_0, q4_0_block(1.0, [0x88] * 16))
@@ -337,7 +457,7 @@ def test_iq4_xs_table_and_interleave():  # reference/iq_shared.rs:16-18, iq4_xs.
 # ------------------------------------------------------------------ unsupported / shapes
 def test_unsupported_type():
     assert O.dequant_block(3, np.zeros(64, np.uint8), out_len=32)[0] == UNSUPPORTED
-    assert O.gemv(10, np.zeros(84, np.uint8), 1, 256, np.zeros(256, np.float32))[0] == UNSUPPORTED   # Q2_K
+    assert O.gemv(16, np.zeros(84, np.uint8), 1, 256, np.zeros(256, np.float32))[0] == UNSUPPORTED   # IQ2_XXS
 
 
 @pytest.mark.parametrize("qtype", S.ALL_TYPES)
@@ -467,6 +587,45 @@ def test_dequant_bit_exact_vs_numpy_restatement(qtype):
         st, got = O.dequant_block(qtype, b)
         assert st == OK
         assert np.array_equal(got.view(np.uint32), _np_dequant(qtype, b).view(np.uint32))
+
+
+def test_q2_k_against_gguf_py():
+    """Q2_K is canonical GGUF in the reference: bit-identical to gguf-py."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    for b in S.gen_blocks(S.Q2_K, 40, seed=12).reshape(40, 84):
+        _, got = O.dequant_block(S.Q2_K, b)
+        g = quants.dequantize(b[None, :].copy(), gguf.GGMLQuantizationType.Q2_K).reshape(-1).astype(np.float32)
+        assert np.array_equal(got.view(np.uint32), g.view(np.uint32))
+
+
+def test_q3_k_against_gguf_py_up_to_the_scale_packing():
+    """The reference packs Q3_K's sixteen 6-bit scales differently from llama.cpp (reference/
+    q3_k.rs:29-59: bytes 0-7 hold scales 0-7 in their low six bits; llama.cpp keeps the low
+    four bits of scales 0-7 / 8-15 in the nibbles of bytes 0-7 and all high bit pairs in bytes
+    8-11), so a block means different weights to the two.  Everything else (mask bits, 2-bit
+    quants, element order, arithmetic) is the same: the same sixteen scale values packed each
+    way give bit-identical weights."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    rng = np.random.default_rng(3)
+    for _ in range(20):
+        raw = rng.integers(0, 64, 16)
+        ref = np.zeros(12, np.uint8)
+        cpp = np.zeros(12, np.uint8)
+        for j in range(4):
+            ref[j] = (raw[j] & 0x3F) | ((raw[8 + j] >> 4) << 6)
+            ref[4 + j] = (raw[4 + j] & 0x3F) | ((raw[12 + j] >> 4) << 6)
+            ref[8 + j] = (raw[8 + j] & 0x0F) | ((raw[12 + j] & 0x0F) << 4)
+            cpp[j] = (raw[j] & 0x0F) | ((raw[8 + j] & 0x0F) << 4)
+            cpp[4 + j] = (raw[4 + j] & 0x0F) | ((raw[12 + j] & 0x0F) << 4)
+            cpp[8 + j] = (raw[j] >> 4) | ((raw[4 + j] >> 4) << 2) | ((raw[8 + j] >> 4) << 4) | ((raw[12 + j] >> 4) << 6)
+        hmask, qs = rng.integers(0, 256, 32, dtype=np.uint8), rng.integers(0, 256, 64, dtype=np.uint8)
+        d = f16b(float(rng.uniform(1e-3, 2e-2)))
+        _, got = O.dequant_block(S.Q3_K, np.concatenate([hmask, qs, ref, d]))
+        g = quants.dequantize(np.concatenate([hmask, qs, cpp, d])[None, :].copy(),
+                              gguf.GGMLQuantizationType.Q3_K).reshape(-1).astype(np.float32)
+        assert np.array_equal(got.view(np.uint32), g.view(np.uint32))
 
 
 @pytest.mark.parametrize("qtype,gname", [(S.Q8_0, "Q8_0"), (S.Q4_K, "Q4_K"), (S.Q6_K, "Q6_K"),
