@@ -241,15 +241,56 @@ def moe_rate(torch, ctx, qtype, stream, n_local=8, expert_begin=0):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons while the timed region runs (read-only queries).
+
+    NVML through pynvml when it is importable: a background thread samples every 2 ms and
+    the timing loop calls sample_now() once while its launches are still executing, so that
+    even a region of a few milliseconds has a sample taken under load.  Without pynvml,
+    nvidia-smi in a loop (its first line takes longer than a short region)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.nvml, self.handle, self.samples, self.stop_flag, self.t = None, None, [], False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip() != ""]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    def sample_now(self):
+        if not self.nvml:
+            return
+        n = self.nvml
+        try:
+            sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+            smax = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+            r = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
+                else n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+            self.samples.append((float(sm), float(smax), int(r)))
+        except Exception:
+            pass
+
+    def _loop(self):
+        while not self.stop_flag:
+            self.sample_now()
+            time.sleep(0.002)
 
     def start(self):
+        if self.nvml:
+            self.t = threading.Thread(target=self._loop, daemon=True)
+            self.t.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -264,6 +305,24 @@ class ClockSampler:
             self.lines.append(ln.strip())
 
     def stop(self):
+        if self.nvml:
+            self.stop_flag = True
+            if self.t:
+                self.t.join(timeout=2)
+            n = self.nvml
+            names = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown", "nvmlClocksThrottleReasonHwSlowdown"),
+                     ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
+                     ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"),
+                     ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap", "nvmlClocksThrottleReasonSwPowerCap"))
+            reasons = set()
+            for name, a, b in names:
+                bit = getattr(n, a, None) or getattr(n, b, None)
+                if bit and any(r & bit for _, _, r in self.samples):
+                    reasons.add(name)
+            sm = [v[0] for v in self.samples]
+            return {"sm_mhz": statistics.median(sm) if sm else None,
+                    "sm_max_mhz": max(v[1] for v in self.samples) if sm else None,
+                    "reasons": sorted(reasons), "samples": len(sm), "source": "nvml"}
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -285,7 +344,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------ CPU arm
@@ -508,6 +567,8 @@ def run_ours(args):
         for _ in range(args.steps):
             run()
         ev[1].record(stream)
+        if rank == 0:
+            sampler.sample_now()  # the launches above are still executing
         barrier()
         ms = ev[0].elapsed_time(ev[1])
         check_device_status(ctx, stream)

@@ -269,6 +269,36 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
   }
 }
 
+// The previous sharded call's gathered result, from its tagged slots into its plain buffer:
+// the calling warps of all CTAs share the slots, eight loads in flight per lane; a slot whose
+// tag has not arrived yet is waited for (bounded).
+__device__ __forceinline__ void unpack_slots(const QkPeers &peers, unsigned uwant, uint32_t lane, unsigned *status) {
+  const uint64_t stride = (uint64_t)gridDim.x * 32;
+  bool arrived = true;
+  for (uint64_t base = (uint64_t)blockIdx.x * 32 + lane; base < peers.unpack_n; base += 8 * stride) {
+    unsigned long long w[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const uint64_t i = base + j * stride;
+      w[j] = i < peers.unpack_n ? qkpeer::slot_load(peers.unpack_slots + i) : 0ull;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const uint64_t i = base + j * stride;
+      if (i >= peers.unpack_n) break;
+      float v = __uint_as_float((unsigned)w[j]);
+      if ((unsigned)(w[j] >> 32) != uwant) {  // not there yet: the bounded wait
+        if (arrived && !qkpeer::slot_wait(peers.unpack_slots + i, uwant, v)) {
+          arrived = false;
+          atomicOr(status, QK_DEV_TIMEOUT);
+        }
+        if (!arrived) v = 0.f;
+      }
+      peers.unpack_out[i] = v;
+    }
+  }
+}
+
 // PEER: the variant that can store its results into every rank's tagged slots and read
 // gathered activations out of slots (kept out of the single-GPU variant, whose speed is
 // sensitive to its code size).
@@ -282,7 +312,7 @@ __device__ void xsplit_in_cta(const float *__restrict__ x, uint32_t cols, uint32
 // silu(gate) * up (crates/oxillama-arch/src/common/swiglu.rs:15-21) where a plain matvec
 // writes its dot products.
 template <class F, int M, bool INCTA, int CW, int G, int MODE>
-__global__ void __launch_bounds__((CW + 1) * 32, 1)
+__global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
     qk_gemv_imma_kernel(QkLayout L, const uint8_t *__restrict__ W, const uint8_t *__restrict__ W2,
                            const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
@@ -377,35 +407,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         if (p == q + 4 && p < peers.n) slots_b = peers.slots[p];
       }
     }
-    if (PEER && peers.unpack_n) {
-      // In passing: the previous sharded call's gathered result goes from its slots into its
-      // plain buffer.  The producer warps of all CTAs share the slots, eight loads in flight
-      // per lane; this warp has nothing else to do until the first chunk is reduced.
-      const uint64_t stride = (uint64_t)gridDim.x * 32;
-      bool arrived = true;
-      for (uint64_t base = (uint64_t)blockIdx.x * 32 + lane; base < peers.unpack_n; base += 8 * stride) {
-        unsigned long long w[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const uint64_t i = base + j * stride;
-          w[j] = i < peers.unpack_n ? qkpeer::slot_load(peers.unpack_slots + i) : 0ull;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const uint64_t i = base + j * stride;
-          if (i >= peers.unpack_n) break;
-          float v = __uint_as_float((unsigned)w[j]);
-          if ((unsigned)(w[j] >> 32) != uwant) {  // not there yet: the bounded wait
-            if (arrived && !qkpeer::slot_wait(peers.unpack_slots + i, uwant, v)) {
-              arrived = false;
-              atomicOr(status, QK_DEV_TIMEOUT);
-            }
-            if (!arrived) v = 0.f;
-          }
-          peers.unpack_out[i] = v;
-        }
-      }
-    }
+    // In passing: the previous sharded call's gathered result goes from its slots into its
+    // plain buffer -- by a warp of its own when the launch has one (see below), else here,
+    // where this warp has nothing else to do until the first chunk is reduced.
+    if (PEER && peers.unpack_n && blockDim.x == (CW + 1) * 32) unpack_slots(peers, uwant, lane, status);
     uint32_t slot = 0, sph = 0;
     float gate_v = 0.f;  // two matrices: the gate chunk's sum, kept until the up chunk's arrives
     for (uint32_t c = 0; c < my_chunks; c++) {
@@ -454,6 +459,19 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       __syncwarp();
       QK_STAMP(c < 30, 64 + c);
       if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
+    }
+    return;
+  }
+
+  if (PEER && warp == CW + 1) {
+    // ================= unpack warp (launched only when there is something to unpack) =================
+    // On the producer / reducer warp the unpacking (two or three rounds of slot loads, about
+    // a microsecond each) held up the first reductions; a warp of its own runs beside them.
+    pdl_wait();
+    if (peers.unpack_n) {
+      unsigned uwant;
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(uwant) : "l"(peers.unpack_epoch) : "memory");
+      unpack_slots(peers, uwant, lane, status);
     }
     return;
   }
@@ -674,7 +692,8 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   uint32_t grid = (uint32_t)sm_count * (uint32_t)ctas;  // persistent
   if (grid > L.chunks) grid = L.chunks;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1) * 32), cfg.dynamicSmemBytes = P.total, cfg.stream = s;
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1 + ((MODE == 1 && peers && peers->unpack_n) ? 1 : 0)) * 32);
+  cfg.dynamicSmemBytes = P.total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
   QkPeers pv = {};
   if (peers) pv = *peers;
