@@ -426,7 +426,19 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
         for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
       const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (WG * M * 8);
       float v = 0.f;
-      if (lane < 8 * M) {
+      if (PEER && M == 1 && peers.n) {
+        // One activation row, sharded output: every lane sums the row it stores (lane (q, r):
+        // row r, for ranks q and q + 4), so that no shuffle sits between the sums and the
+        // stores -- the last chunks of a CTA are reduced one after the other, and what each
+        // costs here is the tail of the launch.
+        const uint32_t r = lane & 7u, row = (blockIdx.x + c * gridDim.x) * 8 + r;
+#pragma unroll
+        for (int wv = 0; wv < WG; wv++) v += red[wv * 8 + r];
+        if (row < L.rows) {
+          if (slots_a) qkpeer::slot_store(slots_a + row, v, tag);
+          if (slots_b) qkpeer::slot_store(slots_b + row, v, tag);
+        }
+      } else if (lane < 8 * M) {
         const uint32_t m = lane >> 3, r = lane & 7u;
 #pragma unroll
         for (int wv = 0; wv < WG; wv++) v += red[(wv * M + m) * 8 + r];
@@ -443,7 +455,7 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
           y[(uint64_t)m * ldy + row] = v;
         }
       }
-      if (PEER && peers.n) {
+      if (PEER && peers.n && M > 1) {
         // The same (value, tag) word into the slot of every rank: lane (q, r) stores row r
         // to ranks q, q + 4 (eight consecutive slots = 64 bytes per rank and activation row).
         const uint32_t r = lane & 7u, row = (blockIdx.x + c * gridDim.x) * 8 + r;
