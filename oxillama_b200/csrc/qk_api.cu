@@ -405,18 +405,83 @@ extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk
   }
   if (n_local == 0 || tokens == 0) return QK_OK;
   const size_t slots = tokens * top_k;
-  // scratch: ids, wts, counts, lists, then the per-expert activations (sized for every token)
   auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  auto grow_moe = [&](size_t need) -> int {
+    if (need > c->moe_cap) {
+      CK(c, cudaDeviceSynchronize());
+      if (c->moe) cudaFree(c->moe);
+      c->moe = nullptr, c->moe_cap = 0;
+      CK(c, cudaMalloc(&c->moe, need));
+      c->moe_cap = need;
+    }
+    return QK_OK;
+  };
+
+  // Grouped route: batches of more than a handful of tokens, experts of one format the
+  // tensor-core kernel takes.  Every projection is one conversion launch (which also gathers
+  // the routed rows) and one matmul launch over all local experts; the per-expert token
+  // counts stay on the device and nothing is read back, so the whole call is a fixed
+  // sequence of launches with no host synchronisation.  An expert may receive every token:
+  // the activation arrays reserve `cap` rows per expert, of which only the live ones are
+  // touched.
+  bool grouped = !c->force_simple && !qk_knob("QK_NO_MOE_GROUPED") && tokens > 16 && n_local <= QK_MAX_GROUPS &&
+                 hidden > 0 && inter > 0;
+  for (size_t e = 0; e < n_local && grouped; e++)
+    grouped = gate[e]->L.type == gate[0]->L.type && up[e]->L.type == gate[0]->L.type &&
+              down[e]->L.type == down[0]->L.type && qk_gemm_tc_supported(gate[e]->L, 1) &&
+              qk_gemm_tc_supported(down[e]->L, 1);
+  if (grouped) {
+    const size_t cap = qk_gemm_tc_group_cap((uint32_t)tokens), rows = n_local * cap;
+    const size_t o_ids = 0, o_wts = o_ids + al(slots * 4), o_cnt = o_wts + al(slots * 4);
+    const size_t o_lists = o_cnt + al(n_local * 4), o_pos = o_lists + al(n_local * slots * 4);
+    const size_t o_g = o_pos + al(slots * 4), o_u = o_g + al(rows * inter * 4);
+    const size_t o_o = o_u + al(rows * inter * 4), need = o_o + al(rows * hidden * 4);
+    int st = grow_moe(need);
+    if (st) return st;
+    unsigned char *base = (unsigned char *)c->moe;
+    int *ids = (int *)(base + o_ids), *cnt = (int *)(base + o_cnt), *lists = (int *)(base + o_lists);
+    int *pos = (int *)(base + o_pos);
+    float *wts = (float *)(base + o_wts), *g = (float *)(base + o_g), *u = (float *)(base + o_u);
+    float *o = (float *)(base + o_o);
+    size_t sneed = qk_gemm_tc_grouped_scratch_bytes(gate[0]->L, (uint32_t)n_local, (uint32_t)tokens);
+    const size_t sdown = qk_gemm_tc_grouped_scratch_bytes(down[0]->L, (uint32_t)n_local, (uint32_t)tokens);
+    if (sdown > sneed) sneed = sdown;
+    if (sneed > c->scratch_cap) {
+      CK(c, cudaDeviceSynchronize());
+      cudaFree(c->scratch);
+      c->scratch = nullptr, c->scratch_cap = 0;
+      CK(c, cudaMalloc(&c->scratch, sneed));
+      c->scratch_cap = sneed;
+    }
+    const uint8_t *wg[QK_MAX_GROUPS], *wu[QK_MAX_GROUPS], *wd[QK_MAX_GROUPS];
+    for (size_t e = 0; e < n_local; e++) wg[e] = gate[e]->dev, wu[e] = up[e]->dev, wd[e] = down[e]->dev;
+    CK(c, qk_launch_moe_route(logits_dev, (uint32_t)tokens, (uint32_t)n_exp, (uint32_t)top_k, ids, wts, s));
+    CK(c, qk_launch_moe_lists(ids, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)expert_begin, (uint32_t)n_local,
+                              cnt, lists, pos, s));
+    CK(c, qk_launch_gemm_tc_grouped(gate[0]->L, wg, (uint32_t)n_local, cnt, (uint32_t)tokens, x_dev, lists,
+                                    (uint32_t)slots, (uint32_t)top_k, g, inter, c->status_dev, c->scratch,
+                                    c->sm_count, s));
+    CK(c, qk_launch_gemm_tc_grouped(up[0]->L, wu, (uint32_t)n_local, cnt, (uint32_t)tokens, x_dev, lists,
+                                    (uint32_t)slots, (uint32_t)top_k, u, inter, c->status_dev, c->scratch,
+                                    c->sm_count, s));
+    CK(c, qk_launch_moe_silu_mul_grouped(g, u, cnt, (uint32_t)n_local, (uint32_t)tokens, (uint32_t)cap,
+                                         (uint32_t)inter, s));
+    CK(c, qk_launch_gemm_tc_grouped(down[0]->L, wd, (uint32_t)n_local, cnt, (uint32_t)tokens, u, nullptr, 0, 1, o,
+                                    hidden, c->status_dev, c->scratch, c->sm_count, s));
+    CK(c, qk_launch_moe_combine(o, ids, pos, wts, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)expert_begin,
+                                (uint32_t)n_local, (uint32_t)cap, (uint32_t)hidden, y_dev, s));
+    return QK_OK;
+  }
+
+  // Few tokens (decode): per expert, on the decode kernels, sized by the token counts read back.
+  // scratch: ids, wts, counts, lists, then the per-expert activations (sized for every token)
   const size_t o_ids = 0, o_wts = o_ids + al(slots * 4), o_cnt = o_wts + al(slots * 4);
   const size_t o_lists = o_cnt + al(n_local * 4), o_xe = o_lists + al(n_local * slots * 4);
   const size_t o_g = o_xe + al(tokens * hidden * 4), o_u = o_g + al(tokens * inter * 4);
   const size_t o_o = o_u + al(tokens * inter * 4), need = o_o + al(tokens * hidden * 4);
-  if (need > c->moe_cap) {
-    CK(c, cudaDeviceSynchronize());
-    if (c->moe) cudaFree(c->moe);
-    c->moe = nullptr, c->moe_cap = 0;
-    CK(c, cudaMalloc(&c->moe, need));
-    c->moe_cap = need;
+  {
+    int st = grow_moe(need);
+    if (st) return st;
   }
   unsigned char *base = (unsigned char *)c->moe;
   int *ids = (int *)(base + o_ids), *cnt = (int *)(base + o_cnt), *lists = (int *)(base + o_lists);
@@ -426,7 +491,7 @@ extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk
   CK(c, cudaMemsetAsync(y_dev, 0, tokens * hidden * sizeof(float), s));
   CK(c, qk_launch_moe_route(logits_dev, (uint32_t)tokens, (uint32_t)n_exp, (uint32_t)top_k, ids, wts, s));
   CK(c, qk_launch_moe_lists(ids, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)expert_begin, (uint32_t)n_local,
-                            cnt, lists, s));
+                            cnt, lists, nullptr, s));
   // the token counts size the per-expert matmuls: one small copy and a stream synchronise
   std::vector<int> counts(n_local);
   CK(c, cudaMemcpyAsync(counts.data(), cnt, n_local * sizeof(int), cudaMemcpyDeviceToHost, s));

@@ -438,7 +438,9 @@ template <int T>
 __global__ void __launch_bounds__(256)
     qk_x16_kernel(const float *__restrict__ x, uint32_t m, uint32_t cols, uint32_t m_pad,
                   uint32_t Kp, __half *__restrict__ out, float *__restrict__ scales,
-                  float *__restrict__ y, uint64_t ldy, uint32_t zero_rows, uint32_t cached) {
+                  float *__restrict__ y, uint64_t ldy, uint32_t zero_rows, uint32_t cached,
+                  const int *__restrict__ counts, uint32_t cap, uint32_t bn, const int *__restrict__ lists,
+                  uint32_t list_stride, uint32_t list_div) {
   extern __shared__ __align__(16) float row[];  // the row, when it fits (cached != 0)
   __shared__ float red[8];
   pdl_launch_dependents();
@@ -451,10 +453,19 @@ __global__ void __launch_bounds__(256)
   const uint32_t per_row = Kp / 8;
   const bool vec = (cols & 3u) == 0 && ((uintptr_t)x & 15u) == 0;  // rows start 16-byte aligned
   for (uint32_t t = blockIdx.x; t < m_pad; t += gridDim.x) {
+    // Grouped call (counts != nullptr): row t is row t % cap of group t / cap, live below the
+    // group's count; rows of token blocks that hold no live row are never read and are skipped.
+    bool live = t < m;
     const float *xr = x + (uint64_t)t * cols;
+    if (counts) {
+      const uint32_t e = t / cap, tl = t % cap, cnt = (uint32_t)counts[e];
+      if ((tl / bn) * bn >= cnt) continue;  // block-uniform
+      live = tl < cnt;
+      if (lists && live) xr = x + (uint64_t)(lists[(uint64_t)e * list_stride + tl] / (int)list_div) * cols;
+    }
     float amax = 0.f;
     __syncthreads();  // the previous row's readers of `row` and `red` are done
-    if (t < m) {
+    if (live) {
       if (vec) {
         for (uint32_t k = threadIdx.x * 4; k < cols; k += 1024) {
           const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + k));
@@ -491,7 +502,7 @@ __global__ void __launch_bounds__(256)
         const uint32_t p = 8 * c + j;
         const uint32_t k = (p & ~255u) + WFmt<T>::src(p & 255u);
         float v = 0.f;
-        if (t < m && k < cols) v = (cached ? row[k] : __ldg(xr + k)) * inv;
+        if (live && k < cols) v = (cached ? row[k] : __ldg(xr + k)) * inv;
         h[j] = __float2half_rn(v);
       }
       *reinterpret_cast<uint4 *>(out + (uint64_t)t * Kp + 8ull * c) = *reinterpret_cast<const uint4 *>(h);
@@ -502,12 +513,12 @@ __global__ void __launch_bounds__(256)
 // ---------------------------------------------------------------- main kernel
 // T: weight format.  BN: tokens per tile (the MMA's N).  RH: 128-row halves per tile;
 // with RH = 2 one activation stage feeds the MMAs of both halves.
-template <int T, int BN, int RH>
+template <int T, int BN, int RH, bool GRP>
 __global__ void __launch_bounds__(NTHREADS, 1)
     qk_gemm_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
                           const __grid_constant__ CUtensorMap xmap, const float *__restrict__ xscale,
                           float *__restrict__ y, uint64_t ldy, uint32_t m_tokens, uint32_t tok_blocks, uint32_t row_blocks,
-                          uint32_t KS, unsigned *status, GemmSmem S) {
+                          uint32_t KS, unsigned *status, GemmSmem S, const __grid_constant__ QkGroups G) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -518,6 +529,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   const uint32_t n_tiles = tok_blocks * row_blocks, n_units = n_tiles * KS;
   auto sb_begin = [&](uint32_t t) { return (t / n_tiles) * nsb_all / KS; };
   auto sb_end = [&](uint32_t t) { return (t / n_tiles + 1) * nsb_all / KS; };
+  // Grouped call: row block rb belongs to group rb / G.rbpg, whose weights are G.w[group] and
+  // whose activation / output rows are token blocks group * G.tbpg .. of the padded arrays; a
+  // unit whose token block lies beyond the group's row count is skipped by every role alike
+  // (the counts do not change while the kernel runs).
+  constexpr bool grouped = GRP;  // a separate instantiation: the one-matrix kernel keeps its registers
+  auto u_rb = [&](uint32_t t) { return (t % n_tiles) / tok_blocks; };
+  auto u_tbl = [&](uint32_t t) { return (t % n_tiles) % tok_blocks; };
+  auto u_group = [&](uint32_t t) { return grouped ? u_rb(t) / G.rbpg : 0u; };
+  auto u_rows = [&](uint32_t t) { return grouped ? (uint32_t)__ldg(G.counts + u_group(t)) : m_tokens; };
+  auto u_valid = [&](uint32_t t) { return !grouped || u_tbl(t) * BN < u_rows(t); };
+  auto u_tb = [&](uint32_t t) { return grouped ? u_group(t) * G.tbpg + u_tbl(t) : u_tbl(t); };
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   // Accumulators: RH of BN columns per tile.  Where tensor memory holds two sets, the
   // MMAs of tile i+1 overlap the epilogue of tile i.  Every MMA accumulates; the
@@ -583,7 +605,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       pdl_wait();  // X16 belongs to the previous kernel until it has finished
       uint32_t st = 0, use = 0, gstep = 0;
       for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
-        const uint32_t tb = (t % n_tiles) % tok_blocks;
+        if (!u_valid(t)) continue;
+        const uint32_t tb = u_tb(t);
         for (uint32_t step = sb_begin(t) * 4; step < sb_end(t) * 4; step++, gstep++) {
           if (use >= 1 && !mbar_wait_bounded(sbase + S.b_empty + st * 8, (use - 1) & 1u)) {
             dead = true;
@@ -612,7 +635,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       uint32_t unit = 0, upar = 0;  // the group's next unit and the parity of its use count
       const uint32_t abar = sbase + S.a_full + me * UPG * 8, aebar = sbase + S.a_empty + me * UPG * 8;
       const uint32_t a0 = sbase + S.a + me * UPG * A_HALF;
-      for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x, i++) {
+      for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
+        if (!u_valid(t)) continue;
         const uint32_t buf = i % NBUF, use = i / NBUF, nsb = sb_end(t) - sb_begin(t);
         // the epilogue of the tile that last used these accumulators must have drained and zeroed them
         if (use >= 1 && !mbar_wait_bounded(sbase + S.acc_empty + buf * 8, (use - 1) & 1u)) {
@@ -654,6 +678,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         if (dead) break;
         umma_commit(sbase + S.acc_full + buf * 8);  // this warp's share of the tile has retired
+        i++;
       }
       if (dead) atomicOr(status, QK_DEV_TIMEOUT);
     }
@@ -676,7 +701,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     constexpr int CPG = BN >= 128 ? BN / 4 : 32;  // columns per group
     constexpr uint32_t NCH = RH * CPG / 16;       // pieces per tile
     bool epi_active = false;
-    uint32_t epi_it = 0, epi_rb = 0, epi_tb = 0, epi_next = 0;
+    uint32_t epi_it = 0, epi_rb = 0, epi_tb = 0, epi_next = 0;  // epi_rb: row block inside its matrix; epi_tb: token block of the padded arrays
+    uint32_t epi_t0 = 0, epi_m = 0;                              // first token of the block inside its group, and the group's row count
     auto epi_piece = [&]() -> bool {
       const uint32_t buf = epi_it % NBUF;
       if (epi_it == 0 && epi_next == 0) pdl_wait();  // y and the activation scales: see above
@@ -712,11 +738,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           if (KS == 1) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (epi_tb * BN + c0 + j < m_tokens) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]) * __ldg(sp + j);
+              if (epi_t0 + c0 + j < epi_m) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]) * __ldg(sp + j);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (epi_tb * BN + c0 + j < m_tokens)
+              if (epi_t0 + c0 + j < epi_m)
                 atomicAdd(yp + (uint64_t)j * ldy, __uint_as_float(v[j]) * __ldg(sp + j));
           }
         }
@@ -736,8 +762,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // and PF_AHEAD super-blocks ahead as L2 prefetches.
     using F = WFmt<T>;
     constexpr uint32_t PF_AHEAD = 6;
-    auto chunk_of = [&](uint32_t t, int rh) -> uint32_t {
-      const uint32_t chunk = (((t % n_tiles) / tok_blocks) * RH + rh) * 16 + chunk_in_half;
+    auto chunk_of = [&](uint32_t t, int rh) -> uint32_t {  // inside the unit's own matrix
+      const uint32_t rbl = grouped ? u_rb(t) % G.rbpg : u_rb(t);
+      const uint32_t chunk = (rbl * RH + rh) * 16 + chunk_in_half;
       return chunk < L.chunks ? chunk : L.chunks - 1;  // rows past the end: valid bytes, results unused
     };
     uint32_t it = 0, u = 0;  // u: super-blocks done = uses of each of this group's A units
@@ -745,11 +772,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     uint32_t lt = blockIdx.x, pt = blockIdx.x;
     uint32_t lsb = 0, lse = 0, psb = 0, pse = 0;  // runs [lsb, lse), [psb, pse) of super-blocks
     const uint8_t *lchunk[RH], *pchunk[RH];       // and where their 8-row chunks start
-    auto enter = [&](uint32_t t, uint32_t &sb, uint32_t &se, const uint8_t **chunk) {
+    auto enter = [&](uint32_t &t, uint32_t &sb, uint32_t &se, const uint8_t **chunk) {
+      while (t < n_units && !u_valid(t)) t += gridDim.x;  // the cursors skip what the main loop skips
       if (t >= n_units) return;
       sb = sb_begin(t), se = sb_end(t);
+      const uint8_t *Wm = grouped ? G.w[u_group(t)] : W;
 #pragma unroll
-      for (int rh = 0; rh < RH; rh++) chunk[rh] = chunk_addr(L, W, chunk_of(t, rh));
+      for (int rh = 0; rh < RH; rh++) chunk[rh] = chunk_addr(L, Wm, chunk_of(t, rh));
     };
     enter(lt, lsb, lse, lchunk), enter(pt, psb, pse, pchunk);
     typename F::Pk nk[RH];
@@ -770,8 +799,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     load_next();
     for (uint32_t k = 0; k <= PF_AHEAD; k++) prefetch_next(k > 0);
 
-    for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x, it++) {
-      const uint32_t rb = (t % n_tiles) / tok_blocks, tb = (t % n_tiles) % tok_blocks;
+    for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
+      if (!u_valid(t)) continue;
+      const uint32_t rb = grouped ? u_rb(t) % G.rbpg : u_rb(t), tb = u_tb(t);
       const uint32_t nsb = sb_end(t) - sb_begin(t);
       for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, u++) {
         typename F::Pk pk[RH];
@@ -816,6 +846,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       while (epi_active && !dead)  // a tile too short to have carried all the pieces
         if (!epi_piece()) dead = true;
       epi_active = true, epi_it = it, epi_rb = rb, epi_tb = tb, epi_next = 0;
+      epi_t0 = u_tbl(t) * BN, epi_m = u_rows(t);
+      it++;
     }
     while (epi_active && !dead)
       if (!epi_piece()) dead = true;
@@ -883,10 +915,19 @@ bool plan_gemm(int bn, int rh, GemmSmem *S, uint32_t *total) {
   return true;
 }
 
+// Grouped call: the groups' weights and row counts, the rows reserved per group in the
+// activation and output arrays, and (optionally) the lists the activation rows are gathered by.
+struct GroupArgs {
+  QkGroups G;
+  uint32_t cap;
+  const int *lists;
+  uint32_t list_stride, list_div;
+};
+
 template <int T, int BN>
 cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, float *y, uint32_t m,
                         uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
-                        cudaStream_t s) {
+                        cudaStream_t s, const GroupArgs *ga = nullptr) {
   // RH = 2 (256-row tiles, half the activation traffic per MMA) measured slower on B200
   // (76 us against 61 us at Q4_K 14336 x 4096, 512 tokens): its activation ring is only
   // three stages deep.  The kernel keeps the parameter; only RH = 1 is built.
@@ -894,17 +935,27 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   GemmSmem S;
   uint32_t total;
   if (!plan_gemm(BN, RH, &S, &total)) return cudaErrorInvalidConfiguration;
-  auto kern = qk_gemm_tc_kernel<T, BN, RH>;
+  auto kern = ga ? qk_gemm_tc_kernel<T, BN, RH, true> : qk_gemm_tc_kernel<T, BN, RH, false>;
   static QkPerDevice attr_set;
   if (attr_set.first()) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return attr_set.reset(), e;
   }
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
   const uint32_t Kp = ((L.cols + 255u) / 256u) * 256u;
-  const uint32_t tok_blocks = (m + BN - 1) / BN, m_pad = tok_blocks * BN;
-  const uint32_t row_blocks = (L.rows + RH * BM - 1) / (RH * BM);
+  // grouped: m = rows reserved per group (a multiple of BN); the arrays hold G.n * m rows
+  QkGroups G = {};
+  uint32_t tok_blocks = (m + BN - 1) / BN, m_pad = tok_blocks * BN;
+  uint32_t row_blocks = (L.rows + RH * BM - 1) / (RH * BM);
+  if (ga) {
+    G = ga->G;
+    G.rbpg = row_blocks, G.tbpg = tok_blocks;
+    m_pad = G.n * ga->cap;
+    row_blocks *= G.n;
+  }
   __half *x16 = reinterpret_cast<__half *>(scratch);
   float *xscale = reinterpret_cast<float *>(scratch + (((size_t)m_pad * Kp * 2 + 255) & ~(size_t)255));
 
@@ -931,7 +982,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   // rounding not fixed for more.
   const uint32_t n_tiles = tok_blocks * row_blocks, nsb = Kp / 256u;
   uint32_t ks = 1;
-  if (n_tiles * 4 < (uint32_t)sm_count * 3) ks = (uint32_t)sm_count / n_tiles;
+  if (n_tiles * 4 < (uint32_t)sm_count * 3 && !ga) ks = (uint32_t)sm_count / n_tiles;
   if (ks > 8) ks = 8;
   if (ks > nsb) ks = nsb;
   if (const char *ev = qk_knob("QK_GEMM_KS")) {
@@ -951,7 +1002,9 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   }
   c0.dynamicSmemBytes = cached ? ((row_bytes + 15u) & ~15u) : 0u;
   cudaError_t e = cudaLaunchKernelEx(&c0, qk_x16_kernel<T>, x, m, L.cols, m_pad, Kp, x16, xscale, y, ldy,
-                                     ks > 1 ? L.rows : 0u, cached);
+                                     ks > 1 ? L.rows : 0u, cached, ga ? ga->G.counts : (const int *)nullptr,
+                                     ga ? ga->cap : 0u, (uint32_t)BN, ga ? ga->lists : (const int *)nullptr,
+                                     ga ? ga->list_stride : 0u, ga ? ga->list_div : 1u);
   if (e != cudaSuccess) return e;
 
   uint32_t grid = n_tiles * ks;
@@ -959,7 +1012,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NTHREADS), cfg.dynamicSmemBytes = total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_blocks, row_blocks, ks, status, S);
+  return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_blocks, row_blocks, ks, status, S, G);
 }
 
 int pick_bn(uint32_t m) {
@@ -973,16 +1026,35 @@ int pick_bn(uint32_t m) {
 template <int T>
 cudaError_t launch_fmt(const QkLayout &L, const uint8_t *tiled, const float *x, float *y, uint32_t m,
                        uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
-                       cudaStream_t s) {
+                       cudaStream_t s, const GroupArgs *ga = nullptr) {
   switch (pick_bn(m)) {
     case 32:
-      return launch_gemm<T, 32>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<T, 32>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
     case 64:
-      return launch_gemm<T, 64>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<T, 64>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
     case 128:
-      return launch_gemm<T, 128>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<T, 128>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
     default:
-      return launch_gemm<T, 256>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
+      return launch_gemm<T, 256>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
+  }
+}
+
+cudaError_t launch_type(const QkLayout &L, const uint8_t *tiled, const float *x, float *y, uint32_t m,
+                        uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count, cudaStream_t s,
+                        const GroupArgs *ga) {
+  switch (L.type) {
+    case QK_T_Q4_K:
+      return launch_fmt<QK_T_Q4_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
+    case QK_T_Q8_0:
+      return launch_fmt<QK_T_Q8_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
+    case QK_T_Q4_0:
+      return launch_fmt<QK_T_Q4_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
+    case QK_T_Q6_K:
+      return launch_fmt<QK_T_Q6_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
+    case QK_T_IQ4_XS:
+      return launch_fmt<QK_T_IQ4_XS>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, ga);
+    default:
+      return cudaErrorInvalidValue;
   }
 }
 
@@ -1010,18 +1082,31 @@ size_t qk_gemm_tc_scratch_bytes(const QkLayout &L, uint32_t m) {
 cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                               uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
                               int sm_count, cudaStream_t s) {
-  switch (L.type) {
-    case QK_T_Q4_K:
-      return launch_fmt<QK_T_Q4_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    case QK_T_Q8_0:
-      return launch_fmt<QK_T_Q8_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    case QK_T_Q4_0:
-      return launch_fmt<QK_T_Q4_0>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    case QK_T_Q6_K:
-      return launch_fmt<QK_T_Q6_K>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    case QK_T_IQ4_XS:
-      return launch_fmt<QK_T_IQ4_XS>(L, tiled, x, y, m, ldy, status, scratch, sm_count, s);
-    default:
-      return cudaErrorNotSupported;
-  }
+  return launch_type(L, tiled, x, y, m, ldy, status, scratch, sm_count, s, nullptr);
+}
+
+uint32_t qk_gemm_tc_group_cap(uint32_t max_rows_per_group) {
+  const uint32_t bn = (uint32_t)pick_bn(max_rows_per_group ? max_rows_per_group : 1u);
+  return ((max_rows_per_group + bn - 1) / bn) * bn + (max_rows_per_group ? 0u : bn);
+}
+
+size_t qk_gemm_tc_grouped_scratch_bytes(const QkLayout &L, uint32_t n_groups, uint32_t max_rows_per_group) {
+  const uint64_t m_pad = (uint64_t)n_groups * qk_gemm_tc_group_cap(max_rows_per_group);
+  const size_t x16 = (size_t)(m_pad * ((L.cols + 255ull) / 256ull) * 256ull * 2ull);
+  return ((x16 + 255) & ~(size_t)255) + (size_t)m_pad * 4;
+}
+
+cudaError_t qk_launch_gemm_tc_grouped(const QkLayout &L, const uint8_t *const *tiled, uint32_t n_groups,
+                                      const int *counts_dev, uint32_t max_rows_per_group, const float *x,
+                                      const int *lists, uint32_t list_stride, uint32_t list_div, float *y,
+                                      uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
+                                      cudaStream_t s) {
+  if (n_groups == 0 || n_groups > QK_MAX_GROUPS || !counts_dev || !qk_gemm_tc_supported(L, 1))
+    return cudaErrorInvalidValue;
+  GroupArgs ga = {};
+  ga.G.n = n_groups, ga.G.counts = counts_dev;
+  for (uint32_t e = 0; e < n_groups; e++) ga.G.w[e] = tiled[e];
+  ga.cap = qk_gemm_tc_group_cap(max_rows_per_group);
+  ga.lists = lists, ga.list_stride = list_stride, ga.list_div = list_div ? list_div : 1u;
+  return launch_type(L, tiled[0], x, y, ga.cap, ldy, status, scratch, sm_count, s, &ga);
 }

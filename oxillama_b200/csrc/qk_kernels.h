@@ -124,6 +124,26 @@ cudaError_t qk_launch_gemm_sb(const QkLayout &L, const uint8_t *tiled, const flo
 // Q4_K batched matmul on tcgen05 / TMEM (any m; used for m > QK_GEMV_MAX_M).  `scratch`
 // holds the fp16 copy of the activations: qk_gemm_tc_scratch_bytes(L, m) bytes.
 bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m);
+
+// Grouped form (mixture-of-experts projections): `n` weight matrices of one shape and format,
+// group e multiplying its own activation rows [e * cap, e * cap + counts[e]) (counts on the
+// device: no host round trip sizes the launch) into output rows of the same numbers.
+// Optionally the activation rows are gathered on the fly: row (e, i) = x[lists[e * list_stride
+// + i] / list_div].  One conversion launch and one matmul launch for all groups.
+#define QK_MAX_GROUPS 16
+struct QkGroups {
+  uint32_t n;                        // 0: one matrix (the ordinary call)
+  uint32_t rbpg, tbpg;               // 128-row blocks and token blocks per group
+  const int *counts;                 // device: valid activation rows per group
+  const uint8_t *w[QK_MAX_GROUPS];   // each group's tiled weights
+};
+uint32_t qk_gemm_tc_group_cap(uint32_t max_rows_per_group);  // activation rows reserved per group
+size_t qk_gemm_tc_grouped_scratch_bytes(const QkLayout &L, uint32_t n_groups, uint32_t max_rows_per_group);
+cudaError_t qk_launch_gemm_tc_grouped(const QkLayout &L, const uint8_t *const *tiled, uint32_t n_groups,
+                                      const int *counts_dev, uint32_t max_rows_per_group, const float *x,
+                                      const int *lists, uint32_t list_stride, uint32_t list_div, float *y,
+                                      uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
+                                      cudaStream_t s);
 size_t qk_gemm_tc_scratch_bytes(const QkLayout &L, uint32_t m);
 cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const float *x, float *y,
                               uint32_t m, uint64_t ldy, unsigned *status, unsigned char *scratch,
@@ -133,7 +153,12 @@ cudaError_t qk_launch_gemm_tc(const QkLayout &L, const uint8_t *tiled, const flo
 cudaError_t qk_launch_moe_route(const float *logits, uint32_t tokens, uint32_t n_exp, uint32_t top_k,
                                 int *ids, float *wts, cudaStream_t s);
 cudaError_t qk_launch_moe_lists(const int *ids, uint32_t tokens, uint32_t top_k, uint32_t expert_begin,
-                                uint32_t n_local, int *counts, int *lists, cudaStream_t s);
+                                uint32_t n_local, int *counts, int *lists, int *pos, cudaStream_t s);
+cudaError_t qk_launch_moe_silu_mul_grouped(const float *g, float *u, const int *counts, uint32_t n_local,
+                                           uint32_t max_rows, uint32_t cap, uint32_t inter, cudaStream_t s);
+cudaError_t qk_launch_moe_combine(const float *o, const int *ids, const int *pos, const float *wts, uint32_t tokens,
+                                  uint32_t top_k, uint32_t expert_begin, uint32_t n_local, uint32_t cap,
+                                  uint32_t hidden, float *y, cudaStream_t s);
 cudaError_t qk_launch_moe_gather(const float *x, const int *list, uint32_t n, uint32_t top_k,
                                  uint32_t hidden, float *xe, cudaStream_t s);
 cudaError_t qk_launch_moe_silu_mul(const float *g, float *u, uint64_t n, cudaStream_t s);

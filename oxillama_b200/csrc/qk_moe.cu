@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(128)
 // One warp per local expert: the (token, slot) pairs routed to it, in token order.
 __global__ void __launch_bounds__(32)
     qk_moe_lists_kernel(const int *__restrict__ ids, uint32_t tokens, uint32_t top_k,
-                        uint32_t expert_begin, int *__restrict__ counts, int *__restrict__ lists) {
+                        uint32_t expert_begin, int *__restrict__ counts, int *__restrict__ lists,
+                        int *__restrict__ pos) {
   const uint32_t e = blockIdx.x, lane = threadIdx.x;
   const int want = (int)(expert_begin + e);
   const uint64_t n = (uint64_t)tokens * top_k;
@@ -59,7 +60,11 @@ __global__ void __launch_bounds__(32)
     const uint64_t i = base + lane;
     const bool hit = i < n && ids[i] == want;
     const uint32_t mask = __ballot_sync(0xffffffffu, hit);
-    if (hit) lists[(uint64_t)e * n + count + __popc(mask & ((1u << lane) - 1u))] = (int)i;
+    if (hit) {
+      const uint32_t p = count + __popc(mask & ((1u << lane) - 1u));
+      lists[(uint64_t)e * n + p] = (int)i;
+      if (pos) pos[i] = (int)p;  // where (token, slot) i sits in its expert's list
+    }
     count += __popc(mask);
   }
   if (lane == 0) counts[e] = (int)count;
@@ -108,6 +113,42 @@ __global__ void __launch_bounds__(256)
     dst[c] = __fadd_rn(dst[c], __fmul_rn(w, o[(uint64_t)i * hidden + c]));
 }
 
+
+// Grouped form of the element-wise step: u[(e, i)] <- silu(g[(e, i)]) * u[(e, i)] for the live rows
+// i < counts[e] of every local expert; rows are `cap` apart per expert (moe.rs:96-112).
+__global__ void __launch_bounds__(256)
+    qk_moe_silu_mul_grouped_kernel(const float *__restrict__ g, float *__restrict__ u, const int *__restrict__ counts,
+                                   uint32_t cap, uint32_t inter) {
+  const uint32_t e = blockIdx.y, i = blockIdx.x;
+  if ((int)i >= counts[e]) return;
+  const uint64_t base = ((uint64_t)e * cap + i) * inter;
+  for (uint32_t c = threadIdx.x; c < inter; c += 256) {
+    const float v = g[base + c];
+    const float sig = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v)));
+    u[base + c] = __fmul_rn(u[base + c], __fmul_rn(v, sig));
+  }
+}
+
+// y[token] = sum over the token's slots, in slot order, of w[slot] * o[(expert, position)] for
+// the slots whose expert is local (moe.rs:232-255 accumulates in that order); a token none of
+// whose experts is local gets zeros.
+__global__ void __launch_bounds__(256)
+    qk_moe_combine_kernel(const float *__restrict__ o, const int *__restrict__ ids, const int *__restrict__ pos,
+                          const float *__restrict__ wts, uint32_t top_k, uint32_t expert_begin, uint32_t n_local,
+                          uint32_t cap, uint32_t hidden, float *__restrict__ y) {
+  const uint32_t t = blockIdx.x;
+  for (uint32_t c = threadIdx.x; c < hidden; c += 256) {
+    float acc = 0.f;
+    for (uint32_t k = 0; k < top_k; k++) {
+      const int id = ids[(uint64_t)t * top_k + k];
+      if (id < (int)expert_begin || id >= (int)(expert_begin + n_local)) continue;
+      const uint64_t row = (uint64_t)(id - (int)expert_begin) * cap + (uint32_t)pos[(uint64_t)t * top_k + k];
+      acc = __fadd_rn(acc, __fmul_rn(wts[(uint64_t)t * top_k + k], o[row * hidden + c]));
+    }
+    y[(uint64_t)t * hidden + c] = acc;
+  }
+}
+
 }  // namespace
 
 cudaError_t qk_launch_moe_route(const float *logits, uint32_t tokens, uint32_t n_exp, uint32_t top_k,
@@ -117,9 +158,22 @@ cudaError_t qk_launch_moe_route(const float *logits, uint32_t tokens, uint32_t n
   return cudaGetLastError();
 }
 cudaError_t qk_launch_moe_lists(const int *ids, uint32_t tokens, uint32_t top_k, uint32_t expert_begin,
-                                uint32_t n_local, int *counts, int *lists, cudaStream_t s) {
+                                uint32_t n_local, int *counts, int *lists, int *pos, cudaStream_t s) {
   if (n_local == 0) return cudaSuccess;
-  qk_moe_lists_kernel<<<n_local, 32, 0, s>>>(ids, tokens, top_k, expert_begin, counts, lists);
+  qk_moe_lists_kernel<<<n_local, 32, 0, s>>>(ids, tokens, top_k, expert_begin, counts, lists, pos);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_silu_mul_grouped(const float *g, float *u, const int *counts, uint32_t n_local,
+                                           uint32_t max_rows, uint32_t cap, uint32_t inter, cudaStream_t s) {
+  if (n_local == 0 || max_rows == 0 || inter == 0) return cudaSuccess;
+  qk_moe_silu_mul_grouped_kernel<<<dim3(max_rows, n_local), 256, 0, s>>>(g, u, counts, cap, inter);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_combine(const float *o, const int *ids, const int *pos, const float *wts, uint32_t tokens,
+                                  uint32_t top_k, uint32_t expert_begin, uint32_t n_local, uint32_t cap,
+                                  uint32_t hidden, float *y, cudaStream_t s) {
+  if (tokens == 0 || hidden == 0) return cudaSuccess;
+  qk_moe_combine_kernel<<<tokens, 256, 0, s>>>(o, ids, pos, wts, top_k, expert_begin, n_local, cap, hidden, y);
   return cudaGetLastError();
 }
 cudaError_t qk_launch_moe_gather(const float *x, const int *list, uint32_t n, uint32_t top_k,

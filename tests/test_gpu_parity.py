@@ -434,6 +434,54 @@ def test_moe_ffn_matches_oracle(t, tokens):
     ex.free()
 
 
+@pytest.mark.parametrize("t,tokens,top_k", [(S.Q4_K, 17, 2), (S.Q8_0, 70, 1), (S.Q4_K, 300, 2), (S.Q6_K, 130, 3)])
+def test_moe_grouped_route_cases(t, tokens, top_k):
+    """More than 16 tokens take the grouped route (one conversion and one matmul launch per
+    projection over all local experts, counts on the device).  Cases: every token-tile width
+    (17 -> 32, 70 -> 128, 130 / 300 -> 256 tokens per block), an expert that receives no token,
+    an expert that receives every token while the others' second token block stays empty
+    (300 tokens: two blocks of 256 reserved per expert), top_k of 1, 2 and 3, a repeated call,
+    and a shard of the experts (expert_begin > 0)."""
+    import torch
+    from oxillama_b200 import moe
+    hidden, inter, n_exp = 256, 512, 5
+    gate, up, down, logits, x, gf, uf, df = _moe_case(t, hidden, inter, n_exp, tokens, seed=63)
+    logits[:, 4] = -30.0          # expert 4 idle
+    logits[:, 1] += 6.0           # expert 1 in every token's selection
+    ref = O.moe_ffn_f32(gf, uf, df, logits, x, top_k)
+    ids, _ = O.moe_route(logits, top_k)
+    assert not np.any(ids == 4) and np.all((ids == 1).sum(axis=1) == 1)
+    lg, xd = torch.from_numpy(logits).cuda(), torch.from_numpy(x).cuda()
+    ex = moe.MoeExperts(t, gate, up, down, hidden, inter, n_exp)
+    y = torch.full((tokens, hidden), float("nan"), device="cuda")
+    ex.forward(lg, xd, y, top_k)
+    torch.cuda.synchronize()
+    from oxillama_b200.device import check_device_status
+    check_device_status()
+    got = y.cpu().numpy()
+    assert np.all(np.isfinite(got))
+    assert rel_inf(got, ref) <= 2 * TOL
+    y2 = torch.full((tokens, hidden), float("nan"), device="cuda")
+    ex.forward(lg, xd, y2, top_k)
+    torch.cuda.synchronize()
+    # The tensor-core matmul is not bit-reproducible (f32 differences of a few 1e-7), and the down
+    # projection rounds silu(g) * u to fp16 again: a last-bit difference in g or u can move such a
+    # rounding, so two runs of the chain agree to fp16 rounding of single terms, not to f32's.
+    assert rel_inf(y2.cpu().numpy(), got) <= 2e-4
+    # the second half of the experts alone (expert_begin > 0); tokens without a local expert get zeros
+    b, e = moe.expert_range(n_exp, 2, 1)
+    sh = moe.MoeExperts(t, gate[b:e], up[b:e], down[b:e], hidden, inter, n_exp, expert_begin=b)
+    yp = torch.full((tokens, hidden), float("nan"), device="cuda")
+    sh.forward(lg, xd, yp, top_k)
+    torch.cuda.synchronize()
+    part = yp.cpu().numpy()
+    assert np.all(np.isfinite(part))
+    local = ((ids >= b) & (ids < e)).any(axis=1)
+    assert np.all(part[~local] == 0.0)
+    sh.free()
+    ex.free()
+
+
 def test_moe_argument_checks():
     import ctypes as C
     import torch
