@@ -217,8 +217,12 @@ int qk_moe_route_dev(qk_ctx *ctx, const float *logits_dev, size_t tokens, size_t
  * gate[e], up[e] are [inter x hidden] shards, down[e] is [hidden x inter].  With every
  * expert local this is MoeFfn::forward given the router's logits; an expert-sharded
  * layer sums the y of its ranks.  logits_dev is [tokens x n_exp], x_dev [tokens x hidden].
- * The call synchronises `stream` once (the per-expert token counts size its matmuls) and
- * keeps its own device scratch, grown on first use. */
+ * More than 16 tokens, at most 16 local experts of one format: every projection is one
+ * grouped matmul launch over all local experts, the per-expert token counts stay on the
+ * device and the call does not synchronise (a fixed sequence of launches on `stream`).
+ * Otherwise (decode-sized calls) the experts run one after the other on the decode kernels
+ * and the call synchronises `stream` once to read the counts that size them.  The context
+ * keeps the device scratch, grown (with a device synchronise) on first use of a larger size. */
 int qk_moe_ffn_dev(qk_ctx *ctx, const qk_weights *const *gate, const qk_weights *const *up,
                    const qk_weights *const *down, size_t n_local, size_t expert_begin, size_t n_exp,
                    const float *logits_dev, const float *x_dev, float *y_dev, size_t tokens,

@@ -1,7 +1,9 @@
 // Mixture-of-experts FFN around the quantized matmuls (crates/oxillama-arch/src/common/moe.rs:184-258):
 // routing, the per-expert token lists, and the element-wise steps between the three
 // matmuls of an expert (moe.rs:75-126).  The matmuls themselves are the ordinary
-// dequant-matmul kernels, run once per expert on the tokens routed to it.
+// dequant-matmul kernels: for decode-sized calls run once per expert on the tokens routed to
+// it, for batches as one grouped launch per projection over all local experts (the _grouped
+// kernels below work on arrays that reserve `cap` rows per expert, live below counts[e]).
 #include <cfloat>
 
 #include "qk_kernels.h"
