@@ -513,7 +513,10 @@ __global__ void __launch_bounds__(256)
 // ---------------------------------------------------------------- main kernel
 // T: weight format.  BN: tokens per tile (the MMA's N).  RH: 128-row halves per tile;
 // with RH = 2 one activation stage feeds the MMAs of both halves.
-template <int T, int BN, int RH, bool GRP>
+// TBU: token blocks per work unit.  With TBU = 2 a unit multiplies one expanded weight tile into
+// two token blocks (two accumulators of BN columns: all of tensor memory at BN = 256), so the
+// weights of a row block are expanded once for 512 tokens instead of twice.
+template <int T, int BN, int RH, bool GRP, int TBU>
 __global__ void __launch_bounds__(NTHREADS, 1)
     qk_gemm_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
                           const __grid_constant__ CUtensorMap xmap, const float *__restrict__ xscale,
@@ -534,8 +537,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   // unit whose token block lies beyond the group's row count is skipped by every role alike
   // (the counts do not change while the kernel runs).
   constexpr bool grouped = GRP;  // a separate instantiation: the one-matrix kernel keeps its registers
+  // (tok_blocks counts work units along the tokens: TBU token blocks each)
   auto u_rb = [&](uint32_t t) { return (t % n_tiles) / tok_blocks; };
-  auto u_tbl = [&](uint32_t t) { return (t % n_tiles) % tok_blocks; };
+  auto u_tbl = [&](uint32_t t) { return ((t % n_tiles) % tok_blocks) * TBU; };
   auto u_group = [&](uint32_t t) { return grouped ? u_rb(t) / G.rbpg : 0u; };
   auto u_rows = [&](uint32_t t) { return grouped ? (uint32_t)__ldg(G.counts + u_group(t)) : m_tokens; };
   auto u_valid = [&](uint32_t t) { return !grouped || u_tbl(t) * BN < u_rows(t); };
@@ -544,8 +548,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   // Accumulators: RH of BN columns per tile.  Where tensor memory holds two sets, the
   // MMAs of tile i+1 overlap the epilogue of tile i.  Every MMA accumulates; the
   // epilogue leaves the columns it has read zeroed.
-  constexpr uint32_t NBUF = 2 * RH * BN <= 512 ? 2 : 1;
-  constexpr uint32_t TMEM_COLS = NBUF * RH * BN < 32 ? 32 : NBUF * RH * BN;
+  constexpr uint32_t ACC_COLS = RH * BN * TBU;  // accumulator columns of one unit
+  constexpr uint32_t NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;
+  constexpr uint32_t TMEM_COLS = NBUF * ACC_COLS < 32 ? 32 : NBUF * ACC_COLS;
   // A half-stage units: each of the four groups writes its half-stages round-robin into
   // UPG units of its own.
   constexpr int UPG = RH == 1 ? QK_GEMM_UPG : 2 * RH;
@@ -607,16 +612,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
         if (!u_valid(t)) continue;
         const uint32_t tb = u_tb(t);
-        for (uint32_t step = sb_begin(t) * 4; step < sb_end(t) * 4; step++, gstep++) {
-          if (use >= 1 && !mbar_wait_bounded(sbase + S.b_empty + st * 8, (use - 1) & 1u)) {
-            dead = true;
-            break;
+        for (uint32_t step = sb_begin(t) * 4; step < sb_end(t) * 4 && !dead; step++, gstep++) {
+#pragma unroll
+          for (int j = 0; j < TBU; j++) {  // the step's tile of each token block of the unit, in consecutive stages
+            if (use >= 1 && !mbar_wait_bounded(sbase + S.b_empty + st * 8, (use - 1) & 1u)) {
+              dead = true;
+              break;
+            }
+            const uint32_t bar = sbase + S.b_full + ((use & 1u) * MAX_RING + st) * 8;
+            mbar_expect_tx(bar, BN * 128);
+            tma_load_2d(sbase + S.b + st * S.b_stage, &xmap, (int)(step * 64), (int)((tb + (uint32_t)j) * BN), bar);
+            if (++st == NB) st = 0, use++;
           }
-          const uint32_t bar = sbase + S.b_full + ((use & 1u) * MAX_RING + st) * 8;
-          mbar_expect_tx(bar, BN * 128);
-          tma_load_2d(sbase + S.b + st * S.b_stage, &xmap, (int)(step * 64), (int)(tb * BN), bar);
           QK_GSTAMP(gstep < 256, 256 + gstep);
-          if (++st == NB) st = 0, use++;
         }
       }
       if (dead) atomicOr(status, QK_DEV_TIMEOUT);
@@ -631,7 +639,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // same columns (a tile's sum does not depend on the order).
     if (lane == 0) {
       const uint32_t me = warp;
-      uint32_t bst = me % NB, buse = me / NB, usea = 0, i = 0;
+      uint32_t bst = (me * TBU) % NB, buse = (me * TBU) / NB, usea = 0, i = 0;  // first of the TBU stages of this warp's next step
       uint32_t unit = 0, upar = 0;  // the group's next unit and the parity of its use count
       const uint32_t abar = sbase + S.a_full + me * UPG * 8, aebar = sbase + S.a_empty + me * UPG * 8;
       const uint32_t a0 = sbase + S.a + me * UPG * A_HALF;
@@ -644,17 +652,24 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * RH * BN;
+        const uint32_t tmem_d = tmem_base + buf * ACC_COLS;
         for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, usea++) {
           const uint32_t bbar = sbase + S.b_full + ((buse & 1u) * MAX_RING + bst) * 8, bpar = (buse >> 1) & 1u;
+          // the second token block's tile sits in the next stage (which may be the ring's first again)
+          const uint32_t bst1 = bst + 1 == NB ? 0u : bst + 1, buse1 = bst + 1 == NB ? buse + 1 : buse;
+          const uint32_t bbar1 = sbase + S.b_full + ((buse1 & 1u) * MAX_RING + bst1) * 8, bpar1 = (buse1 >> 1) & 1u;
           // both polls in flight together; the slow path only when one is not ready yet
           const bool a_ok = mbar_try_wait(abar + unit * 8, upar), b_ok = mbar_try_wait(bbar, bpar);
           if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar + unit * 8, upar) || !mbar_wait_bounded(bbar, bpar))) {
             dead = true;
             break;
           }
+          if (TBU == 2 && !mbar_wait_bounded(bbar1, bpar1)) {
+            dead = true;
+            break;
+          }
           QK_GSTAMP(usea < 64, 512 + usea * 4 + me);
-          const uint32_t b0 = sbase + S.b + bst * S.b_stage;
+          const uint32_t b0 = sbase + S.b + bst * S.b_stage, b1 = sbase + S.b + bst1 * S.b_stage;
 #pragma unroll
           for (int rh = 0; rh < RH; rh++) {
 #pragma unroll
@@ -666,14 +681,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               const uint32_t au = a0 + unit * A_HALF;
               umma_f16(tmem_d + rh * BN, umma_desc_sw64(au), umma_desc(b0 + hf * 64), IDESC, 1u);
               umma_f16(tmem_d + rh * BN, umma_desc_sw64(au + 32), umma_desc(b0 + hf * 64 + 32), IDESC, 1u);
-              umma_commit(aebar + unit * 8);  // the unit is free when these two retire
+              if (TBU == 2) {  // the same weights into the second token block's accumulator
+                umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au), umma_desc(b1 + hf * 64), IDESC, 1u);
+                umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au + 32), umma_desc(b1 + hf * 64 + 32), IDESC, 1u);
+              }
+              umma_commit(aebar + unit * 8);  // the unit is free when these retire
               if (++unit == (uint32_t)UPG) unit = 0, upar ^= 1u;
             }
             if (dead) break;
           }
           if (dead) break;
           umma_commit(sbase + S.b_empty + bst * 8);
-          bst += NI;
+          if (TBU == 2) umma_commit(sbase + S.b_empty + bst1 * 8);
+          bst += NI * TBU;
           while (bst >= NB) bst -= NB, buse++;
         }
         if (dead) break;
@@ -699,7 +719,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // all go after the next tile's first super-block.  This warp reads accumulator lanes
     // 32 (warp % 4) .. + 32 and its group's share of the columns of every row half.
     constexpr int CPG = BN >= 128 ? BN / 4 : 32;  // columns per group
-    constexpr uint32_t NCH = RH * CPG / 16;       // pieces per tile
+    constexpr uint32_t NCH1 = RH * CPG / 16;      // pieces per token block
+    constexpr uint32_t NCH = TBU * NCH1;          // pieces per unit
     bool epi_active = false;
     uint32_t epi_it = 0, epi_rb = 0, epi_tb = 0, epi_next = 0;  // epi_rb: row block inside its matrix; epi_tb: token block of the padded arrays
     uint32_t epi_t0 = 0, epi_m = 0;                              // first token of the block inside its group, and the group's row count
@@ -712,11 +733,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         tc_fence_after();
         QK_GSTAMP(grp == 0 && (warp & 3u) == 0 && epi_it < 16, 1900 + epi_it);
       }
-      const uint32_t rh = epi_next / (CPG / 16);
-      const int c0 = (int)grp * CPG + (int)(epi_next % (CPG / 16)) * 16;
+      const uint32_t tbj = epi_next / NCH1, piece = epi_next % NCH1;  // token block of the unit, piece inside it
+      const uint32_t rh = piece / (CPG / 16);
+      const int c0 = (int)grp * CPG + (int)(piece % (CPG / 16)) * 16;
       if ((int)grp * CPG < BN) {
         const uint32_t row = (epi_rb * RH + rh) * BM + r;
-        const uint32_t taddr = tmem_base + ((32 * (warp & 3u)) << 16) + (buf * RH + rh) * BN + (uint32_t)c0;
+        const uint32_t taddr =
+            tmem_base + ((32 * (warp & 3u)) << 16) + buf * ACC_COLS + (tbj * RH + rh) * BN + (uint32_t)c0;
         uint32_t v[16];
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -733,16 +756,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                        "r"(0u)
                        : "memory");
         if (row < L.rows) {
-          float *yp = y + (uint64_t)(epi_tb * BN + c0) * ldy + row;
-          const float *sp = xscale + epi_tb * BN + c0;  // the tokens' activation scales (inside the padded array)
+          float *yp = y + (uint64_t)((epi_tb + tbj) * BN + c0) * ldy + row;
+          const float *sp = xscale + (epi_tb + tbj) * BN + c0;  // the tokens' activation scales (inside the padded array)
           if (KS == 1) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (epi_t0 + c0 + j < epi_m) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]) * __ldg(sp + j);
+              if (epi_t0 + tbj * BN + c0 + j < epi_m) yp[(uint64_t)j * ldy] = __uint_as_float(v[j]) * __ldg(sp + j);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (epi_t0 + c0 + j < epi_m)
+              if (epi_t0 + tbj * BN + c0 + j < epi_m)
                 atomicAdd(yp + (uint64_t)j * ldy, __uint_as_float(v[j]) * __ldg(sp + j));
           }
         }
@@ -935,12 +958,23 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   GemmSmem S;
   uint32_t total;
   if (!plan_gemm(BN, RH, &S, &total)) return cudaErrorInvalidConfiguration;
-  auto kern = ga ? qk_gemm_tc_kernel<T, BN, RH, true> : qk_gemm_tc_kernel<T, BN, RH, false>;
+  // Two token blocks per unit (the weights of a row block expanded once for both) where the
+  // batch has an even number of 256-token blocks and the matrix still has units for most SMs
+  // (measured: Q4_K 14336 x 4096 x 512, 112 units, 70.2 -> 64.2 us; Q8_0 4096^2 x 512, which then
+  // needs four K splits instead of two, 36.9 -> 39.1 us); only built for BN = 256.
+  constexpr bool HAS2 = BN == 256;
+  const uint32_t units2 = ((L.rows + RH * BM - 1) / (RH * BM)) * (((m + BN - 1) / BN) / 2);
+  const bool two = HAS2 && !ga && m > (uint32_t)BN && ((m + BN - 1) / BN) % 2 == 0 &&
+                   units2 * 5 >= (uint32_t)sm_count * 3 && !qk_knob("QK_GEMM_TBU1");
+  auto kern = ga ? qk_gemm_tc_kernel<T, BN, RH, true, 1>
+                 : (two ? qk_gemm_tc_kernel<T, BN, RH, false, HAS2 ? 2 : 1> : qk_gemm_tc_kernel<T, BN, RH, false, 1>);
   static QkPerDevice attr_set;
   if (attr_set.first()) {
-    cudaError_t e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess && HAS2)
+      e = cudaFuncSetAttribute(qk_gemm_tc_kernel<T, BN, RH, false, HAS2 ? 2 : 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return attr_set.reset(), e;
   }
   EncodeTiledFn enc = encode_fn();
@@ -980,7 +1014,8 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   // Split K when the tiles alone would leave most SMs idle.  Partial sums meet in y
   // through atomic adds: bit-reproducible for two splits (a + b = b + a), order of
   // rounding not fixed for more.
-  const uint32_t n_tiles = tok_blocks * row_blocks, nsb = Kp / 256u;
+  const uint32_t tok_units = two ? tok_blocks / 2 : tok_blocks;  // work units along the tokens
+  const uint32_t n_tiles = tok_units * row_blocks, nsb = Kp / 256u;
   uint32_t ks = 1;
   if (n_tiles * 4 < (uint32_t)sm_count * 3 && !ga) ks = (uint32_t)sm_count / n_tiles;
   if (ks > 8) ks = 8;
@@ -1012,7 +1047,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NTHREADS), cfg.dynamicSmemBytes = total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_blocks, row_blocks, ks, status, S, G);
+  return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_units, row_blocks, ks, status, S, G);
 }
 
 int pick_bn(uint32_t m) {
