@@ -965,7 +965,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   constexpr bool HAS2 = BN == 256;
   const uint32_t units2 = ((L.rows + RH * BM - 1) / (RH * BM)) * (((m + BN - 1) / BN) / 2);
   const bool two = HAS2 && !ga && m > (uint32_t)BN && ((m + BN - 1) / BN) % 2 == 0 &&
-                   units2 * 5 >= (uint32_t)sm_count * 3 && !qk_knob("QK_GEMM_TBU1");
+                   (units2 * 5 >= (uint32_t)sm_count * 3 || qk_knob("QK_GEMM_TBU2")) && !qk_knob("QK_GEMM_TBU1");
   auto kern = ga ? qk_gemm_tc_kernel<T, BN, RH, true, 1>
                  : (two ? qk_gemm_tc_kernel<T, BN, RH, false, HAS2 ? 2 : 1> : qk_gemm_tc_kernel<T, BN, RH, false, 1>);
   static QkPerDevice attr_set;
