@@ -251,44 +251,55 @@ extern "C" int qk_weights_info(const qk_weights *h, int *type, size_t *rows, siz
   return QK_OK;
 }
 
-// Cheap content fingerprint of a host weight buffer: every byte when it is small,
-// else head, tail and 2048 evenly spread 8-byte samples.  It guards the
-// pointer-keyed cache against a freed buffer's address being reused for other
+// Cheap content fingerprint of a host weight buffer: every byte when it is small, else its
+// first and last 256 bytes and 64 evenly spread 8-byte samples (about 70 cache lines: the
+// check runs on every host-pointer call, and the 2048 samples it once took were a dozen
+// microseconds of cache misses per call on weights that do not fit the host's caches).  It
+// guards the pointer-keyed cache against a freed buffer's address being reused for other
 // weights; it does not detect a few bytes edited in place (qk_weights_cache_evict).
 static uint64_t fingerprint(const uint8_t *w, size_t n) {
   uint64_t h = 1469598103934665603ull ^ n;
   auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; h ^= h >> 29; };
-  if (n <= 65536) {
+  if (n <= 4096) {
     size_t i = 0;
     for (; i + 8 <= n; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
     for (; i < n; i++) mix(w[i]);
     return h;
   }
-  for (size_t i = 0; i < 4096; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
-  for (size_t i = n - 4096; i + 8 <= n; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
-  size_t step = (n - 8) / 2048;
-  for (size_t k = 0; k < 2048; k++) { uint64_t v; memcpy(&v, w + k * step, 8); mix(v); }
+  for (size_t i = 0; i < 256; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
+  for (size_t i = n - 256; i + 8 <= n; i += 8) { uint64_t v; memcpy(&v, w + i, 8); mix(v); }
+  const size_t step = (n - 8) / 64;
+  for (size_t k = 0; k < 64; k++) { uint64_t v; memcpy(&v, w + k * step, 8); mix(v); }
   return h;
 }
 
-// Cached device copy for the host-pointer entry points.
+// Cached device copy for the host-pointer entry points, keyed by (pointer, length, type,
+// shape); a hit whose fingerprint no longer matches is uploaded again.
 static int cached(qk_ctx *c, int type, const uint8_t *w, size_t w_len, size_t n_rows, size_t n_cols,
                   qk_weights **out) {
-  size_t need0 = need_bytes(type, n_rows, n_cols);
-  qk_ctx::Key k(w, w_len, type, n_rows, n_cols, fingerprint(w, need0));
+  const size_t need = need_bytes(type, n_rows, n_cols);
+  const uint64_t fp = fingerprint(w, need);
+  qk_ctx::Key k(w, w_len, type, n_rows, n_cols, 0);
   auto it = c->cache.find(k);
   if (it != c->cache.end()) {
-    *out = it->second;
-    return QK_OK;
+    if (it->second->fp == fp) {
+      *out = it->second;
+      return QK_OK;
+    }
+    CK(c, cudaStreamSynchronize(c->stream));  // other contents behind the same address: drop the stale copy
+    c->cache_bytes -= it->second->algo_bytes;
+    free_weights(it->second);
+    c->cache.erase(it);
   }
-  size_t need = need_bytes(type, n_rows, n_cols);
   if (c->cache_bytes + need > c->cache_cap) {  // simplest policy: start over
+    CK(c, cudaStreamSynchronize(c->stream));
     for (auto &kv : c->cache) free_weights(kv.second);
     c->cache.clear();
     c->cache_bytes = 0;
   }
   int st = upload_impl(c, type, w, n_cols, 0, n_rows, out);
   if (st == QK_OK) {
+    (*out)->fp = fp;
     c->cache[k] = *out;
     c->cache_bytes += need;
   }

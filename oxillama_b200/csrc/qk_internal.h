@@ -13,6 +13,7 @@ struct qk_weights {
   uint8_t *dev;
   int device;
   size_t algo_bytes;
+  uint64_t fp = 0;  // content fingerprint of the host buffer it was uploaded from (host-pointer cache only)
 };
 
 struct qk_ctx {

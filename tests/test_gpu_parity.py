@@ -616,6 +616,37 @@ def test_upload_from_gguf_file(tmp_path):
     g2.close()
 
 
+# ---------------------------------------------------------------- host-pointer weight cache
+def test_host_pointer_cache_follows_the_buffer_contents(K, disp):
+    """The host-pointer calls keep a device copy per (pointer, length, type, shape).  New weights
+    written over the same buffer are noticed by the content fingerprint (first / last 256 bytes and
+    64 spread samples) and uploaded again; an edit of a few bytes in place needs
+    qk_weights_cache_evict, as the header says."""
+    t, rows, cols = S.Q4_K, 64, 4096
+    k = disp.get_kernel(t)
+    buf = S.gen_weight(t, rows, cols, seed=90).copy()
+    x = S.gen_acts(1, cols, seed=90)[0]
+    y = np.empty(rows, np.float32)
+    k.gemv(K.QuantTensor(buf, (rows, cols), t), x, y)
+    assert rel_inf(y, O.gemv(t, buf, rows, cols, x)[1]) <= TOL_F32
+    k.gemv(K.QuantTensor(buf, (rows, cols), t), x, y)          # a hit
+    assert rel_inf(y, O.gemv(t, buf, rows, cols, x)[1]) <= TOL_F32
+    buf[:] = S.gen_weight(t, rows, cols, seed=91)               # other weights behind the same address
+    k.gemv(K.QuantTensor(buf, (rows, cols), t), x, y)
+    assert rel_inf(y, O.gemv(t, buf, rows, cols, x)[1]) <= TOL_F32
+    # one block edited in place, away from every sample: the stale copy answers until it is evicted
+    before = y.copy()
+    blk = (rows // 2) * (cols // 256) * 144 + 7 * 144
+    buf[blk:blk + 2] = f16b(0.5)
+    k.gemv(K.QuantTensor(buf, (rows, cols), t), x, y)
+    ref_new = O.gemv(t, buf, rows, cols, x)[1]
+    if rel_inf(y, ref_new) > TOL_F32:                            # (a sample may by chance fall on the edit)
+        assert np.array_equal(y, before)
+        K.default_context().lib.qk_weights_cache_evict(K.default_context().handle, buf.ctypes.data)
+        k.gemv(K.QuantTensor(buf, (rows, cols), t), x, y)
+    assert rel_inf(y, ref_new) <= TOL_F32
+
+
 # ---------------------------------------------------------------- Q5_K, Q2_K, Q3_K, Q8_K (generic kernels: exact, not tuned)
 def _next_kat(t):
     """One known answer of the reference's own tests per format: (block, expected value of all 256 weights)."""
