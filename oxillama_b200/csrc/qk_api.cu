@@ -445,8 +445,8 @@ extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk
     const size_t cap = qk_gemm_tc_group_cap((uint32_t)tokens), rows = n_local * cap;
     const size_t o_ids = 0, o_wts = o_ids + al(slots * 4), o_cnt = o_wts + al(slots * 4);
     const size_t o_lists = o_cnt + al(n_local * 4), o_pos = o_lists + al(n_local * slots * 4);
-    const size_t o_g = o_pos + al(slots * 4), o_u = o_g + al(rows * inter * 4);
-    const size_t o_o = o_u + al(rows * inter * 4), need = o_o + al(rows * hidden * 4);
+    const size_t o_g = o_pos + al(slots * 4), o_u = o_g + rows * inter * 4;  // u directly behind g
+    const size_t o_o = al(o_u + rows * inter * 4), need = o_o + al(rows * hidden * 4);
     int st = grow_moe(need);
     if (st) return st;
     unsigned char *base = (unsigned char *)c->moe;
@@ -464,20 +464,32 @@ extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk
       CK(c, cudaMalloc(&c->scratch, sneed));
       c->scratch_cap = sneed;
     }
-    const uint8_t *wg[QK_MAX_GROUPS], *wu[QK_MAX_GROUPS], *wd[QK_MAX_GROUPS];
-    for (size_t e = 0; e < n_local; e++) wg[e] = gate[e]->dev, wu[e] = up[e]->dev, wd[e] = down[e]->dev;
+    const uint8_t *wgu[QK_MAX_GROUPS], *wd[QK_MAX_GROUPS];
+    const bool one_launch = 2 * n_local <= QK_MAX_GROUPS;  // gate and up as 2 n groups over n activation groups
+    for (size_t e = 0; e < n_local; e++) wd[e] = down[e]->dev;
     CK(c, qk_launch_moe_route(logits_dev, (uint32_t)tokens, (uint32_t)n_exp, (uint32_t)top_k, ids, wts, s));
     CK(c, qk_launch_moe_lists(ids, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)expert_begin, (uint32_t)n_local,
                               cnt, lists, pos, s));
-    CK(c, qk_launch_gemm_tc_grouped(gate[0]->L, wg, (uint32_t)n_local, cnt, (uint32_t)tokens, x_dev, lists,
-                                    (uint32_t)slots, (uint32_t)top_k, g, inter, c->status_dev, c->scratch,
-                                    c->sm_count, s));
-    CK(c, qk_launch_gemm_tc_grouped(up[0]->L, wu, (uint32_t)n_local, cnt, (uint32_t)tokens, x_dev, lists,
-                                    (uint32_t)slots, (uint32_t)top_k, u, inter, c->status_dev, c->scratch,
-                                    c->sm_count, s));
+    if (one_launch) {
+      // u directly behind g: groups 0 .. n - 1 write g, groups n .. 2 n - 1 write u
+      u = g + rows * inter;
+      for (size_t e = 0; e < n_local; e++) wgu[e] = gate[e]->dev, wgu[n_local + e] = up[e]->dev;
+      CK(c, qk_launch_gemm_tc_grouped(gate[0]->L, wgu, (uint32_t)(2 * n_local), (uint32_t)n_local, cnt,
+                                      (uint32_t)tokens, x_dev, lists, (uint32_t)slots, (uint32_t)top_k, g, inter,
+                                      c->status_dev, c->scratch, c->sm_count, s));
+    } else {
+      for (size_t e = 0; e < n_local; e++) wgu[e] = gate[e]->dev;
+      CK(c, qk_launch_gemm_tc_grouped(gate[0]->L, wgu, (uint32_t)n_local, (uint32_t)n_local, cnt, (uint32_t)tokens,
+                                      x_dev, lists, (uint32_t)slots, (uint32_t)top_k, g, inter, c->status_dev,
+                                      c->scratch, c->sm_count, s));
+      for (size_t e = 0; e < n_local; e++) wgu[e] = up[e]->dev;
+      CK(c, qk_launch_gemm_tc_grouped(up[0]->L, wgu, (uint32_t)n_local, (uint32_t)n_local, cnt, (uint32_t)tokens,
+                                      x_dev, lists, (uint32_t)slots, (uint32_t)top_k, u, inter, c->status_dev,
+                                      c->scratch, c->sm_count, s));
+    }
     CK(c, qk_launch_moe_silu_mul_grouped(g, u, cnt, (uint32_t)n_local, (uint32_t)tokens, (uint32_t)cap,
                                          (uint32_t)inter, s));
-    CK(c, qk_launch_gemm_tc_grouped(down[0]->L, wd, (uint32_t)n_local, cnt, (uint32_t)tokens, u, nullptr, 0, 1, o,
+    CK(c, qk_launch_gemm_tc_grouped(down[0]->L, wd, (uint32_t)n_local, (uint32_t)n_local, cnt, (uint32_t)tokens, u, nullptr, 0, 1, o,
                                     hidden, c->status_dev, c->scratch, c->sm_count, s));
     CK(c, qk_launch_moe_combine(o, ids, pos, wts, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)expert_begin,
                                 (uint32_t)n_local, (uint32_t)cap, (uint32_t)hidden, y_dev, s));

@@ -541,9 +541,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   auto u_rb = [&](uint32_t t) { return (t % n_tiles) / tok_blocks; };
   auto u_tbl = [&](uint32_t t) { return ((t % n_tiles) % tok_blocks) * TBU; };
   auto u_group = [&](uint32_t t) { return grouped ? u_rb(t) / G.rbpg : 0u; };
-  auto u_rows = [&](uint32_t t) { return grouped ? (uint32_t)__ldg(G.counts + u_group(t)) : m_tokens; };
+  auto u_agroup = [&](uint32_t t) { return grouped ? u_group(t) % G.n_act : 0u; };  // whose activations it reads
+  auto u_rows = [&](uint32_t t) { return grouped ? (uint32_t)__ldg(G.counts + u_agroup(t)) : m_tokens; };
   auto u_valid = [&](uint32_t t) { return !grouped || u_tbl(t) * BN < u_rows(t); };
-  auto u_tb = [&](uint32_t t) { return grouped ? u_group(t) * G.tbpg + u_tbl(t) : u_tbl(t); };
+  auto u_tb = [&](uint32_t t) { return grouped ? u_group(t) * G.tbpg + u_tbl(t) : u_tbl(t); };        // output rows
+  auto u_tba = [&](uint32_t t) { return grouped ? u_agroup(t) * G.tbpg + u_tbl(t) : u_tbl(t); };     // activation rows
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   // Accumulators: RH of BN columns per tile.  Where tensor memory holds two sets, the
   // MMAs of tile i+1 overlap the epilogue of tile i.  Every MMA accumulates; the
@@ -611,7 +613,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       uint32_t st = 0, use = 0, gstep = 0;
       for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
         if (!u_valid(t)) continue;
-        const uint32_t tb = u_tb(t);
+        const uint32_t tb = u_tba(t);
         for (uint32_t step = sb_begin(t) * 4; step < sb_end(t) * 4 && !dead; step++, gstep++) {
 #pragma unroll
           for (int j = 0; j < TBU; j++) {  // the step's tile of each token block of the unit, in consecutive stages
@@ -724,6 +726,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     bool epi_active = false;
     uint32_t epi_it = 0, epi_rb = 0, epi_tb = 0, epi_next = 0;  // epi_rb: row block inside its matrix; epi_tb: token block of the padded arrays
     uint32_t epi_t0 = 0, epi_m = 0;                              // first token of the block inside its group, and the group's row count
+    uint32_t epi_tba = 0;                                        // token block of the activation arrays (the scales)
     auto epi_piece = [&]() -> bool {
       const uint32_t buf = epi_it % NBUF;
       if (epi_it == 0 && epi_next == 0) pdl_wait();  // y and the activation scales: see above
@@ -757,7 +760,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                        : "memory");
         if (row < L.rows) {
           float *yp = y + (uint64_t)((epi_tb + tbj) * BN + c0) * ldy + row;
-          const float *sp = xscale + (epi_tb + tbj) * BN + c0;  // the tokens' activation scales (inside the padded array)
+          const float *sp = xscale + (epi_tba + tbj) * BN + c0;  // the tokens' activation scales (inside the padded array)
           if (KS == 1) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
@@ -869,7 +872,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       while (epi_active && !dead)  // a tile too short to have carried all the pieces
         if (!epi_piece()) dead = true;
       epi_active = true, epi_it = it, epi_rb = rb, epi_tb = tb, epi_next = 0;
-      epi_t0 = u_tbl(t) * BN, epi_m = u_rows(t);
+      epi_t0 = u_tbl(t) * BN, epi_m = u_rows(t), epi_tba = u_tba(t);
       it++;
     }
     while (epi_active && !dead)
@@ -987,7 +990,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   if (ga) {
     G = ga->G;
     G.rbpg = row_blocks, G.tbpg = tok_blocks;
-    m_pad = G.n * ga->cap;
+    m_pad = G.n_act * ga->cap;  // activation rows; the output has G.n * cap rows
     row_blocks *= G.n;
   }
   __half *x16 = reinterpret_cast<__half *>(scratch);
@@ -1131,15 +1134,16 @@ size_t qk_gemm_tc_grouped_scratch_bytes(const QkLayout &L, uint32_t n_groups, ui
   return ((x16 + 255) & ~(size_t)255) + (size_t)m_pad * 4;
 }
 
-cudaError_t qk_launch_gemm_tc_grouped(const QkLayout &L, const uint8_t *const *tiled, uint32_t n_groups,
+cudaError_t qk_launch_gemm_tc_grouped(const QkLayout &L, const uint8_t *const *tiled, uint32_t n_groups, uint32_t n_act,
                                       const int *counts_dev, uint32_t max_rows_per_group, const float *x,
                                       const int *lists, uint32_t list_stride, uint32_t list_div, float *y,
                                       uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
                                       cudaStream_t s) {
-  if (n_groups == 0 || n_groups > QK_MAX_GROUPS || !counts_dev || !qk_gemm_tc_supported(L, 1))
+  if (n_groups == 0 || n_groups > QK_MAX_GROUPS || n_act == 0 || n_groups % n_act || !counts_dev ||
+      !qk_gemm_tc_supported(L, 1))
     return cudaErrorInvalidValue;
   GroupArgs ga = {};
-  ga.G.n = n_groups, ga.G.counts = counts_dev;
+  ga.G.n = n_groups, ga.G.n_act = n_act, ga.G.counts = counts_dev;
   for (uint32_t e = 0; e < n_groups; e++) ga.G.w[e] = tiled[e];
   ga.cap = qk_gemm_tc_group_cap(max_rows_per_group);
   ga.lists = lists, ga.list_stride = list_stride, ga.list_div = list_div ? list_div : 1u;

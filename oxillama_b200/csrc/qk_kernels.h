@@ -133,13 +133,17 @@ bool qk_gemm_tc_supported(const QkLayout &L, uint32_t m);
 #define QK_MAX_GROUPS 16
 struct QkGroups {
   uint32_t n;                        // 0: one matrix (the ordinary call)
+  uint32_t n_act;                    // groups e and e + n_act read the same activation rows (gate and up of an expert)
   uint32_t rbpg, tbpg;               // 128-row blocks and token blocks per group
   const int *counts;                 // device: valid activation rows per group
   const uint8_t *w[QK_MAX_GROUPS];   // each group's tiled weights
 };
 uint32_t qk_gemm_tc_group_cap(uint32_t max_rows_per_group);  // activation rows reserved per group
 size_t qk_gemm_tc_grouped_scratch_bytes(const QkLayout &L, uint32_t n_groups, uint32_t max_rows_per_group);
-cudaError_t qk_launch_gemm_tc_grouped(const QkLayout &L, const uint8_t *const *tiled, uint32_t n_groups,
+// n_act: number of distinct activation groups (n_groups a multiple of it; counts_dev, x and the
+// lists describe n_act groups, y holds n_groups * cap rows: group e + k n_act multiplies the
+// activations of group e).
+cudaError_t qk_launch_gemm_tc_grouped(const QkLayout &L, const uint8_t *const *tiled, uint32_t n_groups, uint32_t n_act,
                                       const int *counts_dev, uint32_t max_rows_per_group, const float *x,
                                       const int *lists, uint32_t list_stride, uint32_t list_div, float *y,
                                       uint64_t ldy, unsigned *status, unsigned char *scratch, int sm_count,
