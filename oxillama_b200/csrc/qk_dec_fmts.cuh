@@ -93,6 +93,7 @@ struct DecQ80 {
   static constexpr uint32_t COLB = 8 * 272, XSB = 8;
   static constexpr int MAX_M = 4;
   static constexpr bool HAS_DUAL = false;
+  static constexpr bool SPLIT_PRODUCER = false;  // the tile producer as a warp of its own (measured per format)
   // digit order inside a 32-column block: the lane's 8 bytes are columns 4 tig .. + 3 and
   // 16 + 4 tig .. + 3, the two 4-byte pieces of its A fragment (bytes 4 tig of both 16-byte granules)
   __device__ static __forceinline__ void store_digits(unsigned char *row_img, uint32_t PS, uint32_t e0, uint32_t w0,
@@ -163,6 +164,7 @@ struct DecQ40 {
   static constexpr uint32_t COLB = 8 * 144, XSB = 8;
   static constexpr int MAX_M = 4;
   static constexpr bool HAS_DUAL = false;
+  static constexpr bool SPLIT_PRODUCER = false;  // the tile producer as a warp of its own (measured per format)
   // The lane's word (bytes 4 tig .. + 3 of the block) holds elements 8 tig .. + 7: low
   // nibbles the even ones, high nibbles the odd ones.  Digits go evens first, then odds,
   // inside every group of 8 columns.
@@ -243,6 +245,7 @@ struct DecIQ4XS {
   static constexpr uint32_t COLB = 1088, XSB = 8;
   static constexpr int MAX_M = 4;
   static constexpr bool HAS_DUAL = false;
+  static constexpr bool SPLIT_PRODUCER = false;  // the tile producer as a warp of its own (measured per format)
   __device__ static __forceinline__ void store_digits(unsigned char *row_img, uint32_t PS, uint32_t e0, uint32_t w0,
                                                       uint32_t w1, uint32_t w2) {
     store_digits_natural(row_img, PS, e0, w0, w1, w2);
@@ -337,6 +340,7 @@ struct DecIQ4XS {
 struct DecQ6K {
   static constexpr uint32_t COLB = 1680, XSB = 16;
   static constexpr bool HAS_DUAL = false;
+  static constexpr bool SPLIT_PRODUCER = false;  // the tile producer as a warp of its own (measured per format)
   static constexpr int MAX_M = 2;  // three rows and up spill heavily (twelve weight words and sixteen fragments per column)
   __device__ static __forceinline__ void store_digits(unsigned char *row_img, uint32_t PS, uint32_t e0, uint32_t w0,
                                                       uint32_t w1, uint32_t w2) {

@@ -28,7 +28,8 @@ struct DecQ4K {
   static constexpr uint32_t COLB = 1152;  // 8 x 16 header bytes + 4 x 8 x 32 nibble bytes
   static constexpr uint32_t XSB = 8;      // (sx, Sx) per 32-column block
   static constexpr int MAX_M = 4;
-  static constexpr bool HAS_DUAL = true;  // the gate-and-up mode of a feed-forward block is built for this format
+  static constexpr bool HAS_DUAL = true;
+  static constexpr bool SPLIT_PRODUCER = true;  // the tile producer as a warp of its own (measured per format)
 
   // digit planes in natural column order
   __device__ static __forceinline__ void store_digits(unsigned char *row_img, uint32_t PS, uint32_t e0, uint32_t w0,

@@ -68,6 +68,7 @@ constexpr int MAX_SLOT = MAX_STAGE + 1;
 
 struct SmemMma {
   uint32_t full, redfull, xbar;  // mbarriers (8 B each)
+  uint32_t prog;                 // chunks the reducer warp has read so far (one word, polled by the producer warp)
   uint32_t red, ximg, stage;
   uint32_t PS;         // digit plane stride, bytes
   uint32_t xs_off;     // offset of the (sx, Sx) table inside the x image
@@ -312,13 +313,18 @@ __device__ __forceinline__ void unpack_slots(const QkPeers &peers, unsigned uwan
 // silu(gate) * up (crates/oxillama-arch/src/common/swiglu.rs:15-21) where a plain matvec
 // writes its dot products.
 template <class F, int M, bool INCTA, int CW, int G, int MODE>
-__global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
+__global__ void __launch_bounds__((CW + 1 + (F::SPLIT_PRODUCER ? 1 : 0) + (MODE == 1 ? 1 : 0)) * 32, 1)
     qk_gemv_imma_kernel(QkLayout L, const uint8_t *__restrict__ W, const uint8_t *__restrict__ W2,
                            const float *__restrict__ x,
                            const unsigned char *__restrict__ ximg_g, float *__restrict__ y,
                            uint64_t ldy, unsigned *status, int nstage, int nslot,
                            uint32_t stage_bytes, SmemMma S, uint32_t Kp, QkPeers peers, int npre) {
   constexpr int WG = CW / G;  // warps per group; a group owns every G-th chunk
+  // The tile producer as a warp of its own (F::SPLIT_PRODUCER) or as a second job of the reducer
+  // warp: measured per format (Q4_K 14336 x 4096: 8.2 -> 7.8 us with its own warp; Q6_K
+  // 128256 x 4096: 85 -> 90 us).
+  constexpr bool SPLIT = F::SPLIT_PRODUCER;
+  constexpr int XW = CW + 1 + (SPLIT ? 1 : 0);  // first warp behind the compute, reducer and producer warps
   constexpr bool PEER = MODE == 1, DUAL = MODE == 2;
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -335,38 +341,98 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
     for (int s = 0; s < nstage; s++) mbar_init(sbase + S.full + s * 8, 1);
     for (int s = 0; s < nslot; s++) mbar_init(sbase + S.redfull + s * 8, WG);
     mbar_init(sbase + S.xbar, 1);
+    *reinterpret_cast<volatile uint32_t *>(smem + S.prog) = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
 
-  if (warp == CW) {
-    // ================= producer / reducer warp =================
-    // Lane 0 streams tiles; after a chunk's partials are complete the warp sums
-    // them, writes the 8 x M outputs, and only then refills the stages the chunk
-    // occupied.  Gating the refills on the reduction bounds how far the compute
-    // warps can run ahead, which is what makes the ring of `nslot` partial
-    // buffers safe without a second handshake.
-    uint32_t pc = 0, pkt = 0, pst = 0;  // chunk ordinal, k-tile and stage of the next item
-    const uint64_t policy = stream_policy();
-    auto issue = [&]() {                // lane 0 only
-      const uint32_t chunk = blockIdx.x + (DUAL ? pc >> 1 : pc) * gridDim.x;
-      const uint8_t *Wc = (DUAL && (pc & 1u)) ? W2 : W;
-      const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
-      const uint32_t bar = sbase + S.full + pst * 8;
-      mbar_expect_tx(bar, bytes);
-      bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, Wc + qk_tile_offset(L, chunk, pkt), bytes, bar, policy);
-      if (++pkt == L.ktiles) pkt = 0, pc++;
-      if (++pst == (uint32_t)nstage) pst = 0;
-    };
-    uint32_t item = 0;
-    if (lane == 0) {
-      // weights are immutable: their prefetch need not wait for the previous kernel
-      for (; item < (uint32_t)npre && item < my_items; item++) issue();
+  // tile issue state and helpers of whichever warp streams the tiles
+  uint32_t pc = 0, pkt = 0, pst = 0;  // chunk ordinal, k-tile and stage of the next item
+  const uint64_t policy = stream_policy();
+  auto issue = [&]() {                // lane 0 only
+    const uint32_t chunk = blockIdx.x + (DUAL ? pc >> 1 : pc) * gridDim.x;
+    const uint8_t *Wc = (DUAL && (pc & 1u)) ? W2 : W;
+    const uint32_t bytes = QK_TILE_ROWS * qk_tile_nb(L, pkt) * L.bb;
+    const uint32_t bar = sbase + S.full + pst * 8;
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s_stream(sbase + S.stage + pst * stage_bytes, Wc + qk_tile_offset(L, chunk, pkt), bytes, bar, policy);
+    if (++pkt == L.ktiles) pkt = 0, pc++;
+    if (++pst == (uint32_t)nstage) pst = 0;
+  };
+  uint32_t item = 0;  // items issued so far; kept in step by every lane
+  auto issue_upto = [&](uint32_t limit) {
+    const uint32_t end = limit < my_items ? limit : my_items;
+    if (lane == 0)
+      for (uint32_t i = item; i < end; i++) issue();
+    if (end > item) item = end;
+  };
+  if (SPLIT && warp == CW + 1) {
+    // ================= producer warp =================
+    // Lane 0 streams the tiles: the first ring fill, then the k-tiles of chunk c + (ring depth)
+    // as soon as the compute warps have handed chunk c over (they are done with its stages
+    // then).  A warp of its own, because a copy instruction does not return until the copy
+    // unit has room for it -- a third of a microsecond and more under a saturated stream --
+    // and behind the reducer's sums the refills went out up to 1.7 us late, leaving the
+    // stream idle between the first ring fill and the refills.  The producer stays at most
+    // one chunk ahead of the reducer (S.prog), which is what makes the ring of `nslot`
+    // partial buffers safe: chunk c + nslot cannot be computed, let alone handed over,
+    // before the reducer has read chunk c.
+    issue_upto((uint32_t)npre);  // weights are immutable: their prefetch need not wait for the previous kernel
+    pdl_wait();                  // the x image belongs to the previous kernel until it has finished
+    if (!INCTA && lane == 0) {
+      mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
+      bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
     }
+    if (npre < nstage) {
+      // The rest of the first ring fill goes out once the compute warps' activation loads
+      // have landed (named barrier 2), so that those loads do not queue behind a whole
+      // ring of weight tiles from every CTA: measured 11.1 -> 9.7 us per launch at 14336 x 4096.
+      if (INCTA) asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
+      issue_upto((uint32_t)nstage);
+    }
+    uint32_t slot = 0, sph = 0;
+    const volatile uint32_t *prog = reinterpret_cast<const volatile uint32_t *>(smem + S.prog);
+    for (uint32_t c = 0; c < my_chunks && item < my_items; c++) {
+      if (!mbar_wait_bounded(sbase + S.redfull + slot * 8, sph)) {  // chunk c handed over
+        if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
+        break;
+      }
+      unsigned long long t0 = 0;
+      uint32_t polls = 0;
+      bool dead = false;
+      while (*prog < c) {  // the reducer has read the chunks before c
+        if ((++polls & 1023u) == 0) {
+          unsigned long long t;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+          if (!t0) t0 = t;
+          if (t - t0 > 250000000ull) {
+            dead = true;
+            break;
+          }
+        }
+      }
+      if (dead) {
+        if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
+        break;
+      }
+      issue_upto(item + L.ktiles);
+      if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
+    }
+    return;
+  }
+
+  if (warp == CW) {
+    // ================= reducer warp (and, without a producer warp, the tile producer) =================
+    // When a chunk's partials are complete the warp sums them and writes the 8 x M outputs
+    // (or stores them into every rank's slots), then says so in S.prog.  Where it also streams
+    // the tiles (!SPLIT) it refills the chunk's stages first: gating the refills on the
+    // reduction bounds how far the compute warps can run ahead, which is what makes the ring
+    // of `nslot` partial buffers safe without a second handshake.
+    if (!SPLIT) issue_upto((uint32_t)npre);  // weights are immutable: their prefetch need not wait for the previous kernel
     pdl_wait();  // the x image and y belong to the previous kernel until it has finished
     QK_STAMP(true, 120);
-    if (!INCTA && lane == 0) {
+    if (!SPLIT && !INCTA && lane == 0) {
       mbar_expect_tx(sbase + S.xbar, S.ximg_bytes);
       bulk_g2s(sbase + S.ximg, ximg_g, S.ximg_bytes, sbase + S.xbar);
     }
@@ -387,13 +453,10 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
         *reinterpret_cast<volatile unsigned *>(peers.epoch) = e_count + 1u;
       }
     }
-    if (npre < nstage) {
-      // The rest of the first ring fill goes out once the compute warps' activation loads
-      // have landed (named barrier 2), so that those loads do not queue behind a whole
-      // ring of weight tiles from every CTA: measured 11.1 -> 9.7 us per launch at 14336 x 4096.
+    if (!SPLIT && npre < nstage) {
+      // the rest of the first ring fill, once the activation loads are out (see the producer warp)
       if (INCTA) asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
-      if (lane == 0)
-        for (; item < (uint32_t)nstage && item < my_items; item++) issue();
+      issue_upto((uint32_t)nstage);
     }
     const unsigned tag = (PEER && peers.n) ? __shfl_sync(0xffffffffu, e_count, 0) + 1u : 0u;
     // this lane's two destination ranks (lane / 8 and lane / 8 + 4), held in registers: an
@@ -410,7 +473,7 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
     // In passing: the previous sharded call's gathered result goes from its slots into its
     // plain buffer -- by a warp of its own when the launch has one (see below), else here,
     // where this warp has nothing else to do until the first chunk is reduced.
-    if (PEER && peers.unpack_n && blockDim.x == (CW + 1) * 32) unpack_slots(peers, uwant, lane, status);
+    if (PEER && peers.unpack_n && blockDim.x == XW * 32) unpack_slots(peers, uwant, lane, status);
     uint32_t slot = 0, sph = 0;
     float gate_v = 0.f;  // two matrices: the gate chunk's sum, kept until the up chunk's arrives
     for (uint32_t c = 0; c < my_chunks; c++) {
@@ -418,12 +481,9 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
         if (lane == 0) atomicOr(status, QK_DEV_TIMEOUT);
         break;
       }
-      // Every warp of the owning group released the chunk's stages before it posted its
-      // partials: refill them first, the sums and stores below follow the copies out.  (The
-      // partial-sum ring is one slot deeper than the stage ring, so a group that runs ahead
-      // through the refilled stages cannot reach the slot that is being read here.)
-      if (lane == 0)
-        for (uint32_t k = 0; k < L.ktiles && item < my_items; k++, item++) issue();
+      // (!SPLIT) every warp of the owning group released the chunk's stages before it posted its
+      // partials: refill them first, the sums and stores below follow the copies out
+      if (!SPLIT) issue_upto(item + L.ktiles);
       const float *red = reinterpret_cast<const float *>(smem + S.red) + slot * (WG * M * 8);
       float v = 0.f;
       if (PEER && M == 1 && peers.n) {
@@ -469,13 +529,14 @@ __global__ void __launch_bounds__((CW + 1 + (MODE == 1 ? 1 : 0)) * 32, 1)
         }
       }
       __syncwarp();
+      if (SPLIT && lane == 0) *reinterpret_cast<volatile uint32_t *>(smem + S.prog) = c + 1u;  // read: its slot may be written again
       QK_STAMP(c < 30, 64 + c);
       if (++slot == (uint32_t)nslot) slot = 0, sph ^= 1;
     }
     return;
   }
 
-  if (PEER && warp == CW + 1) {
+  if (PEER && warp == XW) {
     // ================= unpack warp (launched only when there is something to unpack) =================
     // On the producer / reducer warp the unpacking (two or three rounds of slot loads, about
     // a microsecond each) held up the first reductions; a warp of its own runs beside them.
@@ -621,6 +682,7 @@ inline bool make_plan_mma(const QkLayout &L, uint32_t m, PlanMma *P, uint32_t xs
   S.full = off, off += MAX_STAGE * 8;
   S.redfull = off, off += MAX_SLOT * 8;
   S.xbar = off, off += 8;
+  S.prog = off, off += 8;
   off = (off + 127u) & ~127u;
   S.red = off, off += MAX_SLOT * MAX_CW * m * 8 * 4;
   off = (off + 127u) & ~127u;
@@ -704,21 +766,21 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   uint32_t grid = (uint32_t)sm_count * (uint32_t)ctas;  // persistent
   if (grid > L.chunks) grid = L.chunks;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1 + ((MODE == 1 && peers && peers->unpack_n) ? 1 : 0)) * 32);
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3((CW + 1 + (F::SPLIT_PRODUCER ? 1 : 0) + ((MODE == 1 && peers && peers->unpack_n) ? 1 : 0)) * 32);
   cfg.dynamicSmemBytes = P.total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = use_pdl ? 1 : 0;
   QkPeers pv = {};
   if (peers) pv = *peers;
   // Weight tiles issued before the wait on the previous kernel; the rest of the ring follows
-  // the activation loads.  Measured at 14336 x 4096, M = 1, 8 warps: 1 tile 8.2 us, 2 8.3,
-  // 3 8.6, 4 8.8, 6 9.2; M = 2: 2 tiles 13.1 us, 3 12.9, 4 12.7.  QK_PRE overrides
-  // (developer knob).
+  // the activation loads.  Measured at 14336 x 4096, M = 1, 8 warps: with the producer a warp
+  // of its own 1 tile 8.04 us, 2 7.81, 3 7.97; with the reducer issuing 1 tile 8.2 us, 2 8.3,
+  // 3 8.6; M = 2: 2 tiles 13.1 us, 3 12.9, 4 12.7.  QK_PRE overrides (developer knob).
   static int npre_env = -1;
   if (npre_env < 0) {
     const char *e = qk_knob("QK_PRE");
     npre_env = e ? atoi(e) : 0;
   }
-  int npre = npre_env > 0 ? npre_env : (M == 1 ? (CW == 12 ? 2 : 1) : (M == 2 ? 4 : 3));
+  int npre = npre_env > 0 ? npre_env : (M == 1 ? ((F::SPLIT_PRODUCER || CW == 12) ? 2 : 1) : (M == 2 ? 4 : 3));
   if (npre > P.nstage) npre = P.nstage;
   return cudaLaunchKernelEx(&cfg, kern, L, W, W2, x, (const unsigned char *)ximg, y, ldy, status,
                             P.nstage, P.nslot, P.stage_bytes, P.S, P.Kp, pv, npre);
