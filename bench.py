@@ -51,7 +51,7 @@ METRIC = "q4_k_gemv_weight_bandwidth"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the
 # ncu capture summarised in profiles/q4k_gemv_14336x4096_m1_ncu.md
-DRAM_BYTES_PER_LAUNCH = 33108480
+DRAM_BYTES_PER_LAUNCH = 33113600
 WORKLOAD = "config[1]: Q4_K 14336x4096 matvec, M=1, f32 N(0,1) activations, seed 0"
 
 
