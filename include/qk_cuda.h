@@ -228,6 +228,20 @@ int qk_moe_ffn_dev(qk_ctx *ctx, const qk_weights *const *gate, const qk_weights 
                    const float *logits_dev, const float *x_dev, float *y_dev, size_t tokens,
                    size_t top_k, void *stream);
 
+/* ---- token exchange for an expert-sharded layer whose ranks each own their own tokens ---- */
+/* (new; stands where a multi-process port of MoeFfn::forward, moe.rs:184-258, would send each
+ * token's row to the ranks that hold its selected experts and take their partial outputs back) */
+
+/* out_dev[i][:] = x_dev[idx_dev[i]][:] for i < n: rows of `width` floats, packed in send order. */
+int qk_moe_take_rows_dev(qk_ctx *ctx, const float *x_dev, const int *idx_dev, size_t n, size_t width,
+                         float *out_dev, void *stream);
+
+/* y_dev[t][:] = +0 + src_dev[idx_dev[t][0]][:] + src_dev[idx_dev[t][1]][:] + ..., added in that
+ * order, negative entries skipped; idx_dev is [tokens x per_row].  The partial outputs that came
+ * back for a token are summed in the order of the ranks that computed them, the same on every run. */
+int qk_moe_sum_rows_dev(qk_ctx *ctx, const float *src_dev, const int *idx_dev, size_t tokens, size_t per_row,
+                        size_t width, float *y_dev, void *stream);
+
 /* ---- row-sharded layers on the GPUs of one node: outputs gathered by peer stores ---- */
 /* (new; stands where a sharded port of QuantLinear::forward would call an all-gather,
  * crates/oxillama-arch/src/common/linear.rs:77-132) */

@@ -64,6 +64,8 @@ SIGNATURES = {
     "qk_gemm_gather_unpack_dev": (C.c_int, [vp, vp, vp, sz, vp, vp, vp, vp]),
     "qk_gather_wait_dev": (C.c_int, [vp, vp, vp]),
     "qk_moe_route_dev": (C.c_int, [vp, vp, sz, sz, sz, vp, vp, vp]),
+    "qk_moe_take_rows_dev": (C.c_int, [vp, vp, vp, sz, sz, vp, vp]),
+    "qk_moe_sum_rows_dev": (C.c_int, [vp, vp, vp, sz, sz, sz, vp, vp]),
     "qk_moe_ffn_dev": (C.c_int, [vp, vp, vp, vp, sz, sz, sz, vp, vp, vp, sz, sz, vp]),
     "qk_check_device_status": (C.c_int, [vp, vp]),
 }

@@ -397,6 +397,27 @@ extern "C" int qk_moe_route_dev(qk_ctx *c, const float *logits_dev, size_t token
   return QK_OK;
 }
 
+extern "C" int qk_moe_take_rows_dev(qk_ctx *c, const float *x_dev, const int *idx_dev, size_t n, size_t width,
+                                    float *out_dev, void *stream) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (n == 0 || width == 0) return QK_OK;
+  if (!x_dev || !idx_dev || !out_dev || n > 0x7fffffffu || width > 0x7fffffffu) return QK_INVALID_ARGUMENT;
+  CK(c, qk_launch_moe_take_rows(x_dev, idx_dev, (uint32_t)n, (uint32_t)width, out_dev, (cudaStream_t)stream));
+  return QK_OK;
+}
+
+extern "C" int qk_moe_sum_rows_dev(qk_ctx *c, const float *src_dev, const int *idx_dev, size_t tokens,
+                                   size_t per_row, size_t width, float *y_dev, void *stream) {
+  if (!c) return QK_INVALID_ARGUMENT;
+  if (tokens == 0 || width == 0) return QK_OK;
+  if (!y_dev || (per_row && (!src_dev || !idx_dev)) || tokens > 0x7fffffffu || per_row > 0x7fffffffu ||
+      width > 0x7fffffffu)
+    return QK_INVALID_ARGUMENT;
+  CK(c, qk_launch_moe_sum_rows(src_dev, idx_dev, (uint32_t)tokens, (uint32_t)per_row, (uint32_t)width, y_dev,
+                               (cudaStream_t)stream));
+  return QK_OK;
+}
+
 extern "C" int qk_moe_ffn_dev(qk_ctx *c, const qk_weights *const *gate, const qk_weights *const *up,
                               const qk_weights *const *down, size_t n_local, size_t expert_begin,
                               size_t n_exp, const float *logits_dev, const float *x_dev, float *y_dev,

@@ -170,3 +170,7 @@ cudaError_t qk_launch_moe_silu_mul(const float *g, float *u, uint64_t n, cudaStr
 cudaError_t qk_launch_swiglu(float *g, const float *u, uint64_t n, cudaStream_t s);
 cudaError_t qk_launch_moe_scatter(const float *o, const int *list, const float *wts, uint32_t n,
                                   uint32_t top_k, uint32_t hidden, float *y, cudaStream_t s);
+cudaError_t qk_launch_moe_take_rows(const float *x, const int *idx, uint32_t n, uint32_t width, float *out,
+                                    cudaStream_t s);
+cudaError_t qk_launch_moe_sum_rows(const float *src, const int *idx, uint32_t tokens, uint32_t per_row,
+                                   uint32_t width, float *y, cudaStream_t s);

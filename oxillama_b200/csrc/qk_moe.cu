@@ -151,6 +151,30 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// out[i][:] = x[idx[i]][:]: the rows a rank sends to another rank, in send order.
+__global__ void __launch_bounds__(256)
+    qk_moe_take_rows_kernel(const float *__restrict__ x, const int *__restrict__ idx, uint32_t width,
+                            float *__restrict__ out) {
+  const uint64_t src = (uint64_t)(uint32_t)idx[blockIdx.x] * width, dst = (uint64_t)blockIdx.x * width;
+  for (uint32_t c = threadIdx.x; c < width; c += 256) out[dst + c] = x[src + c];
+}
+
+// y[t][:] = +0 + src[idx[t][0]] + src[idx[t][1]] + ... in that order, entries below zero skipped:
+// the partial outputs that came back for token t, in the order of the ranks that made them.
+__global__ void __launch_bounds__(256)
+    qk_moe_sum_rows_kernel(const float *__restrict__ src, const int *__restrict__ idx, uint32_t per_row,
+                           uint32_t width, float *__restrict__ y) {
+  const uint32_t t = blockIdx.x;
+  for (uint32_t c = threadIdx.x; c < width; c += 256) {
+    float acc = 0.f;
+    for (uint32_t j = 0; j < per_row; j++) {
+      const int r = idx[(uint64_t)t * per_row + j];
+      if (r >= 0) acc = __fadd_rn(acc, src[(uint64_t)r * width + c]);
+    }
+    y[(uint64_t)t * width + c] = acc;
+  }
+}
+
 }  // namespace
 
 cudaError_t qk_launch_moe_route(const float *logits, uint32_t tokens, uint32_t n_exp, uint32_t top_k,
@@ -201,5 +225,18 @@ cudaError_t qk_launch_moe_scatter(const float *o, const int *list, const float *
                                   uint32_t top_k, uint32_t hidden, float *y, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
   qk_moe_scatter_kernel<<<n, 256, 0, s>>>(o, list, wts, n, top_k, hidden, y);
+  return cudaGetLastError();
+}
+
+cudaError_t qk_launch_moe_take_rows(const float *x, const int *idx, uint32_t n, uint32_t width, float *out,
+                                    cudaStream_t s) {
+  if (n == 0 || width == 0) return cudaSuccess;
+  qk_moe_take_rows_kernel<<<n, 256, 0, s>>>(x, idx, width, out);
+  return cudaGetLastError();
+}
+cudaError_t qk_launch_moe_sum_rows(const float *src, const int *idx, uint32_t tokens, uint32_t per_row,
+                                   uint32_t width, float *y, cudaStream_t s) {
+  if (tokens == 0 || width == 0) return cudaSuccess;
+  qk_moe_sum_rows_kernel<<<tokens, 256, 0, s>>>(src, idx, per_row, width, y);
   return cudaGetLastError();
 }

@@ -8,7 +8,8 @@ softmax -> top-k -> renormalised weights -> sum of the selected experts'
 
 Expert sharding (one process per GPU): every rank holds a contiguous range of
 experts, computes their contribution for all tokens, and the ranks' outputs are
-summed (`ExpertShardedMoe`).
+summed (`ExpertShardedMoe`).  Where every rank owns its own tokens instead, only the
+routed rows cross between the ranks, by two all-to-all exchanges (`TokenExchangeMoe`).
 """
 from __future__ import annotations
 
@@ -112,3 +113,145 @@ class ExpertShardedMoe:
             else:
                 self.all_reduce_sum(y)
         return y
+
+
+def expert_owner(n_experts: int, world: int):
+    """owner[e] = the rank whose `expert_range` holds expert e."""
+    owner = np.empty(n_experts, dtype=np.int64)
+    for r in range(world):
+        b, e = expert_range(n_experts, world, r)
+        owner[b:e] = r
+    return owner
+
+
+def exchange_plan(ids: np.ndarray, n_experts: int, world: int):
+    """Which of this rank's token rows go to which rank, from the routed ids [tokens x top_k].
+
+    A token goes once to every rank that holds at least one of its selected experts (ids
+    below zero are empty slots).  Returns `(send_idx, send_counts, back)`: the token
+    indices in send order (by rank, then by token), the number of rows per destination
+    rank, and an int32 table [tokens x min(top_k, world)] holding, for each token, the
+    positions in send order of its rows in rank order, -1 where it has fewer.
+    """
+    tokens, top_k = ids.shape
+    owner = expert_owner(n_experts, world)
+    goes = np.zeros((tokens, world), dtype=bool)
+    for k in range(top_k):
+        sel = ids[:, k] >= 0
+        goes[np.nonzero(sel)[0], owner[ids[sel, k]]] = True
+    send_counts = goes.sum(axis=0).astype(np.int64)
+    ranks, toks = np.nonzero(goes.T)  # rank-major, tokens ascending inside a rank
+    send_idx = toks.astype(np.int32)
+    per_row = max(1, min(top_k, world))
+    back = np.full((tokens, per_row), -1, dtype=np.int32)
+    fill = np.zeros(tokens, dtype=np.int64)
+    for pos, t in enumerate(toks):
+        back[t, fill[t]] = pos
+        fill[t] += 1
+    return send_idx, send_counts, back
+
+
+def take_rows(x, idx, ctx=None, stream=None):
+    """x[idx] on the device (`qk_moe_take_rows_dev`): x [n x width] f32, idx int32 [m]."""
+    import torch
+    from .device import _stream_ptr
+    from .kernels import default_context
+    ctx = ctx or default_context()
+    out = torch.empty((idx.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
+    ctx.check(ctx.lib.qk_moe_take_rows_dev(ctx.handle, C.c_void_p(x.data_ptr()), C.c_void_p(idx.data_ptr()),
+                                           idx.shape[0], x.shape[1], C.c_void_p(out.data_ptr()), _stream_ptr(stream)))
+    return out
+
+
+def sum_rows(src, table, width: int, ctx=None, stream=None):
+    """y[t] = sum in order of src[table[t][j]] over the entries >= 0 (`qk_moe_sum_rows_dev`)."""
+    import torch
+    from .device import _stream_ptr
+    from .kernels import default_context
+    ctx = ctx or default_context()
+    y = torch.empty((table.shape[0], width), dtype=torch.float32, device=table.device)
+    ctx.check(ctx.lib.qk_moe_sum_rows_dev(ctx.handle, C.c_void_p(src.data_ptr()), C.c_void_p(table.data_ptr()),
+                                          table.shape[0], table.shape[1], width, C.c_void_p(y.data_ptr()),
+                                          _stream_ptr(stream)))
+    return y
+
+
+class TokenExchangeMoe:
+    """One rank of an expert-sharded MoE layer whose tokens are sharded as well.
+
+    Every rank owns its own tokens and a contiguous range of experts.  Only routed rows
+    cross between the ranks: a token's activation row and its logits row go once to each
+    rank that holds one of its selected experts (an all-to-all), that rank computes its
+    experts' weighted contribution for the rows it received (`local_forward`, on a GPU
+    `MoeExperts.forward`: the router is a function of the token's own logits row, so the
+    receiver recomputes the same ids and weights), the partial outputs return by the
+    reverse all-to-all, and the owner adds a token's partials in rank order.
+
+    The step is split in three so that a test can drive several ranks of one process in
+    lock-step: `begin` (route, plan, pack), `compute` (the local experts over the received
+    rows) and `finish` (the sum); `forward` runs them around the two exchanges.
+    The hooks default to the device entry points and `torch.distributed`:
+    `route_ids(logits, top_k) -> int32 [tokens x top_k]`, `take(x, idx)`, `total(src, table, width)`,
+    `all_to_all(out, inp, out_counts, in_counts)`.
+    """
+
+    def __init__(self, n_experts: int, world: int, rank: int, local_forward: Callable,
+                 route_ids: Callable | None = None, take: Callable | None = None, total: Callable | None = None,
+                 all_to_all: Callable | None = None):
+        self.n_experts, self.world, self.rank = n_experts, world, rank
+        self.begin_expert, self.end_expert = expert_range(n_experts, world, rank)
+        self.local_forward = local_forward
+        self.route_ids = route_ids or (lambda logits, top_k: route(logits, top_k)[0])
+        self.take = take or take_rows
+        self.total = total or sum_rows
+        self.all_to_all = all_to_all or self._dist_all_to_all
+
+    @staticmethod
+    def _dist_all_to_all(out, inp, out_counts, in_counts):
+        import torch.distributed as dist
+        dist.all_to_all_single(out, inp, list(out_counts), list(in_counts))
+
+    def begin(self, logits, x, top_k: int):
+        """Routes the local tokens; returns the packed rows to send and the step's state."""
+        import torch
+        tokens = x.shape[0]
+        if tokens:
+            ids = self.route_ids(logits, top_k).cpu().numpy()
+        else:
+            ids = np.empty((0, top_k), dtype=np.int32)
+        send_idx, send_counts, back = exchange_plan(ids, self.n_experts, self.world)
+        idx = torch.from_numpy(send_idx).to(x.device)
+        state = {"tokens": tokens, "width": x.shape[1], "send_counts": [int(c) for c in send_counts],
+                 "back": torch.from_numpy(back).to(x.device), "top_k": top_k}
+        if len(send_idx):
+            return self.take(x, idx), self.take(logits, idx), state
+        return x.new_empty((0, x.shape[1])), logits.new_empty((0, logits.shape[1])), state
+
+    def compute(self, recv_logits, recv_x, top_k: int):
+        """The local experts' weighted contribution for the rows received, one row each."""
+        if recv_x.shape[0] == 0:
+            return recv_x.new_empty((0, recv_x.shape[1]))
+        return self.local_forward(recv_logits, recv_x, top_k)
+
+    def finish(self, returned, state):
+        """y [tokens x hidden]: every token's partial outputs added in rank order."""
+        if state["tokens"] == 0:
+            return returned.new_empty((0, state["width"]))
+        return self.total(returned, state["back"], state["width"])
+
+    def forward(self, logits, x, top_k: int):
+        import torch
+        send_x, send_l, st = self.begin(logits, x, top_k)
+        sc = st["send_counts"]
+        cnt_in = torch.tensor(sc, dtype=torch.int64, device=x.device)
+        cnt_out = torch.empty_like(cnt_in)
+        self.all_to_all(cnt_out, cnt_in, [1] * self.world, [1] * self.world)
+        rc = [int(v) for v in cnt_out.cpu().tolist()]
+        recv_x = x.new_empty((sum(rc), x.shape[1]))
+        recv_l = logits.new_empty((sum(rc), logits.shape[1]))
+        self.all_to_all(recv_x, send_x, rc, sc)
+        self.all_to_all(recv_l, send_l, rc, sc)
+        part = self.compute(recv_l, recv_x, top_k)
+        returned = x.new_empty((sum(sc), x.shape[1]))
+        self.all_to_all(returned, part, sc, rc)
+        return self.finish(returned, st)

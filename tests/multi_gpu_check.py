@@ -5,8 +5,9 @@
 
 Every rank uploads its row shard, runs the sharded matvec / small matmul with the
 peer-store gather (`qk_gemm_gather_dev`) and with an NCCL all-gather, and compares both
-with the oracle's result for the whole matrix; then two chained sharded layers, and an
-expert-sharded mixture of experts summed by NCCL.  Exits non-zero on a mismatch.
+with the oracle's result for the whole matrix; then two chained sharded layers, an
+expert-sharded mixture of experts summed by NCCL, and the same layer with the tokens sharded
+as well (routed rows exchanged by NCCL's all-to-all).  Exits non-zero on a mismatch.
 """
 import os
 import sys
@@ -156,6 +157,28 @@ def main():
         if not err <= 2e-3:
             bad += 1
             print(f"rank {rank}: expert-sharded MoE {S.NAMES[t]}: err {err}", flush=True)
+        check_device_status()
+        # the same layer with the tokens sharded too: rank r owns a ragged share of them (the last
+        # rank none when there are several), routed rows cross by NCCL's all-to-all and come back
+        cuts = [round(tokens * r / max(world - 1, 1)) for r in range(world)] + [tokens] if world > 1 else [0, tokens]
+        lo, hi = cuts[rank], cuts[rank + 1]
+
+        def rows_forward(lg_, x_, k_):
+            y = torch.empty((x_.shape[0], hidden), device="cuda")
+            ex.forward(lg_, x_, y, k_)
+            return y
+
+        xch = moe.TokenExchangeMoe(n_exp, world, rank, rows_forward)
+        y = xch.forward(lg[lo:hi].contiguous(), xd[lo:hi].contiguous(), top_k)
+        torch.cuda.synchronize()
+        if tuple(y.shape) != (hi - lo, hidden):
+            bad += 1
+            print(f"rank {rank}: token-exchange MoE {S.NAMES[t]}: shape {tuple(y.shape)}", flush=True)
+        elif hi > lo:
+            err = np.abs(y.cpu().numpy() - ref[lo:hi]).max() / np.abs(ref).max()
+            if not err <= 2e-3:
+                bad += 1
+                print(f"rank {rank}: token-exchange MoE {S.NAMES[t]}: err {err}", flush=True)
         check_device_status()
         ex.free()
     tot = torch.tensor([bad], device="cuda")

@@ -3,7 +3,9 @@
 Each rank computes its experts' contribution with a numpy stand-in for the
 device call, the ranks' outputs are summed with a gloo all-reduce, and the
 result must equal the oracle's whole-layer output
-(crates/oxillama-arch/src/common/moe.rs:184-258).
+(crates/oxillama-arch/src/common/moe.rs:184-258).  The token exchange (every rank owns
+its own tokens, routed rows cross by all-to-all) runs the same way, with numpy stand-ins
+for the device calls and gloo's all-to-all.
 """
 import os
 import sys
@@ -81,3 +83,70 @@ def test_expert_sharded_moe_two_ranks():
         assert p.exitcode == 0
     assert sorted(r for r, _ in res) == [0, 1]
     assert all(err <= 1e-5 for _, err in res), res
+
+
+def test_exchange_plan():
+    ids = np.array([[0, 3], [2, 3], [1, 0], [-1, -1], [3, 1]], dtype=np.int32)
+    send_idx, counts, back = moe.exchange_plan(ids, 4, 2)  # experts 0, 1 on rank 0; 2, 3 on rank 1
+    assert send_idx.tolist() == [0, 2, 4, 0, 1, 4] and counts.tolist() == [3, 3]
+    assert back.tolist() == [[0, 3], [4, -1], [1, -1], [-1, -1], [2, 5]]
+    send_idx, counts, back = moe.exchange_plan(np.empty((0, 2), np.int32), 4, 2)
+    assert len(send_idx) == 0 and counts.tolist() == [0, 0] and back.shape == (0, 2)
+    # more ranks than slots: a token has at most top_k rows out
+    send_idx, counts, back = moe.exchange_plan(np.array([[5, 0]], dtype=np.int32), 8, 8)
+    assert counts.tolist() == [1, 0, 0, 0, 0, 1, 0, 0] and back.tolist() == [[0, 1]]
+    assert moe.expert_owner(5, 4).tolist() == [0, 0, 1, 2, 3]
+
+
+def _cpu_hooks():
+    """numpy / torch-on-CPU stand-ins for the device entry points of the token exchange."""
+    def route_ids(logits, top_k):
+        return torch.from_numpy(O.moe_route(logits.numpy(), top_k)[0].astype(np.int32))
+
+    def take(x, idx):
+        return x[idx.long()].contiguous()
+
+    def total(src, table, width):
+        y = torch.zeros((table.shape[0], width), dtype=torch.float32)
+        for t in range(table.shape[0]):
+            for j in table[t].tolist():
+                if j >= 0:
+                    y[t] += src[j]
+        return y
+    return dict(route_ids=route_ids, take=take, total=total)
+
+
+def _exchange_worker(rank, world, port, q, split):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(11)
+    n_exp, hidden, inter, tokens, top_k = 4, 32, 48, 12, 2
+    gate = rng.standard_normal((n_exp, inter, hidden)).astype(np.float32) * 0.2
+    up = rng.standard_normal((n_exp, inter, hidden)).astype(np.float32) * 0.2
+    down = rng.standard_normal((n_exp, hidden, inter)).astype(np.float32) * 0.2
+    logits = rng.standard_normal((tokens, n_exp)).astype(np.float32)
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    b, e = moe.expert_range(n_exp, world, rank)
+    lo, hi = (0, split) if rank == 0 else (split, tokens)  # this rank's own tokens
+    layer = moe.TokenExchangeMoe(n_exp, world, rank, _local_numpy(gate, up, down, b, e), **_cpu_hooks())
+    y = layer.forward(torch.from_numpy(logits[lo:hi].copy()), torch.from_numpy(x[lo:hi].copy()), top_k).numpy()
+    ref = O.moe_ffn_f32(gate, up, down, logits, x, top_k)[lo:hi]
+    err = float(np.abs(y - ref).max() / np.abs(ref).max()) if hi > lo else 0.0
+    q.put((rank, y.shape == ref.shape, err))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("split", [7, 0, 12])  # ragged shares; a rank without tokens, either one
+def test_token_exchange_moe_two_ranks(split):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000) + split
+    procs = [ctx.Process(target=_exchange_worker, args=(r, 2, port, q, split)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert sorted(r for r, _, _ in res) == [0, 1]
+    assert all(ok and err <= 1e-5 for _, ok, err in res), res
