@@ -19,7 +19,7 @@ gathered vector is compared with an NCCL all-gather of the single-GPU results
 before anything is timed (`gather_checked`).
 
 Beside the headline the line carries the other configurations' figures
-(`decode_shapes`, `small_batch`, `layer`, `prefill`, `moe`) and, for N > 1,
+(`decode_shapes`, `small_batch`, `layer`, `prefill`, `moe`) and, for N > 1, `moe_layer` and
 strong-scaling figures of the large shapes (`strong_scaling`).
 
 `--impl reference` times the CPU restatement of the reference's own fastest
@@ -238,6 +238,58 @@ def moe_rate(torch, ctx, qtype, stream, n_local=8, expert_begin=0):
     return {"workload": f"config[4]: 8 x {S.NAMES[qtype]} experts (gate, up 14336x4096; down 4096x14336), "
                         f"256 tokens, top-2; {n_local} experts on this GPU",
             "ms": ms, "tflops": flops / ms / 1e9, "frac": flops / ms / 1e9 / peak, "peak_source": which}
+
+
+def moe_layer_rates(torch, dist, ctx, qtype, stream, world, rank):
+    """config[4] as a whole layer on `world` GPUs, collectives included, both ways of sharding it:
+    tokens replicated and outputs summed by an all-reduce, and tokens sharded with routed rows
+    crossing by two all-to-all exchanges.  Device-timed, max over the ranks."""
+    from oxillama_b200 import moe
+    hidden, inter, n_exp, tokens, top_k = 4096, 14336, 8, 256, 2
+    b, e = moe.expert_range(n_exp, world, rank)
+    g = S.gen_weight(qtype, inter, hidden, seed=5, stream=0)
+    u = S.gen_weight(qtype, inter, hidden, seed=5, stream=1)
+    d = S.gen_weight(qtype, hidden, inter, seed=5, stream=2)
+    n_local = e - b
+    ex = moe.MoeExperts(qtype, [g] * n_local, [u] * n_local, [d] * n_local, hidden, inter, n_exp,
+                        expert_begin=b, ctx=ctx)
+    rng = np.random.default_rng(5)
+    logits = torch.from_numpy(rng.standard_normal((tokens, n_exp)).astype(np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((tokens, hidden)).astype(np.float32)).cuda()
+
+    def rows_forward(lg, xr, k):
+        y = torch.empty((xr.shape[0], hidden), device="cuda")
+        ex.forward(lg, xr, y, k)
+        return y
+
+    lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+    summed = moe.ExpertShardedMoe(n_exp, world, rank, rows_forward)
+    exchanged = moe.TokenExchangeMoe(n_exp, world, rank, rows_forward)
+    my_logits, my_x = logits[lo:hi].contiguous(), x[lo:hi].contiguous()
+    out = {}
+    with torch.cuda.stream(stream):
+        for name, step in (("all_reduce", lambda: summed.forward(logits, x, top_k)),
+                           ("token_exchange", lambda: exchanged.forward(my_logits, my_x, top_k))):
+            for _ in range(2):
+                step()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            iters = 5
+            e0.record(stream)
+            for _ in range(iters):
+                step()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out[name] = {"ms": float(t), "tflops_aggregate": 180.39e9 / float(t) / 1e9}
+    ex.free()
+    out["workload"] = (f"config[4]: 8 x {S.NAMES[qtype]} experts over {world} GPUs, 256 tokens, top-2, whole layer "
+                       "with its collective: all_reduce = tokens replicated, outputs summed by NCCL; "
+                       "token_exchange = 256 / N tokens owned per rank, routed rows by NCCL all-to-all and back "
+                       "(the ids are read back to the host for the split sizes)")
+    return out
 
 
 class ClockSampler:
@@ -687,6 +739,7 @@ def run_ours(args):
             r["tflops_aggregate"] = 180.39e9 / r["ms"] / 1e9
             r["note"] = "local experts' share only; the all-reduce of the outputs is not in the figure"
             extras["moe"] = [r]
+            extras["moe_layer"] = moe_layer_rates(torch, dist, ctx, S.IQ4_XS, stream, world, rank)
 
     t = torch.tensor([ms, (e2e_s or 0.0) * 1e3, kernel_ms, chain_ms or 0.0], device="cuda", dtype=torch.float64)
     if world > 1:

@@ -144,10 +144,10 @@ def exchange_plan(ids: np.ndarray, n_experts: int, world: int):
     send_idx = toks.astype(np.int32)
     per_row = max(1, min(top_k, world))
     back = np.full((tokens, per_row), -1, dtype=np.int32)
-    fill = np.zeros(tokens, dtype=np.int64)
-    for pos, t in enumerate(toks):
-        back[t, fill[t]] = pos
-        fill[t] += 1
+    order = np.argsort(toks, kind="stable")  # a token's rows together, still in rank order
+    st = toks[order]
+    first = np.searchsorted(st, st, side="left")
+    back[st, np.arange(len(st)) - first] = order
     return send_idx, send_counts, back
 
 
