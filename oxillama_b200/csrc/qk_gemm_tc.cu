@@ -967,7 +967,9 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   // needs four K splits instead of two, 36.9 -> 39.1 us); only built for BN = 256.
   constexpr bool HAS2 = BN == 256;
   const uint32_t units2 = ((L.rows + RH * BM - 1) / (RH * BM)) * (((m + BN - 1) / BN) / 2);
-  const bool two = HAS2 && !ga && m > (uint32_t)BN && ((m + BN - 1) / BN) % 2 == 0 &&
+  // (four issuers two stages each: with fewer than four stages a stage would be three uses ahead of
+  // its slowest reader, more than the two "full" barriers per stage tell apart)
+  const bool two = HAS2 && !ga && S.b_stages >= 4 && m > (uint32_t)BN && ((m + BN - 1) / BN) % 2 == 0 &&
                    (units2 * 5 >= (uint32_t)sm_count * 3 || qk_knob("QK_GEMM_TBU2")) && !qk_knob("QK_GEMM_TBU1");
   auto kern = ga ? qk_gemm_tc_kernel<T, BN, RH, true, 1>
                  : (two ? qk_gemm_tc_kernel<T, BN, RH, false, HAS2 ? 2 : 1> : qk_gemm_tc_kernel<T, BN, RH, false, 1>);
