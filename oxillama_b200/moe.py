@@ -151,12 +151,19 @@ def exchange_plan(ids: np.ndarray, n_experts: int, world: int):
     return send_idx, send_counts, back
 
 
+def _need(t, dtype, ndim: int, what: str) -> None:
+    if not (t.is_cuda and t.dtype == dtype and t.dim() == ndim and t.is_contiguous()):
+        raise TypeError(f"{what}: need a contiguous CUDA tensor of {dtype} with {ndim} dimension(s)")
+
+
 def take_rows(x, idx, ctx=None, stream=None):
     """x[idx] on the device (`qk_moe_take_rows_dev`): x [n x width] f32, idx int32 [m]."""
     import torch
     from .device import _stream_ptr
     from .kernels import default_context
     ctx = ctx or default_context()
+    _need(x, torch.float32, 2, "x")
+    _need(idx, torch.int32, 1, "idx")
     out = torch.empty((idx.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
     ctx.check(ctx.lib.qk_moe_take_rows_dev(ctx.handle, C.c_void_p(x.data_ptr()), C.c_void_p(idx.data_ptr()),
                                            idx.shape[0], x.shape[1], C.c_void_p(out.data_ptr()), _stream_ptr(stream)))
@@ -169,6 +176,11 @@ def sum_rows(src, table, width: int, ctx=None, stream=None):
     from .device import _stream_ptr
     from .kernels import default_context
     ctx = ctx or default_context()
+    _need(table, torch.int32, 2, "table")
+    if table.shape[0] and table.shape[1]:
+        _need(src, torch.float32, 2, "src")
+        if src.shape[1] != width:
+            raise ValueError("src rows are not `width` wide")
     y = torch.empty((table.shape[0], width), dtype=torch.float32, device=table.device)
     ctx.check(ctx.lib.qk_moe_sum_rows_dev(ctx.handle, C.c_void_p(src.data_ptr()), C.c_void_p(table.data_ptr()),
                                           table.shape[0], table.shape[1], width, C.c_void_p(y.data_ptr()),
