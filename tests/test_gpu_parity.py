@@ -393,6 +393,26 @@ def _moe_case(t, hidden, inter, n_exp, tokens, seed):
     return gate, up, down, logits, x, deq(gate, inter, hidden), deq(up, inter, hidden), deq(down, hidden, inter)
 
 
+@pytest.mark.parametrize("t", [S.Q4_K, S.Q6_K, S.Q8_0, S.Q4_0, S.IQ4_XS])
+def test_rows_of_several_matrices_uploaded_as_one(t):
+    """q, k and v of a layer read the same input.  GGUF data is row-major, so their bytes one after
+    the other are the matrix [q; k; v]: one launch must give what the three give."""
+    import torch
+    from oxillama_b200.device import DeviceWeights
+    cols, shapes = 4096, (512, 128, 136)
+    ws = [S.gen_weight(t, r, cols, seed=81, stream=i) for i, r in enumerate(shapes)]
+    whole = DeviceWeights(t, np.concatenate([np.asarray(w).reshape(-1) for w in ws]), sum(shapes), cols)
+    for m in (1, 2):
+        x = S.gen_acts(m, cols, seed=81)
+        xd = torch.from_numpy(x).cuda()
+        y = torch.full((m, sum(shapes)), float("nan"), device="cuda")
+        whole.gemm(xd, y, m)
+        torch.cuda.synchronize()
+        ref = np.concatenate([O.gemm(t, w, x, m, r, cols)[1] for w, r in zip(ws, shapes)], axis=1)
+        assert rel_inf(y.cpu().numpy(), ref) <= TOL_F32
+    whole.free()
+
+
 def test_moe_route_matches_oracle():
     import torch
     from oxillama_b200 import moe
