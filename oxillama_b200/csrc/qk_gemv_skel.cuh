@@ -653,8 +653,11 @@ struct PlanMma {
 // per thread and the column pipeline spills; 8 warps (up to 255 registers) stream as fast or
 // faster at every M (14336 x 4096, M = 1: 8.2 us against 8.8 us).  12 warps in three groups
 // (128 registers) start and finish sooner when a CTA has few chunks: 3.3 against 3.8 us at
-// 1024 rows, 4.6 against 4.7 us at 4096, level from 14336 rows on.  QK_CW overrides
-// (developer knob: 8, 12 or 16).
+// 1024 rows, 4.6 against 4.7 us at 4096, level from 14336 rows on.  Q6_K, whose fragment
+// assembly costs the most arithmetic per byte, is bound by its compute warps with 8 of them:
+// 12 take the 128256 x 4096 matvec from 86.4 to 74.1 us (0.76 -> 0.89 of the copy bandwidth),
+// so it takes 12 at every row count (IQ4_XS gains 1 %, Q4_K loses 2 % at 14336 rows and both
+// keep 8).  QK_CW overrides (developer knob: 8, 12 or 16).
 inline int compute_warps(const QkLayout &L, uint32_t m) {
   static int cw_env = -1;
   if (cw_env < 0) {
@@ -664,7 +667,7 @@ inline int compute_warps(const QkLayout &L, uint32_t m) {
   }
   if (m >= 2) return cw_env == 16 ? 16 : 8;  // the 12-warp kernel is built for M = 1 only
   if (cw_env) return cw_env;
-  return (L.ktiles == 1 && L.chunks <= 1024) ? 12 : 8;
+  return (L.ktiles == 1 && (L.chunks <= 1024 || L.type == QK_T_Q6_K)) ? 12 : 8;
 }
 
 // force_cw8: always the 8-warp kernel (the route that takes its split activations from a
