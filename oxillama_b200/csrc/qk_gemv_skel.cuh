@@ -777,7 +777,9 @@ cudaError_t launch_mma(const QkLayout &L, const uint8_t *W, const float *x, floa
   // Weight tiles issued before the wait on the previous kernel; the rest of the ring follows
   // the activation loads.  Measured at 14336 x 4096, M = 1, 8 warps: with the producer a warp
   // of its own 1 tile 8.04 us, 2 7.81, 3 7.97; with the reducer issuing 1 tile 8.2 us, 2 8.3,
-  // 3 8.6; M = 2: 2 tiles 13.1 us, 3 12.9, 4 12.7.  QK_PRE overrides (developer knob).
+  // 3 8.6; M = 2: 2 tiles 13.1 us, 3 12.9, 4 12.7.  The 12-warp plans with one tile instead of
+  // two: within 1 % over the layer's shapes (Q4_0 4096^2 4.7 -> 4.5 us, Q8_0 4096^2 5.2 -> 5.3).
+  // QK_PRE overrides (developer knob).
   static int npre_env = -1;
   if (npre_env < 0) {
     const char *e = qk_knob("QK_PRE");
