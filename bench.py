@@ -291,12 +291,12 @@ def moe_layer_rates(torch, dist, ctx, qtype, stream, world, rank):
     with torch.cuda.stream(stream):
         for name, step in (("all_reduce", lambda: summed.forward(logits, x, top_k)),
                            ("token_exchange", lambda: exchanged.forward(my_logits, my_x, top_k))):
-            for _ in range(2):
+            for _ in range(3):
                 step()
             torch.cuda.synchronize()
             dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            iters = 5
+            iters = 20
             e0.record(stream)
             for _ in range(iters):
                 step()

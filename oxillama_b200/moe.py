@@ -193,7 +193,7 @@ class TokenExchangeMoe:
 
     Every rank owns its own tokens and a contiguous range of experts.  Only routed rows
     cross between the ranks: a token's activation row and its logits row go once to each
-    rank that holds one of its selected experts (an all-to-all), that rank computes its
+    rank that holds one of its selected experts (one all-to-all of packed rows), that rank computes its
     experts' weighted contribution for the rows it received (`local_forward`, on a GPU
     `MoeExperts.forward`: the router is a function of the token's own logits row, so the
     receiver recomputes the same ids and weights), the partial outputs return by the
@@ -259,10 +259,12 @@ class TokenExchangeMoe:
         cnt_out = torch.empty_like(cnt_in)
         self.all_to_all(cnt_out, cnt_in, [1] * self.world, [1] * self.world)
         rc = [int(v) for v in cnt_out.cpu().tolist()]
-        recv_x = x.new_empty((sum(rc), x.shape[1]))
-        recv_l = logits.new_empty((sum(rc), logits.shape[1]))
-        self.all_to_all(recv_x, send_x, rc, sc)
-        self.all_to_all(recv_l, send_l, rc, sc)
+        # one exchange for both: a row travels as its activations followed by its logits
+        hidden = x.shape[1]
+        packed = torch.cat((send_x, send_l), dim=1)
+        recv = x.new_empty((sum(rc), packed.shape[1]))
+        self.all_to_all(recv, packed, rc, sc)
+        recv_x, recv_l = recv[:, :hidden].contiguous(), recv[:, hidden:].contiguous()
         part = self.compute(recv_l, recv_x, top_k)
         returned = x.new_empty((sum(sc), x.shape[1]))
         self.all_to_all(returned, part, sc, rc)
