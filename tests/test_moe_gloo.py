@@ -98,6 +98,25 @@ def test_exchange_plan():
     assert moe.expert_owner(5, 4).tolist() == [0, 0, 1, 2, 3]
 
 
+def test_exchange_plan_properties():
+    """Random routings: every (token, owning rank) pair is sent exactly once, in rank-major token
+    order; the counts match; the return table names each token's rows in rank order."""
+    rng = np.random.default_rng(21)
+    for n_exp, world, top_k, tokens in ((8, 8, 2, 33), (8, 2, 2, 17), (5, 4, 3, 9), (4, 1, 2, 6), (16, 8, 4, 64)):
+        ids = np.stack([rng.permutation(n_exp)[:top_k] for _ in range(tokens)]).astype(np.int32)
+        ids[rng.integers(0, tokens), top_k - 1] = -1  # an empty slot
+        owner = moe.expert_owner(n_exp, world)
+        send_idx, counts, back = moe.exchange_plan(ids, n_exp, world)
+        want = sorted({(int(owner[e]), t) for t in range(tokens) for e in ids[t] if e >= 0})
+        ranks = np.repeat(np.arange(world), counts)
+        assert list(zip(ranks.tolist(), send_idx.tolist())) == want
+        assert back.shape == (tokens, max(1, min(top_k, world)))
+        for t in range(tokens):
+            rows = [j for j in back[t].tolist() if j >= 0]
+            assert [(int(ranks[j]), int(send_idx[j])) for j in rows] == [p for p in want if p[1] == t]
+            assert all(j == -1 for j in back[t, len(rows):].tolist())
+
+
 def _cpu_hooks():
     """numpy / torch-on-CPU stand-ins for the device entry points of the token exchange."""
     def route_ids(logits, top_k):
