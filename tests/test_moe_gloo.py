@@ -135,18 +135,18 @@ def _cpu_hooks():
     return dict(route_ids=route_ids, take=take, total=total)
 
 
-def _exchange_worker(rank, world, port, q, split):
+def _exchange_worker(rank, world, port, q, cuts, n_exp=4):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     rng = np.random.default_rng(11)
-    n_exp, hidden, inter, tokens, top_k = 4, 32, 48, 12, 2
+    hidden, inter, tokens, top_k = 32, 48, 12, 2
     gate = rng.standard_normal((n_exp, inter, hidden)).astype(np.float32) * 0.2
     up = rng.standard_normal((n_exp, inter, hidden)).astype(np.float32) * 0.2
     down = rng.standard_normal((n_exp, hidden, inter)).astype(np.float32) * 0.2
     logits = rng.standard_normal((tokens, n_exp)).astype(np.float32)
     x = rng.standard_normal((tokens, hidden)).astype(np.float32)
     b, e = moe.expert_range(n_exp, world, rank)
-    lo, hi = (0, split) if rank == 0 else (split, tokens)  # this rank's own tokens
+    lo, hi = cuts[rank], cuts[rank + 1]  # this rank's own tokens
     layer = moe.TokenExchangeMoe(n_exp, world, rank, _local_numpy(gate, up, down, b, e), **_cpu_hooks())
     y = layer.forward(torch.from_numpy(logits[lo:hi].copy()), torch.from_numpy(x[lo:hi].copy()), top_k).numpy()
     ref = O.moe_ffn_f32(gate, up, down, logits, x, top_k)[lo:hi]
@@ -155,17 +155,19 @@ def _exchange_worker(rank, world, port, q, split):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("split", [7, 0, 12])  # ragged shares; a rank without tokens, either one
-def test_token_exchange_moe_two_ranks(split):
+# ragged shares; a rank without tokens, either one; three ranks with 2, 2 and 1 of five experts
+@pytest.mark.parametrize("cuts,n_exp", [((0, 7, 12), 4), ((0, 0, 12), 4), ((0, 12, 12), 4), ((0, 5, 5, 12), 5)])
+def test_token_exchange_moe_ranks(cuts, n_exp):
+    world = len(cuts) - 1
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 31500 + (os.getpid() % 2000) + split
-    procs = [ctx.Process(target=_exchange_worker, args=(r, 2, port, q, split)) for r in range(2)]
+    port = 31500 + (os.getpid() % 2000) + cuts[1] + 16 * world
+    procs = [ctx.Process(target=_exchange_worker, args=(r, world, port, q, cuts, n_exp)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in procs]
     for p in procs:
         p.join(60)
         assert p.exitcode == 0
-    assert sorted(r for r, _, _ in res) == [0, 1]
+    assert sorted(r for r, _, _ in res) == list(range(world))
     assert all(ok and err <= 1e-5 for _, ok, err in res), res
