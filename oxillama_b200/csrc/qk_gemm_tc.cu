@@ -52,9 +52,17 @@ namespace {
 constexpr int BM = 128;            // weight rows per tile (UMMA M)
 constexpr int BK = 64;             // columns per stage: one 128-byte swizzle row of fp16
 constexpr int NDW = 16;            // dequant / epilogue warps: four groups of four, group g owns A stage g
-constexpr int NI = 4;              // MMA-issuing warps 0..3: warp j issues the steps of A stage j
-constexpr int FIRST_DW = 5;        // warp 4: activation producer
-constexpr int NTHREADS = (FIRST_DW + NDW) * 32;
+// MMA-issuing warps 0 .. NI - 1, then the activation producer (warp NI), then the NDW expanding warps.
+// Four issuers (warp j issues the steps of A stage j) make 21 warps, which are charged as 768 threads
+// when the register file is divided: 80 registers per thread.  Q6_K's expansion spills 250-360 bytes
+// at 80 and is the slower for it, so it runs three issuers (groups 0, 1 and (2, 3) of every
+// super-block): 20 warps, 96 registers, 4096 x 14336 x 512 in 93.5 us instead of 113.7.  The other
+// formats lose with three (Q4_K 14336 x 4096 x 512: 66.3 against 62.8 us; 32-128 tokens: 33 against
+// 29 us) and keep four.
+template <int T>
+constexpr int n_issuers() { return T == QK_T_Q6_K ? 3 : 4; }
+template <int T>
+constexpr int n_threads() { return (n_issuers<T>() + 1 + NDW) * 32; }
 constexpr int MAX_RING = 8;        // most stages of the activation ring
 constexpr uint32_t A_HALF = BM * 64;  // bytes of one A half-stage: 128 rows of 32 fp16
 #ifndef QK_GEMM_UPG
@@ -517,12 +525,13 @@ __global__ void __launch_bounds__(256)
 // two token blocks (two accumulators of BN columns: all of tensor memory at BN = 256), so the
 // weights of a row block are expanded once for 512 tokens instead of twice.
 template <int T, int BN, int RH, bool GRP, int TBU>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(n_threads<T>(), 1)
     qk_gemm_tc_kernel(QkLayout L, const uint8_t *__restrict__ W,
                           const __grid_constant__ CUtensorMap xmap, const float *__restrict__ xscale,
                           float *__restrict__ y, uint64_t ldy, uint32_t m_tokens, uint32_t tok_blocks, uint32_t row_blocks,
                           uint32_t KS, unsigned *status, GemmSmem S, const __grid_constant__ QkGroups G) {
   extern __shared__ __align__(1024) unsigned char smem[];
+  constexpr int NI = n_issuers<T>(), FIRST_DW = NI + 1, NTHREADS = n_threads<T>();
   const uint32_t sbase = smem_u32(smem);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t NB = (uint32_t)S.b_stages;
@@ -635,74 +644,154 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     // ======================= MMA issuers =======================
     // A tcgen05.mma occupies the tensor pipe for the same 128 cycles whatever its M and
     // N, and the thread that issues it is held until the pipe has taken it, its barrier
-    // polls not hidden behind its own MMAs.  So four warps issue, warp j the steps of
-    // 64-column group j of every super-block: while one is held, the others poll or
-    // queue behind it, and the pipe never waits for a poll.  All accumulate into the
-    // same columns (a tile's sum does not depend on the order).
-    if (lane == 0) {
-      const uint32_t me = warp;
-      uint32_t bst = (me * TBU) % NB, buse = (me * TBU) / NB, usea = 0, i = 0;  // first of the TBU stages of this warp's next step
-      uint32_t unit = 0, upar = 0;  // the group's next unit and the parity of its use count
-      const uint32_t abar = sbase + S.a_full + me * UPG * 8, aebar = sbase + S.a_empty + me * UPG * 8;
-      const uint32_t a0 = sbase + S.a + me * UPG * A_HALF;
-      for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
-        if (!u_valid(t)) continue;
-        const uint32_t buf = i % NBUF, use = i / NBUF, nsb = sb_end(t) - sb_begin(t);
-        // the epilogue of the tile that last used these accumulators must have drained and zeroed them
-        if (use >= 1 && !mbar_wait_bounded(sbase + S.acc_empty + buf * 8, (use - 1) & 1u)) {
-          dead = true;
-          break;
+    // polls not hidden behind its own MMAs.  So several warps issue: with four, warp j the
+    // steps of 64-column group j of every super-block; with three, warps 0 and 1 those of
+    // groups 0 and 1 and warp 2 those of groups 2 and 3.  While one is held, the others poll
+    // or queue behind it, and the pipe never waits for a poll.  A group's steps stay on one
+    // warp, which therefore waits on the group's barriers in order and is never more than
+    // one phase ahead of them.  All accumulate into the same columns (a tile's sum does not
+    // depend on the order).
+    if constexpr (NI == 4) {
+      if (lane == 0) {
+        const uint32_t me = warp;
+        uint32_t bst = (me * TBU) % NB, buse = (me * TBU) / NB, usea = 0, i = 0;  // first of the TBU stages of this warp's next step
+        uint32_t unit = 0, upar = 0;  // the group's next unit and the parity of its use count
+        const uint32_t abar = sbase + S.a_full + me * UPG * 8, aebar = sbase + S.a_empty + me * UPG * 8;
+        const uint32_t a0 = sbase + S.a + me * UPG * A_HALF;
+        for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
+          if (!u_valid(t)) continue;
+          const uint32_t buf = i % NBUF, use = i / NBUF, nsb = sb_end(t) - sb_begin(t);
+          // the epilogue of the tile that last used these accumulators must have drained and zeroed them
+          if (use >= 1 && !mbar_wait_bounded(sbase + S.acc_empty + buf * 8, (use - 1) & 1u)) {
+            dead = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * ACC_COLS;
+          for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, usea++) {
+            const uint32_t bbar = sbase + S.b_full + ((buse & 1u) * MAX_RING + bst) * 8, bpar = (buse >> 1) & 1u;
+            // the second token block's tile sits in the next stage (which may be the ring's first again)
+            const uint32_t bst1 = bst + 1 == NB ? 0u : bst + 1, buse1 = bst + 1 == NB ? buse + 1 : buse;
+            const uint32_t bbar1 = sbase + S.b_full + ((buse1 & 1u) * MAX_RING + bst1) * 8, bpar1 = (buse1 >> 1) & 1u;
+            // both polls in flight together; the slow path only when one is not ready yet
+            const bool a_ok = mbar_try_wait(abar + unit * 8, upar), b_ok = mbar_try_wait(bbar, bpar);
+            if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar + unit * 8, upar) || !mbar_wait_bounded(bbar, bpar))) {
+              dead = true;
+              break;
+            }
+            if (TBU == 2 && !mbar_wait_bounded(bbar1, bpar1)) {
+              dead = true;
+              break;
+            }
+            QK_GSTAMP(usea < 64, 512 + usea * 4 + me);
+            const uint32_t b0 = sbase + S.b + bst * S.b_stage, b1 = sbase + S.b + bst1 * S.b_stage;
+  #pragma unroll
+            for (int rh = 0; rh < RH; rh++) {
+  #pragma unroll
+              for (int hf = 0; hf < 2; hf++) {
+                if ((rh | hf) && !mbar_wait_bounded(abar + unit * 8, upar)) {
+                  dead = true;
+                  break;
+                }
+                const uint32_t au = a0 + unit * A_HALF;
+                umma_f16(tmem_d + rh * BN, umma_desc_sw64(au), umma_desc(b0 + hf * 64), IDESC, 1u);
+                umma_f16(tmem_d + rh * BN, umma_desc_sw64(au + 32), umma_desc(b0 + hf * 64 + 32), IDESC, 1u);
+                if (TBU == 2) {  // the same weights into the second token block's accumulator
+                  umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au), umma_desc(b1 + hf * 64), IDESC, 1u);
+                  umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au + 32), umma_desc(b1 + hf * 64 + 32), IDESC, 1u);
+                }
+                umma_commit(aebar + unit * 8);  // the unit is free when these retire
+                if (++unit == (uint32_t)UPG) unit = 0, upar ^= 1u;
+              }
+              if (dead) break;
+            }
+            if (dead) break;
+            umma_commit(sbase + S.b_empty + bst * 8);
+            if (TBU == 2) umma_commit(sbase + S.b_empty + bst1 * 8);
+            bst += NI * TBU;
+            while (bst >= NB) bst -= NB, buse++;
+          }
+          if (dead) break;
+          umma_commit(sbase + S.acc_full + buf * 8);  // this warp's share of the tile has retired
+          i++;
         }
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * ACC_COLS;
-        for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, usea++) {
-          const uint32_t bbar = sbase + S.b_full + ((buse & 1u) * MAX_RING + bst) * 8, bpar = (buse >> 1) & 1u;
-          // the second token block's tile sits in the next stage (which may be the ring's first again)
-          const uint32_t bst1 = bst + 1 == NB ? 0u : bst + 1, buse1 = bst + 1 == NB ? buse + 1 : buse;
-          const uint32_t bbar1 = sbase + S.b_full + ((buse1 & 1u) * MAX_RING + bst1) * 8, bpar1 = (buse1 >> 1) & 1u;
-          // both polls in flight together; the slow path only when one is not ready yet
-          const bool a_ok = mbar_try_wait(abar + unit * 8, upar), b_ok = mbar_try_wait(bbar, bpar);
-          if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar + unit * 8, upar) || !mbar_wait_bounded(bbar, bpar))) {
+        if (dead) atomicOr(status, QK_DEV_TIMEOUT);
+      }
+    } else {
+      if (lane == 0) {
+        const uint32_t me = warp;
+        // Steps are numbered through the whole run of this CTA: step 4 q + g is the 64-column group g of
+        // the q-th super-block it walks.  Everything a step needs follows from its number: the A units of
+        // group g (2 RH half-units per super-block, round-robin over the group's UPG units) and the
+        // TBU activation stages of the step (round-robin over the ring).
+        uint32_t q = 0, i = 0;  // super-blocks and tiles done
+        for (uint32_t t = blockIdx.x; t < n_units && !dead; t += gridDim.x) {
+          if (!u_valid(t)) continue;
+          const uint32_t buf = i % NBUF, use = i / NBUF, nsb = sb_end(t) - sb_begin(t);
+          // the epilogue of the tile that last used these accumulators must have drained and zeroed them
+          if (use >= 1 && !mbar_wait_bounded(sbase + S.acc_empty + buf * 8, (use - 1) & 1u)) {
             dead = true;
             break;
           }
-          if (TBU == 2 && !mbar_wait_bounded(bbar1, bpar1)) {
-            dead = true;
-            break;
-          }
-          QK_GSTAMP(usea < 64, 512 + usea * 4 + me);
-          const uint32_t b0 = sbase + S.b + bst * S.b_stage, b1 = sbase + S.b + bst1 * S.b_stage;
-#pragma unroll
-          for (int rh = 0; rh < RH; rh++) {
-#pragma unroll
-            for (int hf = 0; hf < 2; hf++) {
-              if ((rh | hf) && !mbar_wait_bounded(abar + unit * 8, upar)) {
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * ACC_COLS;
+          for (uint32_t sbk = 0; sbk < nsb && !dead; sbk++, q++) {
+            for (uint32_t g = 0; g < 4 && !dead; g++) {
+              if ((g < 2 ? g : 2u) != me) continue;  // a group's steps always on the same warp, hence in order
+              const uint32_t abar = sbase + S.a_full + g * UPG * 8, aebar = sbase + S.a_empty + g * UPG * 8;
+              const uint32_t a0 = sbase + S.a + g * UPG * A_HALF;
+              uint32_t h = q * (2 * RH);  // the group's half-units before this super-block
+              const uint32_t tile = (q * 4 + g) * TBU;
+              const uint32_t bst = tile % NB, buse = tile / NB;
+              const uint32_t bbar = sbase + S.b_full + ((buse & 1u) * MAX_RING + bst) * 8, bpar = (buse >> 1) & 1u;
+              // the second token block's tile sits in the next stage (which may be the ring's first again)
+              const uint32_t bst1 = bst + 1 == NB ? 0u : bst + 1, buse1 = bst + 1 == NB ? buse + 1 : buse;
+              const uint32_t bbar1 = sbase + S.b_full + ((buse1 & 1u) * MAX_RING + bst1) * 8, bpar1 = (buse1 >> 1) & 1u;
+              {
+                const uint32_t unit = h % (uint32_t)UPG, upar = (h / (uint32_t)UPG) & 1u;
+                // both polls in flight together; the slow path only when one is not ready yet
+                const bool a_ok = mbar_try_wait(abar + unit * 8, upar), b_ok = mbar_try_wait(bbar, bpar);
+                if (!(a_ok && b_ok) && (!mbar_wait_bounded(abar + unit * 8, upar) || !mbar_wait_bounded(bbar, bpar))) {
+                  dead = true;
+                  break;
+                }
+              }
+              if (TBU == 2 && !mbar_wait_bounded(bbar1, bpar1)) {
                 dead = true;
                 break;
               }
-              const uint32_t au = a0 + unit * A_HALF;
-              umma_f16(tmem_d + rh * BN, umma_desc_sw64(au), umma_desc(b0 + hf * 64), IDESC, 1u);
-              umma_f16(tmem_d + rh * BN, umma_desc_sw64(au + 32), umma_desc(b0 + hf * 64 + 32), IDESC, 1u);
-              if (TBU == 2) {  // the same weights into the second token block's accumulator
-                umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au), umma_desc(b1 + hf * 64), IDESC, 1u);
-                umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au + 32), umma_desc(b1 + hf * 64 + 32), IDESC, 1u);
+              const uint32_t b0 = sbase + S.b + bst * S.b_stage, b1 = sbase + S.b + bst1 * S.b_stage;
+  #pragma unroll
+              for (int rh = 0; rh < RH; rh++) {
+  #pragma unroll
+                for (int hf = 0; hf < 2; hf++, h++) {
+                  const uint32_t unit = h % (uint32_t)UPG, upar = (h / (uint32_t)UPG) & 1u;
+                  if ((rh | hf) && !mbar_wait_bounded(abar + unit * 8, upar)) {
+                    dead = true;
+                    break;
+                  }
+                  const uint32_t au = a0 + unit * A_HALF;
+                  umma_f16(tmem_d + rh * BN, umma_desc_sw64(au), umma_desc(b0 + hf * 64), IDESC, 1u);
+                  umma_f16(tmem_d + rh * BN, umma_desc_sw64(au + 32), umma_desc(b0 + hf * 64 + 32), IDESC, 1u);
+                  if (TBU == 2) {  // the same weights into the second token block's accumulator
+                    umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au), umma_desc(b1 + hf * 64), IDESC, 1u);
+                    umma_f16(tmem_d + (RH + rh) * BN, umma_desc_sw64(au + 32), umma_desc(b1 + hf * 64 + 32), IDESC, 1u);
+                  }
+                  umma_commit(aebar + unit * 8);  // the unit is free when these retire
+                }
+                if (dead) break;
               }
-              umma_commit(aebar + unit * 8);  // the unit is free when these retire
-              if (++unit == (uint32_t)UPG) unit = 0, upar ^= 1u;
+              if (dead) break;
+              umma_commit(sbase + S.b_empty + bst * 8);
+              if (TBU == 2) umma_commit(sbase + S.b_empty + bst1 * 8);
             }
-            if (dead) break;
           }
           if (dead) break;
-          umma_commit(sbase + S.b_empty + bst * 8);
-          if (TBU == 2) umma_commit(sbase + S.b_empty + bst1 * 8);
-          bst += NI * TBU;
-          while (bst >= NB) bst -= NB, buse++;
+          umma_commit(sbase + S.acc_full + buf * 8);  // this warp's share of the tile has retired
+          i++;
         }
-        if (dead) break;
-        umma_commit(sbase + S.acc_full + buf * 8);  // this warp's share of the tile has retired
-        i++;
+        if (dead) atomicOr(status, QK_DEV_TIMEOUT);
       }
-      if (dead) atomicOr(status, QK_DEV_TIMEOUT);
     }
   } else if (warp >= FIRST_DW) {
     // ======================= dequant + epilogue warps =======================
@@ -1050,7 +1139,7 @@ cudaError_t launch_gemm(const QkLayout &L, const uint8_t *W, const float *x, flo
   uint32_t grid = n_tiles * ks;
   if (grid > (uint32_t)sm_count) grid = sm_count;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(NTHREADS), cfg.dynamicSmemBytes = total, cfg.stream = s;
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(n_threads<T>()), cfg.dynamicSmemBytes = total, cfg.stream = s;
   cfg.attrs = at, cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, L, W, map, (const float *)xscale, y, ldy, m, tok_units, row_blocks, ks, status, S, G);
 }
