@@ -760,7 +760,10 @@ def run_ours(args):
             r["tflops_aggregate"] = 180.39e9 / r["ms"] / 1e9
             r["note"] = "local experts' share only; the all-reduce of the outputs is not in the figure"
             extras["moe"] = [r]
-            extras["moe_layer"] = moe_layer_rates(torch, dist, ctx, S.IQ4_XS, stream, world, rank)
+            try:
+                extras["moe_layer"] = moe_layer_rates(torch, dist, ctx, S.IQ4_XS, stream, world, rank)
+            except Exception as exc:  # an auxiliary figure: report it, keep the line
+                extras["moe_layer"] = {"error": repr(exc)}
 
     t = torch.tensor([ms, (e2e_s or 0.0) * 1e3, kernel_ms, chain_ms or 0.0], device="cuda", dtype=torch.float64)
     if world > 1:
