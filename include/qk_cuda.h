@@ -165,8 +165,8 @@ int qk_gguf_tensor_info(const qk_gguf *g, const char *name, int *type, size_t *n
 /* qk_weights_upload of rows [row_begin, row_end) of the named tensor, rows = dimensions[0] and
  * columns = dimensions[1] as the reference reads them, straight from the file: the row range
  * is one contiguous byte range, read through pinned staging buffers, never copied into
- * pageable memory.  Unknown name: QK_INVALID_ARGUMENT; a type outside the five served:
- * QK_UNSUPPORTED_TYPE; data past the end of the file: QK_BUFFER_TOO_SMALL. */
+ * pageable memory.  Unknown name: QK_INVALID_ARGUMENT; a type this library does not
+ * serve: QK_UNSUPPORTED_TYPE; data past the end of the file: QK_BUFFER_TOO_SMALL. */
 int qk_weights_upload_gguf(qk_ctx *ctx, const qk_gguf *g, const char *name, size_t row_begin, size_t row_end,
                            qk_weights **out);
 
